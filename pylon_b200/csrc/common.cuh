@@ -1,0 +1,107 @@
+// Shared helpers of the sm_100a kernels: element types, 32-bit conversions, reductions,
+// and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int pylon_<name>(..., cudaStream_t stream)`.  It returns
+// 0 when the launch was enqueued, or a negative code: -1 for arguments it refuses (the text
+// is kept for pylon_last_error()), -2 when the CUDA runtime refused the launch.  No entry
+// point allocates memory or synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define PYLON_DTYPE_F32 0
+#define PYLON_DTYPE_BF16 1
+
+namespace pylon {
+
+// Text of the last refused call in this thread's library.
+inline char* last_error_buffer() {
+  static thread_local char buffer[512] = {0};
+  return buffer;
+}
+
+#define PYLON_REFUSE(...)                                              \
+  do {                                                                 \
+    snprintf(pylon::last_error_buffer(), 512, __VA_ARGS__);            \
+    return -1;                                                         \
+  } while (0)
+
+#define PYLON_CHECK_LAUNCH(name)                                       \
+  do {                                                                 \
+    cudaError_t err__ = cudaGetLastError();                            \
+    if (err__ != cudaSuccess) {                                        \
+      snprintf(pylon::last_error_buffer(), 512, "%s: %s", name,        \
+               cudaGetErrorString(err__));                             \
+      return -2;                                                       \
+    }                                                                  \
+    return 0;                                                          \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds
+// at least 33 floats of shared memory.  Safe to call repeatedly with the same scratch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : 0.f;
+    w = warp_sum(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : -INFINITY;
+    w = warp_max(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace pylon
+
+// One copy per shared library (each library is built from one translation unit; weak in case
+// several are linked together).
+extern "C" __attribute__((weak)) const char* pylon_last_error() { return pylon::last_error_buffer(); }

@@ -1,0 +1,311 @@
+// Memory-bound kernels around the matrix products: embedding gather, residual add fused
+// with RMSNorm, per-head q/k RMSNorm fused with the rotary rotation and the write of keys
+// and values into cache pages, SwiGLU.  All arithmetic is float32; `T` is only the type
+// activations and cache pages are stored in (float or bfloat16).
+//
+// Replaces these library call sites of raun6k/Pylon: the embedding lookup
+// (src/pylon/model/model.py:133), RMSNorm (src/pylon/model/layers.py:30-40), q/k norm and
+// rotation (layers.py:132-134, 73-78), the page write (src/pylon/kv/cache.py:302-313),
+// silu(gate)*up (layers.py:27) and the residual adds (layers.py:191,200).
+#include "common.cuh"
+
+namespace pylon {
+
+// -----------------------------------------------------------------------------------------
+// embedding: residual[t, :] = table[ids[t], :]   (residual stream is float32)
+// -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                    float* __restrict__ out, int width, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host
+  const T* row = table + (size_t)id * width;
+  float* dst = out + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float<T>(row[i]);
+}
+
+// -----------------------------------------------------------------------------------------
+// residual add + RMSNorm
+//   x = residual[row] (+ delta[row]);  if write_residual: residual[row] = x
+//   out[r] = x / sqrt(mean(x^2) + eps) * weight          (out row r, compact)
+// `rows` (optional) selects which residual rows are normalised; out is [n_rows, width].
+// -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, const int* __restrict__ rows,
+                                   T* __restrict__ out, int width, float eps, int write_residual) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* res = residual + (size_t)row * width;
+  const T* del = delta ? delta + (size_t)row * width : nullptr;
+  T* dst = out + (size_t)r * width;
+  float sumsq = 0.f;
+  // Pass 1: form the 32-bit sum, keep it (in the residual or, when it must not be
+  // written, recomputed in pass 2) and accumulate the square sum.
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = res[i];
+    if (del) x += to_float<T>(del[i]);
+    if (write_residual) res[i] = x;
+    sumsq += x * x;
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float inv = rsqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = res[i];
+    if (del && !write_residual) x += to_float<T>(del[i]);
+    dst[i] = from_float<T>(x * inv * weight[i]);
+  }
+}
+
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) residual[i] += to_float<T>(delta[i]);
+}
+
+// -----------------------------------------------------------------------------------------
+// q/k RMSNorm + rotary rotation + cache write.  One warp per (token, head).
+//   head < nq            : q head, normalised, rotated, written back in place
+//   nq <= head < nq+nkv  : k head, normalised, rotated, written to its page slot
+//   else                 : v head, copied to its page slot
+// Rotation pairs (j, j + rd/2) for j < rd/2 with cos/sin[pos, j]; elements >= rd pass.
+// -----------------------------------------------------------------------------------------
+template <typename T, int MAX_PER_LANE>
+__global__ void qk_norm_rope_kv_write_kernel(
+    T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    float eps, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+    int rotary_dim, int table_positions, const int* __restrict__ positions,
+    const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width,
+    int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
+    int d, int num_tokens) {
+  extern __shared__ float exchange[];  // [warps per block][d]
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)num_tokens * heads) return;
+  const int t = (int)(item / heads), head = (int)(item % heads);
+  T* src = qkv + ((size_t)t * heads + head) * d;
+  const int pos = positions[t];
+
+  T* page_dst = nullptr;
+  if (head >= nq) {
+    const int row = token_row[t];
+    const int page = block_table[(size_t)row * table_width + pos / page_size];
+    if (page < 0 || page >= num_pages) return;  // never for a prepared step; keeps memory safe
+    const int kv_head = (head - nq) % nkv;
+    T* pages = head < nq + nkv ? k_pages : v_pages;
+    page_dst = pages + (((size_t)page * nkv + kv_head) * page_size + pos % page_size) * d;
+  }
+  if (head >= nq + nkv) {  // value: plain copy
+    for (int e = lane; e < d; e += 32) page_dst[e] = src[e];
+    return;
+  }
+
+  float x[MAX_PER_LANE];
+  float sumsq = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAX_PER_LANE; ++k) {
+    const int e = lane + 32 * k;
+    x[k] = e < d ? to_float<T>(src[e]) : 0.f;
+    sumsq += x[k] * x[k];
+  }
+  const float* weight = head < nq ? q_weight : k_weight;
+  if (weight) {
+    sumsq = warp_sum(sumsq);
+    const float inv = rsqrtf(sumsq / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < MAX_PER_LANE; ++k) {
+      const int e = lane + 32 * k;
+      if (e < d) x[k] = x[k] * inv * weight[e];
+    }
+  }
+  T* dst = head < nq ? src : page_dst;
+  if (rotary_dim > 0 && cos_table) {
+    float* mine = exchange + (size_t)warp * d;
+#pragma unroll
+    for (int k = 0; k < MAX_PER_LANE; ++k) {
+      const int e = lane + 32 * k;
+      if (e < d) mine[e] = x[k];
+    }
+    __syncwarp();
+    const int half = rotary_dim >> 1;
+    const int p = pos < table_positions ? pos : table_positions - 1;  // host checks the range
+    const float* c = cos_table + (size_t)p * half;
+    const float* s = sin_table + (size_t)p * half;
+#pragma unroll
+    for (int k = 0; k < MAX_PER_LANE; ++k) {
+      const int e = lane + 32 * k;
+      if (e < d) {
+        float y = x[k];
+        if (e < half) y = x[k] * c[e] - mine[e + half] * s[e];
+        else if (e < rotary_dim) y = x[k] * c[e - half] + mine[e - half] * s[e - half];
+        dst[e] = from_float<T>(y);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < MAX_PER_LANE; ++k) {
+      const int e = lane + 32 * k;
+      if (e < d) dst[e] = from_float<T>(x[k]);
+    }
+  }
+}
+
+// -----------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
+// -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = to_float<T>(gate_up[t * 2 * inter + c]);
+    const float u = to_float<T>(gate_up[t * 2 * inter + inter + c]);
+    // float storage is the true 32-bit path: full-precision exponential there
+    const float e = sizeof(T) == 4 ? expf(-g) : __expf(-g);
+    out[i] = from_float<T>(g / (1.f + e) * u);
+  }
+}
+
+// Vector form for bfloat16 rows whose width is a multiple of 8 (16-byte accesses).
+__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int inter8,
+                                     size_t total8) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total8; i += stride) {
+    const size_t t = i / inter8;
+    const int c = (int)(i - t * inter8);
+    uint4 g4 = gate_up[t * 2 * inter8 + c];
+    uint4 u4 = gate_up[t * 2 * inter8 + inter8 + c];
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]);
+      const float2 u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+    out[i] = o4;
+  }
+}
+
+}  // namespace pylon
+
+using namespace pylon;
+
+extern "C" int pylon_embed_gather(const int* ids, const void* table, float* out, int num_tokens, int width,
+                                  int vocab, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (width <= 0 || vocab <= 0) PYLON_REFUSE("embed_gather: width %d, vocab %d", width, vocab);
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == PYLON_DTYPE_F32)
+    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab);
+  else if (dtype == PYLON_DTYPE_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab);
+  else
+    PYLON_REFUSE("embed_gather: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("embed_gather");
+}
+
+extern "C" int pylon_add_rmsnorm(float* residual, const void* delta, const float* weight, const int* rows,
+                                 void* out, int n_rows, int width, float eps, int write_residual, int dtype,
+                                 cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (width <= 0) PYLON_REFUSE("add_rmsnorm: width %d", width);
+  if (rows && write_residual) PYLON_REFUSE("add_rmsnorm: a row selection cannot update the residual");
+  const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+  if (dtype == PYLON_DTYPE_F32)
+    add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, rows, (float*)out, width, eps, write_residual);
+  else if (dtype == PYLON_DTYPE_BF16)
+    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, width, eps, write_residual);
+  else
+    PYLON_REFUSE("add_rmsnorm: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("add_rmsnorm");
+}
+
+extern "C" int pylon_residual_add(float* residual, const void* delta, long long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  if (dtype == PYLON_DTYPE_F32)
+    residual_add_kernel<float><<<blocks, threads, 0, stream>>>(residual, (const float*)delta, (size_t)n);
+  else if (dtype == PYLON_DTYPE_BF16)
+    residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (size_t)n);
+  else
+    PYLON_REFUSE("residual_add: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("residual_add");
+}
+
+template <typename T>
+static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float eps, const float* cos_t,
+                               const float* sin_t, int rotary_dim, int table_positions, const int* positions,
+                               const int* token_row, const int* block_table, int table_width, int page_size,
+                               T* k_pages, T* v_pages, int num_pages, int nq, int nkv, int d, int num_tokens,
+                               cudaStream_t stream) {
+  const int warps = 4;
+  const long long items = (long long)num_tokens * (nq + 2 * nkv);
+  const int blocks = (int)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * d * sizeof(float);
+#define PYLON_LAUNCH_QK(N)                                                                              \
+  qk_norm_rope_kv_write_kernel<T, N><<<blocks, warps * 32, smem, stream>>>(                             \
+      qkv, qw, kw, eps, cos_t, sin_t, rotary_dim, table_positions, positions, token_row, block_table,   \
+      table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, num_tokens)
+  if (d <= 32) PYLON_LAUNCH_QK(1);
+  else if (d <= 64) PYLON_LAUNCH_QK(2);
+  else if (d <= 128) PYLON_LAUNCH_QK(4);
+  else if (d <= 256) PYLON_LAUNCH_QK(8);
+  else PYLON_LAUNCH_QK(16);
+#undef PYLON_LAUNCH_QK
+  PYLON_CHECK_LAUNCH("qk_norm_rope_kv_write");
+}
+
+extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, const float* k_weight, float eps,
+                                           const float* cos_table, const float* sin_table, int rotary_dim,
+                                           int table_positions, const int* positions, const int* token_row,
+                                           const int* block_table, int table_width, int page_size,
+                                           void* k_pages, void* v_pages, int num_pages, int nq, int nkv, int d,
+                                           int num_tokens, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (d < 2 || d > 512) PYLON_REFUSE("qk_norm_rope_kv_write: head size %d is outside 2..512", d);
+  if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1))
+    PYLON_REFUSE("qk_norm_rope_kv_write: rotary size %d must be even and at most the head size %d", rotary_dim, d);
+  if (nq < 0 || nkv < 1 || page_size < 1 || table_width < 1)
+    PYLON_REFUSE("qk_norm_rope_kv_write: heads %d/%d, page size %d, table width %d", nq, nkv, page_size, table_width);
+  if (dtype == PYLON_DTYPE_F32)
+    return launch_qk_norm_rope<float>((float*)qkv, q_weight, k_weight, eps, cos_table, sin_table, rotary_dim,
+                                      table_positions, positions, token_row, block_table, table_width, page_size,
+                                      (float*)k_pages, (float*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
+  if (dtype == PYLON_DTYPE_BF16)
+    return launch_qk_norm_rope<__nv_bfloat16>((__nv_bfloat16*)qkv, q_weight, k_weight, eps, cos_table, sin_table,
+                                              rotary_dim, table_positions, positions, token_row, block_table,
+                                              table_width, page_size, (__nv_bfloat16*)k_pages,
+                                              (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
+  PYLON_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
+}
+
+extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int dtype,
+                            cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (inter <= 0) PYLON_REFUSE("swiglu: intermediate size %d", inter);
+  const size_t total = (size_t)num_tokens * inter;
+  const int threads = 256;
+  auto grid = [&](size_t n) { size_t b = (n + threads - 1) / threads; return (int)(b < 148 * 32 ? b : 148 * 32); };
+  if (dtype == PYLON_DTYPE_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+    swiglu_bf16x8_kernel<<<grid(total / 8), threads, 0, stream>>>((const uint4*)gate_up, (uint4*)out, inter / 8, total / 8);
+  } else if (dtype == PYLON_DTYPE_BF16) {
+    swiglu_kernel<__nv_bfloat16><<<grid(total), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+  } else if (dtype == PYLON_DTYPE_F32) {
+    swiglu_kernel<float><<<grid(total), threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  } else {
+    PYLON_REFUSE("swiglu: unknown dtype %d", dtype);
+  }
+  PYLON_CHECK_LAUNCH("swiglu");
+}

@@ -1,0 +1,312 @@
+"""Python entry points of the sm_100a kernels (``pylon_b200/csrc``).
+
+Each function checks its tensors (device, dtype, contiguity, sizes), launches on torch's
+current CUDA stream and returns without synchronising.  There is no CPU path: a tensor that
+is not on a CUDA device, or a kernel library that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from pylon_b200.kernels import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels run in float32 or bfloat16, not {dtype}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("pylon_b200 kernels need CUDA tensors; there is no CPU path")
+
+
+def _need(condition: bool, text: str) -> None:
+    if not condition:
+        raise KernelError(text)
+
+
+def _check(library: ctypes.CDLL, code: int) -> None:
+    if code != 0:
+        raise KernelError(library.pylon_last_error().decode(errors="replace") or f"kernel call failed ({code})")
+
+
+_SIGNATURES = {
+    "elementwise.cu": {
+        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "pylon_residual_add": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+        "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
+    "gemm_f32.cu": {
+        "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
+    },
+    "attention_simple.cu": {
+        "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                         c_int, c_int, c_void_p],
+    },
+    "sampling.cu": {
+        "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    },
+}
+
+
+def _library(source: str, defines: Optional[dict[str, int]] = None) -> ctypes.CDLL:
+    library = build.load(source, defines)
+    if not getattr(library, "_pylon_typed", False):
+        for name, argtypes in _SIGNATURES.get(source, {}).items():
+            function = getattr(library, name)
+            function.argtypes = argtypes
+            function.restype = c_int
+        library._pylon_typed = True
+    return library
+
+
+def build_all() -> list[str]:
+    names = []
+    for source in _SIGNATURES:
+        _library(source)
+        names.append(build.library_name(source))
+    return names
+
+
+# ---------------------------------------------------------------------------------------
+# embedding, norms, residual
+# ---------------------------------------------------------------------------------------
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``."""
+    _need_cuda(ids, table, out)
+    _need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), "embed_gather: ids must be contiguous int32 [T]")
+    _need(table.dim() == 2 and table.is_contiguous(), "embed_gather: table must be contiguous [vocab, width]")
+    tokens, (vocab, width) = ids.shape[0], table.shape
+    if out is None:
+        out = torch.empty((tokens, width), dtype=torch.float32, device=table.device)
+    _need(out.dtype == torch.float32 and out.shape == (tokens, width) and out.is_contiguous(), "embed_gather: out must be contiguous float32 [T, width]")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), _stream()))
+    return out
+
+
+def add_rmsnorm(
+    residual: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    weight: torch.Tensor,
+    eps: float,
+    out_dtype: torch.dtype,
+    rows: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``residual += delta`` (float32, in place, skipped when ``rows`` selects rows), then
+    RMSNorm of the selected rows with the float32 ``weight``; returns ``out_dtype [n, width]``."""
+    _need_cuda(residual, delta, weight, rows, out)
+    _need(residual.dtype == torch.float32 and residual.dim() == 2 and residual.is_contiguous(), "add_rmsnorm: residual must be contiguous float32 [T, width]")
+    tokens, width = residual.shape
+    _need(weight.dtype == torch.float32 and weight.shape == (width,) and weight.is_contiguous(), "add_rmsnorm: weight must be float32 [width]")
+    if delta is not None:
+        _need(delta.shape == residual.shape and delta.is_contiguous() and delta.dtype == out_dtype, "add_rmsnorm: delta must be contiguous [T, width] in the activation dtype")
+    n_rows = tokens
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(), "add_rmsnorm: rows must be contiguous int32")
+        n_rows = rows.shape[0]
+    if out is None:
+        out = torch.empty((n_rows, width), dtype=out_dtype, device=residual.device)
+    _need(out.shape == (n_rows, width) and out.dtype == out_dtype and out.is_contiguous(), "add_rmsnorm: out has the wrong shape or dtype")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(rows), _ptr(out), n_rows, width,
+                                              float(eps), 0 if rows is not None else 1, _dtype_code(out_dtype), _stream()))
+    return out
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    _need_cuda(residual, delta)
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and delta.is_contiguous() and delta.shape == residual.shape, "residual_add: shapes differ or tensors are not contiguous")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_residual_add(_ptr(residual), _ptr(delta), residual.numel(), _dtype_code(delta.dtype), _stream()))
+
+
+def qk_norm_rope_kv_write(
+    qkv: torch.Tensor,
+    q_weight: Optional[torch.Tensor],
+    k_weight: Optional[torch.Tensor],
+    eps: float,
+    cos: Optional[torch.Tensor],
+    sin: Optional[torch.Tensor],
+    rotary_dim: int,
+    positions: torch.Tensor,
+    token_row: torch.Tensor,
+    block_table: torch.Tensor,
+    page_size: int,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    nq: int,
+    nkv: int,
+    head_dim: int,
+) -> None:
+    """On ``qkv [T, (nq + 2 nkv) * d]``: RMSNorm each q and k head (when weights are given),
+    rotate them by the float32 ``cos``/``sin [positions, rotary_dim / 2]`` tables, write q
+    back in place and k, v into ``[pages, nkv, page_size, d]`` pages at each token's slot."""
+    _need_cuda(qkv, q_weight, k_weight, cos, sin, positions, token_row, block_table, k_pages, v_pages)
+    tokens = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + 2 * nkv) * head_dim, "qk_norm_rope_kv_write: qkv must be contiguous [T, (nq + 2 nkv) * d]")
+    for weight in (q_weight, k_weight):
+        if weight is not None:
+            _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "qk_norm_rope_kv_write: norm weights must be float32 [d]")
+    table_positions = 0
+    if cos is not None:
+        _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape
+              and cos.dim() == 2 and cos.shape[1] * 2 == rotary_dim and cos.is_contiguous() and sin.is_contiguous(),
+              "qk_norm_rope_kv_write: cos/sin must be float32 [positions, rotary_dim / 2]")
+        table_positions = cos.shape[0]
+    else:
+        rotary_dim = 0
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "qk_norm_rope_kv_write: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "qk_norm_rope_kv_write: block_table must be contiguous int32 [rows, width]")
+    for pages in (k_pages, v_pages):
+        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, head_dim),
+              "qk_norm_rope_kv_write: pages must be contiguous [pages, nkv, page_size, d] in the activation dtype")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_qk_norm_rope_kv_write(
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
+        _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
+        k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` of shape ``[T, 2 * inter]``."""
+    _need_cuda(gate_up, out)
+    _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "swiglu: gate_up must be contiguous [T, 2 * inter]")
+    tokens, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out.shape == (tokens, inter) and out.dtype == gate_up.dtype and out.is_contiguous(), "swiglu: out has the wrong shape or dtype")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, _dtype_code(gate_up.dtype), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# matrix products: y = x @ w.T
+# ---------------------------------------------------------------------------------------
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x [M, K] @ w [N, K].T`` with float32 accumulation.
+
+    float32 operands use the plain-FMA kernel (true 32-bit, no tensor cores).  bfloat16
+    operands go to the library matrix product, as raun6k/Pylon's ``nn.Linear`` layers do
+    (src/pylon/model/layers.py:17-23,95-106); ``out_dtype=torch.float32`` keeps the 32-bit
+    accumulator (used for logits).
+    """
+    _need_cuda(x, w)
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
+    _need(x.dtype == w.dtype, f"linear: activations are {x.dtype} but weights are {w.dtype}")
+    _need(x.stride(1) == 1 and w.stride(1) == 1, "linear: the reduced dimension must be contiguous")
+    out_dtype = out_dtype or x.dtype
+    m, k = x.shape
+    n = w.shape[0]
+    if x.dtype == torch.float32:
+        _need(out_dtype == torch.float32, "linear: float32 operands give float32 results")
+        y = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        library = _library("gemm_f32.cu")
+        _check(library, library.pylon_gemm_f32_nt(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), n, _stream()))
+        return y
+    _need(x.dtype == torch.bfloat16, f"linear: unsupported dtype {x.dtype}")
+    if out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    _need(out_dtype == torch.float32, f"linear: unsupported result dtype {out_dtype}")
+    return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+# ---------------------------------------------------------------------------------------
+# attention over the paged cache
+# ---------------------------------------------------------------------------------------
+def paged_attention(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    positions: torch.Tensor,
+    token_row: torch.Tensor,
+    block_table: torch.Tensor,
+    nq: int,
+    window: Optional[int] = None,
+    scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Causal attention of every token of a step over its request's pages.
+
+    ``q``: ``[T, >= nq * d]`` (only the first ``nq * d`` columns of each row are read, so
+    the fused qkv buffer can be passed as it is); pages ``[P, nkv, page_size, d]``;
+    ``positions``/``token_row`` int32 ``[T]``; ``block_table`` int32 ``[rows, width]``.
+    Returns ``[T, nq * d]``.
+    """
+    _need_cuda(q, k_pages, v_pages, positions, token_row, block_table, out)
+    _need(k_pages.dim() == 4 and k_pages.shape == v_pages.shape and k_pages.is_contiguous() and v_pages.is_contiguous(), "paged_attention: pages must be contiguous [P, nkv, page_size, d]")
+    num_pages, nkv, page_size, d = k_pages.shape
+    tokens = q.shape[0]
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= nq * d and q.dtype == k_pages.dtype, "paged_attention: q must be [T, >= nq * d] in the cache dtype")
+    _need(nq % nkv == 0, f"paged_attention: {nq} query heads over {nkv} KV heads")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "paged_attention: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "paged_attention: block_table must be contiguous int32 [rows, width]")
+    if out is None:
+        out = torch.empty((tokens, nq * d), dtype=q.dtype, device=q.device)
+    _need(out.shape == (tokens, nq * d) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
+    scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
+    library = _library("attention_simple.cu")
+    _check(library, library.pylon_paged_attention_simple(
+        _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
+        block_table.shape[1], page_size, num_pages, nq, nkv, d, int(window or 0), scale, tokens, _dtype_code(q.dtype), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------
+def sample(
+    logits: torch.Tensor,
+    temperature: Optional[torch.Tensor] = None,
+    top_p: Optional[torch.Tensor] = None,
+    uniform: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One token per row of float32 ``logits [R, vocab]``: arg-max where a row's temperature
+    is 0 (or none is given), else a draw from ``softmax(logits / T)`` cut to the ``top_p``
+    nucleus, using the row's number from ``uniform`` (float32 in [0, 1))."""
+    _need_cuda(logits, temperature, top_p, uniform, out)
+    _need(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 [R, vocab]")
+    rows, vocab = logits.shape
+    for per_row in (temperature, top_p, uniform):
+        if per_row is not None:
+            _need(per_row.dtype == torch.float32 and per_row.is_contiguous() and per_row.shape[0] >= rows, "sample: per-row parameters must be float32 [R]")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _need(out.dtype == torch.int32 and out.is_contiguous() and out.shape[0] >= rows, "sample: out must be int32 [R]")
+    library = _library("sampling.cu")
+    _check(library, library.pylon_sample(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(out), _stream()))
+    return out
