@@ -1,0 +1,164 @@
+"""The engine: a model folder in, generated tokens out, on one GPU.
+
+:class:`Engine` loads the model the folder's ``config.json`` names, sets up the cache
+manager, the step function, the sampler and the scheduler, and offers two levels of use:
+
+* ``generate(prompts, sampling)`` — the Python entry point: runs the scheduler until every
+  prompt has its tokens (raun6k/Pylon's counterpart is ``Engine.enqueue`` plus its
+  scheduler thread, src/pylon/engine.py:241-267; here the caller's thread drives the ticks).
+* ``open`` / ``step`` / ``close`` — the step function itself, for callers that decide the
+  batches themselves (trace replay, benchmarks, tests).
+"""
+from __future__ import annotations
+
+import math
+from pathlib import Path
+from typing import Optional, Sequence
+
+import torch
+
+from pylon_b200.cache.manager import CacheManager, RequestCache
+from pylon_b200.config.engine_config import EngineConfig
+from pylon_b200.config.registry import read_config
+from pylon_b200.engine.scheduler import GenerationResult, Scheduler
+from pylon_b200.engine.step import StepEntry, StepFunction
+from pylon_b200.models.decoder import DecoderModel
+from pylon_b200.sampling.params import SamplingParams
+from pylon_b200.sampling.sampler import Sampler
+from pylon_b200.weights.loader import Checkpoint
+
+
+def require_gpu(device: Optional[str | torch.device] = None) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("pylon_b200 needs a CUDA device (NVIDIA B200, sm_100a); there is no CPU path")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    major, minor = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise RuntimeError(f"pylon_b200's kernels are built for sm_100a; this device is sm_{major}{minor}")
+    return device
+
+
+class Engine:
+    def __init__(self, model_dir: str | Path, config: Optional[EngineConfig] = None, device: Optional[str | torch.device] = None) -> None:
+        self.config = config or EngineConfig()
+        self.device = require_gpu(device)
+        self.model_dir = Path(model_dir)
+        self.architecture, self.model_config = read_config(self.model_dir)
+        dtype = self.config.torch_dtype
+
+        checkpoint = Checkpoint(self.model_dir)
+        limit = self.config.max_context
+        if limit is None and self.config.max_cache_tokens is not None:
+            limit = self.config.max_cache_tokens
+        self.spec = self.architecture.build_spec(self.model_config, limit)
+        self.model = DecoderModel(self.spec)
+        checkpoint.verify(self.model.tensor_decls(), self.spec.ignored_tensors)
+        with torch.cuda.device(self.device):
+            self.model.load(checkpoint.fetch, dtype, self.device)
+            needs = self.model.cache_needs()
+            cache_of = [run.cache_of for run in self.spec.order]
+            page_size = self.config.page_size
+            num_pages = self._pool_pages(needs, dtype, page_size)
+            self.cache = CacheManager(
+                needs, cache_of, page_size=page_size, num_pages=num_pages,
+                max_requests=self.config.max_batch_size, dtype=dtype, device=self.device,
+            )
+        self.max_context = min(self.spec.max_positions, num_pages * page_size)
+        self.step_function = StepFunction(self.model, self.cache)
+        self.sampler = Sampler(self.device)
+        self.scheduler = Scheduler(
+            self.cache, self.step_function, self.sampler,
+            max_batch_size=self.config.max_batch_size, prefill_chunk_size=self.config.prefill_chunk_size,
+            max_queue_size=self.config.max_queue_size, admit_skip=self.config.admit_skip, seed=self.config.seed,
+        )
+        self._next_id = 0
+
+    # -- sizing ----------------------------------------------------------------------------
+    def _pool_pages(self, needs, dtype: torch.dtype, page_size: int) -> int:
+        if self.config.max_cache_tokens is not None:
+            return max(1, math.ceil(self.config.max_cache_tokens / page_size))
+        element = torch.empty((), dtype=dtype).element_size()
+        per_token = sum(2 * need.kv.n_kv_heads * need.kv.head_dim * element for need in needs if need is not None and need.kv is not None)
+        free, total = torch.cuda.mem_get_info(self.device)
+        # What is left of the allowed share of the device after the weights, less room for
+        # activations of one full step (raun6k/Pylon sizes its pool the same way,
+        # src/pylon/kv/budget.py:70-113).
+        activation_room = self.config.prefill_chunk_size * self.spec.width * 64
+        budget = int(total * self.config.max_gpu_utilization) - (total - free) - activation_room
+        if per_token == 0:
+            return 1
+        pages = budget // (per_token * page_size)
+        limit = math.ceil(self.spec.max_positions / page_size) * self.config.max_batch_size
+        if pages < 1:
+            raise RuntimeError("no memory is left for the cache after loading the weights")
+        return int(min(pages, limit))
+
+    # -- the step function, for callers that batch themselves --------------------------------
+    def open(self, request_id: object, capacity: int) -> RequestCache:
+        return self.cache.open(request_id, capacity)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        with torch.cuda.device(self.device):
+            return self.step_function(entries)
+
+    def close(self, request: RequestCache) -> None:
+        self.cache.close(request)
+
+    # -- generation --------------------------------------------------------------------------
+    def default_stop_ids(self) -> tuple[int, ...]:
+        return tuple(self.spec.eos_token_ids)
+
+    def generate(
+        self,
+        prompts: Sequence[Sequence[int]],
+        sampling: Optional[SamplingParams | Sequence[SamplingParams]] = None,
+    ) -> list[GenerationResult]:
+        """Generates a continuation for every prompt (lists of token ids); results come back
+        in the order of the prompts."""
+        if sampling is None:
+            sampling = SamplingParams()
+        per_prompt = [sampling] * len(prompts) if isinstance(sampling, SamplingParams) else list(sampling)
+        if len(per_prompt) != len(prompts):
+            raise ValueError("one SamplingParams for all prompts, or one per prompt")
+        for prompt, params in zip(prompts, per_prompt):
+            self._validate(prompt, params)
+        ids = []
+        waiting = list(zip(prompts, per_prompt))
+        results: dict[object, GenerationResult] = {}
+        with torch.cuda.device(self.device):
+            while waiting or self.scheduler.has_work():
+                while waiting and len(self.scheduler.waiting) < self.scheduler.max_queue_size:
+                    prompt, params = waiting.pop(0)
+                    request_id = ("generate", self._next_id)
+                    self._next_id += 1
+                    stop = params.stop_ids if params.stop_ids is not None else self.default_stop_ids()
+                    self.scheduler.add(request_id, prompt, params, stop)
+                    ids.append(request_id)
+                for result in self.scheduler.tick():
+                    results[result.request_id] = result
+        ordered = [results[request_id] for request_id in ids]
+        for result in ordered:
+            if result.error is not None:
+                raise result.error
+        return ordered
+
+    def _validate(self, prompt: Sequence[int], params: SamplingParams) -> None:
+        vocab = self.spec.vocab_size
+        if len(prompt) < 1:
+            raise ValueError("A request prompt must contain at least one token.")
+        for token in prompt:
+            if isinstance(token, bool) or not isinstance(token, int) or not 0 <= token < vocab:
+                raise ValueError(f"Token IDs must be between 0 and {vocab - 1:,}.")
+        needed = len(prompt) + params.max_new_tokens
+        if needed > self.max_context:
+            raise ValueError(f"Request needs {needed:,} cache positions, but the engine supports {self.max_context:,}.")
+
+
+def generate(
+    model_dir: str | Path,
+    prompts: Sequence[Sequence[int]],
+    sampling: Optional[SamplingParams | Sequence[SamplingParams]] = None,
+    config: Optional[EngineConfig] = None,
+) -> list[GenerationResult]:
+    """One-call form: load the model folder, generate, return the results."""
+    return Engine(model_dir, config).generate(prompts, sampling)

@@ -1,0 +1,95 @@
+"""Replay on the GPU: the same requests cut in every way give the plain implementation's
+logits, in true 32-bit and in bfloat16."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import plain_qwen3 as plain
+import trace_tools
+from conftest import TINY_CONFIGS, TINY_PAGE_SIZES
+
+pytestmark = pytest.mark.gpu
+
+REQUEST_LENGTHS = {"tinyA": (70, 45, 133, 8, 96, 33), "tinyB": (40, 131, 64, 9, 77, 24, 1)}
+TOLERANCE = {"float32": dict(rtol=1e-4, atol=1e-5), "bfloat16": dict(rtol=2e-2, atol=2e-2)}
+
+
+def make_requests(name: str) -> dict[str, list[int]]:
+    rng = np.random.default_rng(100 + len(name) + TINY_CONFIGS[name]["vocab_size"])
+    vocab = TINY_CONFIGS[name]["vocab_size"]
+    return {f"r{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate(REQUEST_LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def expected(tiny_folders):
+    """name -> request -> float64 logits of the plain implementation at every position."""
+    out = {}
+    for name, folder in tiny_folders.items():
+        cfg, weights = plain.read_model(folder)
+        out[name] = {rid: plain.as_numpy(plain.forward(cfg, weights, tokens)) for rid, tokens in make_requests(name).items()}
+    return out
+
+
+def make_engine(folder, name, dtype, steps, max_requests=4):
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine
+
+    page = TINY_PAGE_SIZES[name]
+    tokens = trace_tools.pool_tokens(steps, round_to=page)
+    config = EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=tokens, max_context=256, max_batch_size=max_requests)
+    return Engine(folder, config)
+
+
+def compare(got, want, dtype):
+    assert set(got) == set(want)
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, rid
+        np.testing.assert_allclose(got[rid], want[rid], err_msg=f"request {rid}", **TOLERANCE[dtype])
+
+
+CUTTINGS = {
+    "whole": trace_tools.whole,
+    "tail_one_by_one": trace_tools.tail_one_by_one,
+    "changing_portions": trace_tools.changing_portions,
+    "mixed": trace_tools.mixed,
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", list(CUTTINGS))
+@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+def test_cuttings_match_plain(name, cutting, dtype, tiny_folders, expected):
+    requests = make_requests(name)
+    steps = CUTTINGS[cutting](requests)
+    engine = make_engine(tiny_folders[name], name, dtype, steps)
+    got = trace_tools.run_in_process(engine, steps)
+    compare(got, expected[name], dtype)
+    pool = engine.cache.groups[0].pool
+    assert pool.free_count == pool.num_pages            # everything was given back
+    assert pool.acquired_total > pool.num_pages          # and pages were used again
+
+
+@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+def test_cuttings_agree_with_each_other_in_float32(name, tiny_folders):
+    """Beyond agreeing with the oracle: in 32-bit the cuttings agree with each other far
+    below the oracle tolerance, so a fault that depends on the cut shows even where it is
+    smaller than float32-vs-float64 noise."""
+    requests = make_requests(name)
+    results = {}
+    for cutting, build in CUTTINGS.items():
+        steps = build(requests)
+        results[cutting] = trace_tools.run_in_process(make_engine(tiny_folders[name], name, "float32", steps), steps)
+    for cutting, got in results.items():
+        for rid in requests:
+            np.testing.assert_allclose(got[rid], results["whole"][rid], rtol=0, atol=2e-6, err_msg=f"{cutting} {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tiny_folders, expected, tmp_path):
+    """The bin/trace_run program itself, in a process of its own, on a mixed trace."""
+    name = "tinyB"
+    requests = make_requests(name)
+    steps = trace_tools.mixed(requests, seed=3)
+    got = trace_tools.run_program(tiny_folders[name], dtype, steps, tmp_path / "out")
+    compare(got, expected[name], dtype)
