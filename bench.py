@@ -1,0 +1,308 @@
+"""Decode and prefill throughput of the engine at Qwen3-4B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  A "step" is one decode step of a batch of 8 requests whose caches
+hold about 4,096 tokens each (random weights, random token ids; the caches are filled by
+real prefill through the engine).  ``value`` is decoded tokens a second timed on the device
+over exactly K steps of the step function; ``e2e`` is the same through the public entry
+point (``Engine.submit`` / ``Engine.tick``: host token lists in, host token lists out, with
+the scheduler, the host-to-device copy of each step's inputs and the device-to-host read of
+its tokens inside the timed region).  ``prefill`` is one 2,048-token prompt in one step;
+``roofline`` relates the decode step to HBM bandwidth; ``points`` holds batch 1 and 64.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_4B = dict(
+    vocab_size=151_936, hidden_size=2_560, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, intermediate_size=9_728, max_position_embeddings=262_144, rope_theta=5_000_000.0,
+    rms_norm_eps=1e-6, tie_word_embeddings=True,
+)
+CONTEXT = 4_096
+PAGE_SIZE = 256
+PREFILL_TOKENS = 2_048
+# raun6k/Pylon's published decode_heavy output rate at concurrency 8 (README.md:73): an
+# end-to-end HTTP figure on an NVIDIA L4, the only batch-8 number it publishes.
+BASELINE_TOKENS_PER_SECOND = 199.8
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            out["hbm_gbs"] = float(data.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(data.get("bf16_tflops", out["bf16_tflops"]))
+            out["source"] = "measured"
+        except (ValueError, TypeError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0) -> None:
+        self.lines: list[str] = []
+        self.process = None
+        self.device_index = device_index
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self) -> None:
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc) -> None:
+        if self.process is not None:
+            time.sleep(0.15)
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self) -> dict:
+        clocks, top, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(int(float(parts[0])))
+                top = max(top, int(float(parts[1])))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": top or None,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def fill_caches(engine, torch, batch: int, tokens_each: int, rng, chunk: int):
+    """Opens ``batch`` requests and prefills ``tokens_each`` random tokens into each."""
+    from pylon_b200.engine import StepEntry
+
+    vocab = engine.spec.vocab_size
+    requests = [engine.open(("bench", i, time.time_ns()), CONTEXT) for i in range(batch)]
+    for request in requests:
+        done = 0
+        while done < tokens_each:
+            count = min(chunk, tokens_each - done)
+            engine.step([StepEntry(request, rng.integers(0, vocab, size=count).tolist(), ())])
+            done += count
+    torch.cuda.synchronize()
+    return requests
+
+
+def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng) -> dict:
+    """Decode ``warmup + steps`` tokens for ``batch`` requests whose contexts end at CONTEXT;
+    the timed K steps are bracketed by CUDA events on the launching stream."""
+    from pylon_b200.engine import StepEntry
+
+    start_length = CONTEXT - (warmup + steps)
+    requests = fill_caches(engine, torch, batch, start_length, rng, PREFILL_TOKENS)
+    tokens = rng.integers(0, engine.spec.vocab_size, size=batch).tolist()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = 0
+    kv_tokens = 0
+    for index in range(warmup + steps):
+        if index == warmup:
+            torch.cuda.synchronize()
+            launches_before = ops.launches[0]
+            begin.record()
+        if index >= warmup:
+            kv_tokens += sum(request.length + 1 for request in requests)
+        logits = engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])
+        tokens = ops.sample(logits).cpu().tolist()
+    end.record()
+    torch.cuda.synchronize()
+    milliseconds = begin.elapsed_time(end)
+    launches = ops.launches[0] - launches_before
+    for request in requests:
+        engine.close(request)
+    return {"ms_per_step": milliseconds / steps, "tokens_per_second": batch * steps / (milliseconds / 1e3),
+            "launches": launches, "kv_tokens_per_step": kv_tokens / steps}
+
+
+def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
+    """The same decode through submit()/tick(): host tokens in, host tokens out."""
+    from pylon_b200.sampling import SamplingParams
+
+    vocab = engine.spec.vocab_size
+    prompt_length = CONTEXT - (warmup + steps) - 1
+    params = SamplingParams(max_new_tokens=warmup + steps + 1, temperature=0.0, ignore_eos=True)
+    for _ in range(batch):
+        engine.submit(rng.integers(0, vocab, size=prompt_length).tolist(), params)
+    scheduler = engine.scheduler
+    while any(r.pending_token is None for r in scheduler.active) or scheduler.waiting or len(scheduler.active) < batch:
+        engine.tick()
+    for _ in range(warmup):
+        engine.tick()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        before = sum(len(r.output_ids) for r in scheduler.active)
+        finished = engine.tick()
+        produced += sum(len(r.output_ids) for r in scheduler.active) + sum(len(f.output_ids) for f in finished) - before
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    while scheduler.has_work():
+        engine.tick()
+    # per step: the packed int32 metadata buffer goes up, one int32 token per request comes back
+    from pylon_b200.engine.step import StepLayout
+
+    layout = StepLayout(tokens=batch, rows=batch, logits=batch, table_widths=(CONTEXT // PAGE_SIZE,))
+    return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4,
+            "d2h_bytes_per_step": batch * 4, "produced": produced}
+
+
+def time_prefill(engine, torch, repeats: int, rng) -> dict:
+    from pylon_b200.engine import StepEntry
+
+    vocab = engine.spec.vocab_size
+    best = None
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for index in range(repeats):
+        request = engine.open(("prefill", index), PREFILL_TOKENS)
+        tokens = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
+        torch.cuda.synchronize()
+        begin.record()
+        engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        engine.close(request)
+        elapsed = begin.elapsed_time(end)
+        if index >= 2:   # the first runs warm up
+            best = elapsed if best is None else min(best, elapsed)
+    return {"ms": best}
+
+
+def prefill_flops(cfg: dict, tokens: int) -> float:
+    h, q, kv, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"]
+    per_layer = 2 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * inter)
+    attention = 2 * 2 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2   # causal half of QK^T and PV
+    head = 2 * cfg["vocab_size"] * h   # one row
+    return cfg["num_hidden_layers"] * (per_layer + attention) + head
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="pylon_b200", choices=["pylon_b200", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
+                        help="run fewer layers than the configuration has (named in the output)")
+    parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "raun6k/Pylon does not install offline: its build backend uv_build is not in the wheelhouse"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py measures a single-GPU engine; --gpus must be 1")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from pylon_b200.config import EngineConfig, Qwen3Config
+    from pylon_b200.engine import Engine
+    from pylon_b200.kernels import ops
+
+    fields = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    model_config = Qwen3Config(**fields)
+    rng = np.random.default_rng(0)
+    largest = args.batch if args.skip_points else max(args.batch, 64)
+    engine_config = EngineConfig(
+        dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=largest * CONTEXT, max_context=CONTEXT,
+        max_batch_size=largest, max_queue_size=largest, prefill_chunk_size=PREFILL_TOKENS,
+        cuda_graphs=os.environ.get("PYLON_CUDA_GRAPHS", "true").lower() in ("1", "true"),
+    )
+    engine = Engine(None, engine_config, device="cuda:0", model_config=model_config, random_seed=0)
+    peak = peaks()
+
+    prefill = time_prefill(engine, torch, 5, rng)
+    with ClockSampler() as sampler:
+        decode = time_decode(engine, torch, ops, args.batch, args.steps, args.warmup, rng)
+    clocks = sampler.summary()
+    e2e = time_e2e(engine, torch, args.batch, args.steps, args.warmup, rng)
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = round(time_decode(engine, torch, ops, batch, max(16, args.steps // 2), args.warmup, rng)["tokens_per_second"], 1)
+
+    weight_bytes = engine.model.weight_bytes()
+    kv_bytes = decode["kv_tokens_per_step"] * engine.cache.bytes_per_token()
+    achieved = (weight_bytes + kv_bytes) / (decode["ms_per_step"] / 1e3) / 1e9
+    flops = prefill_flops(fields, PREFILL_TOKENS)
+    record = {
+        "metric": "decode tokens/s, Qwen3-4B shape, batch 8, context 4096",
+        "value": round(decode["tokens_per_second"], 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(decode["ms_per_step"], 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": round(decode["tokens_per_second"] / BASELINE_TOKENS_PER_SECOND, 2),
+        "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids, caches filled by real prefill",
+        "config": {
+            "model": "Qwen3-4B shape", "layers": args.layers, "layers_of_model": QWEN3_4B["num_hidden_layers"],
+            "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
+            "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
+            "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single GPU", "cuda_graphs": engine_config.cuda_graphs, "l2": "inputs larger than L2 (8 GB of weights per step)",
+            "peaks": peak["source"], "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
+        },
+        "clocks": clocks,
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items() if k != "produced"},
+        "gpu_launches": decode["launches"],
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
+                    "frac": round(flops / (prefill["ms"] / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -19,13 +19,14 @@ import torch
 
 from pylon_b200.cache.manager import CacheManager, RequestCache
 from pylon_b200.config.engine_config import EngineConfig
-from pylon_b200.config.registry import read_config
+from pylon_b200.config.registry import ARCHITECTURES, read_config
 from pylon_b200.engine.scheduler import GenerationResult, Scheduler
 from pylon_b200.engine.step import StepEntry, StepFunction
 from pylon_b200.models.decoder import DecoderModel
 from pylon_b200.sampling.params import SamplingParams
 from pylon_b200.sampling.sampler import Sampler
 from pylon_b200.weights.loader import Checkpoint
+from pylon_b200.weights.random_init import device_random_fetch
 
 
 def require_gpu(device: Optional[str | torch.device] = None) -> torch.device:
@@ -39,22 +40,44 @@ def require_gpu(device: Optional[str | torch.device] = None) -> torch.device:
 
 
 class Engine:
-    def __init__(self, model_dir: str | Path, config: Optional[EngineConfig] = None, device: Optional[str | torch.device] = None) -> None:
+    def __init__(
+        self,
+        model_dir: Optional[str | Path],
+        config: Optional[EngineConfig] = None,
+        device: Optional[str | torch.device] = None,
+        *,
+        model_config: Optional[object] = None,
+        random_seed: Optional[int] = None,
+    ) -> None:
+        """``model_dir``: a folder with ``config.json`` and safetensors.  Alternatively
+        ``model_dir=None`` with a typed ``model_config`` and a ``random_seed`` draws the
+        weights on the device (same distributions as the random-weights mode that writes a
+        folder; no file is touched), for benchmarks of shapes too large to write out."""
         self.config = config or EngineConfig()
         self.device = require_gpu(device)
-        self.model_dir = Path(model_dir)
-        self.architecture, self.model_config = read_config(self.model_dir)
         dtype = self.config.torch_dtype
-
-        checkpoint = Checkpoint(self.model_dir)
+        if model_dir is not None:
+            self.model_dir = Path(model_dir)
+            self.architecture, self.model_config = read_config(self.model_dir)
+            checkpoint = Checkpoint(self.model_dir)
+        else:
+            if model_config is None or random_seed is None:
+                raise ValueError("without a model folder, a model configuration and a random seed are needed")
+            self.model_dir = None
+            self.architecture, self.model_config = ARCHITECTURES[model_config.architecture], model_config
+            checkpoint = None
         limit = self.config.max_context
         if limit is None and self.config.max_cache_tokens is not None:
             limit = self.config.max_cache_tokens
         self.spec = self.architecture.build_spec(self.model_config, limit)
         self.model = DecoderModel(self.spec)
-        checkpoint.verify(self.model.tensor_decls(), self.spec.ignored_tensors)
+        if checkpoint is not None:
+            checkpoint.verify(self.model.tensor_decls(), self.spec.ignored_tensors)
+            fetch = checkpoint.fetch
+        else:
+            fetch = device_random_fetch(self.model.tensor_decls(), random_seed, self.device, dtype)
         with torch.cuda.device(self.device):
-            self.model.load(checkpoint.fetch, dtype, self.device)
+            self.model.load(fetch, dtype, self.device)
             needs = self.model.cache_needs()
             cache_of = [run.cache_of for run in self.spec.order]
             page_size = self.config.page_size
@@ -105,6 +128,23 @@ class Engine:
         self.cache.close(request)
 
     # -- generation --------------------------------------------------------------------------
+    def submit(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, request_id: Optional[object] = None) -> object:
+        """Queues one request (raun6k/Pylon's ``Engine.enqueue``, src/pylon/engine.py:241-253);
+        returns its id.  :meth:`tick` makes progress; finished requests come back from it."""
+        sampling = sampling or SamplingParams()
+        self._validate(prompt, sampling)
+        if request_id is None:
+            request_id = ("request", self._next_id)
+            self._next_id += 1
+        stop = sampling.stop_ids if sampling.stop_ids is not None else self.default_stop_ids()
+        self.scheduler.add(request_id, prompt, sampling, stop)
+        return request_id
+
+    def tick(self) -> list[GenerationResult]:
+        """One scheduler tick: admit, run one step, accept its tokens."""
+        with torch.cuda.device(self.device):
+            return self.scheduler.tick()
+
     def default_stop_ids(self) -> tuple[int, ...]:
         return tuple(self.spec.eos_token_ids)
 

@@ -49,7 +49,13 @@ def _need(condition: bool, text: str) -> None:
         raise KernelError(text)
 
 
+# Kernels of this package launched so far in this process (library matrix products are
+# not counted).  Benchmarks read it before and after a timed region.
+launches = [0]
+
+
 def _check(library: ctypes.CDLL, code: int) -> None:
+    launches[0] += 1
     if code != 0:
         raise KernelError(library.pylon_last_error().decode(errors="replace") or f"kernel call failed ({code})")
 

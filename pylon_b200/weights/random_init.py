@@ -47,3 +47,20 @@ def write_random_model(config: Any, seed: int, folder: str | Path, dtype: str = 
     data["torch_dtype"] = dtype
     (folder / "config.json").write_text(json.dumps(data, indent=2) + "\n")
     return folder
+
+
+def device_random_fetch(decls, seed: int, device: torch.device, dtype: torch.dtype):
+    """A ``fetch(name)`` for :meth:`DecoderModel.load` that draws each tensor on the device:
+    N(0, 0.02) matrices, 1 + N(0, 0.02) vectors, seeded by (seed, name).  The values differ
+    from :func:`random_tensor`'s (another generator); the distributions are the same."""
+    generator = torch.Generator(device=device)
+
+    def fetch(name: str) -> torch.Tensor:
+        decl = decls[name]
+        generator.manual_seed((int(seed) * 1_000_003 + zlib.crc32(name.encode())) % (2**63 - 1))
+        target = torch.float32 if decl.role == "vector" else dtype
+        values = torch.empty(decl.shape, dtype=target, device=device)
+        values.normal_(0.0, 0.02, generator=generator)
+        return values + 1.0 if decl.role == "vector" else values
+
+    return fetch

@@ -1,0 +1,236 @@
+"""The scheduler's decisions (no GPU): a fake step function that drives the real cache
+manager and returns planned tokens, a hand-driven clock."""
+from __future__ import annotations
+
+import pytest
+
+from pylon_b200.cache import CacheManager, OutOfPages
+from pylon_b200.engine.scheduler import QueueFullError, Scheduler
+from pylon_b200.parts.base import CacheNeed, KVNeed
+from pylon_b200.sampling import SamplingParams
+
+
+class FakeClock:
+    def __init__(self):
+        self.now = 0.0
+
+    def __call__(self):
+        return self.now
+
+
+class FakeStep:
+    """Does the cache bookkeeping of a step like the real one; 'logits' are the row ids."""
+
+    def __init__(self, cache, fail_on=None):
+        self.cache = cache
+        self.calls = []
+        self.fail_on = fail_on
+
+    def __call__(self, entries):
+        batch = [(entry.request, len(entry.tokens)) for entry in entries]
+        self.cache.prepare(batch)
+        if self.fail_on is not None and len(self.calls) == self.fail_on:
+            for request, _ in batch:
+                self.cache.rollback(request)
+            self.calls.append("failed")
+            raise RuntimeError("injected")
+        for request, _ in batch:
+            self.cache.commit(request)
+        self.calls.append([(entry.request.request_id, list(entry.tokens), tuple(entry.want)) for entry in entries])
+        self.cache.check()
+        return [entry.request.request_id for entry in entries if entry.want]
+
+
+def planned_sampler(plan):
+    """plan: request id -> list of tokens it will be given, in order."""
+    cursor = {key: 0 for key in plan}
+
+    def sample(logits, params, randoms):
+        out = []
+        for request_id in logits:
+            out.append(plan[request_id][cursor[request_id]])
+            cursor[request_id] += 1
+        return out
+
+    return sample
+
+
+def make(num_pages=16, page_size=4, slots=4, plan=None, fail_on=None, **options):
+    cache = CacheManager([CacheNeed(kv=KVNeed(1, 4))], [None], page_size=page_size, num_pages=num_pages, max_requests=slots)
+    clock = FakeClock()
+    step = FakeStep(cache, fail_on)
+    options.setdefault("max_batch_size", slots)
+    options.setdefault("free_page_floor", False)
+    scheduler = Scheduler(cache, step, planned_sampler(plan or {}), clock=clock, **options)
+    return scheduler, step, clock, cache
+
+
+GREEDY3 = SamplingParams(max_new_tokens=3, temperature=0.0)
+
+
+def test_prompt_is_cut_under_the_token_budget_and_first_token_comes_with_the_last_portion():
+    scheduler, step, _, cache = make(plan={"a": [50, 51, 52]}, prefill_chunk_size=4)
+    scheduler.add("a", list(range(10)), GREEDY3)
+    results = scheduler.run()
+    assert [call[0][1] for call in step.calls[:3]] == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9]]
+    assert [call[0][2] for call in step.calls[:3]] == [(), (), (1,)]       # the head runs only where a token is chosen
+    assert [call[0][1] for call in step.calls[3:]] == [[50], [51]]          # then one decoded token a step
+    assert results[0].output_ids == [50, 51, 52] and results[0].finish_reason == "length"
+    assert cache.free_pages() == [16] and cache.free_slots() == 4
+
+
+def test_decoded_tokens_ride_beside_prompt_portions_and_do_not_use_the_budget():
+    scheduler, step, _, _ = make(plan={"a": [9, 9, 9, 9, 9], "b": [8, 8]}, prefill_chunk_size=4)
+    scheduler.add("a", [1, 2], SamplingParams(max_new_tokens=5, temperature=0.0))
+    scheduler.tick()
+    scheduler.add("b", list(range(6)), SamplingParams(max_new_tokens=2, temperature=0.0))
+    scheduler.tick()
+    assert step.calls[1] == [("a", [9], (0,)), ("b", [0, 1, 2, 3], ())]       # decode row first, full budget for b
+    scheduler.tick()
+    assert step.calls[2] == [("a", [9], (0,)), ("b", [4, 5], (1,))]
+
+
+def test_one_tick_packs_several_prompts_and_prefers_one_that_finishes():
+    scheduler, step, _, _ = make(plan={"a": [1], "b": [1], "c": [1]}, prefill_chunk_size=8)
+    one = SamplingParams(max_new_tokens=1, temperature=0.0)
+    scheduler.add("a", list(range(12)), one)
+    scheduler.add("b", list(range(5)), one)
+    scheduler.add("c", list(range(3)), one)
+    scheduler.tick()
+    # b fits the budget whole and goes first, then c, the rest of the budget is none: a waits
+    assert [(rid, len(tokens)) for rid, tokens, _ in step.calls[0]] == [("b", 5), ("c", 3)]
+
+
+def test_a_prompt_that_waited_100_ms_goes_first():
+    scheduler, step, clock, _ = make(plan={"a": [1], "b": [1]}, prefill_chunk_size=8)
+    one = SamplingParams(max_new_tokens=1, temperature=0.0)
+    scheduler.add("a", list(range(12)), one)
+    scheduler.add("b", list(range(5)), one)
+    clock.now = 0.2
+    scheduler.tick()
+    assert [(rid, len(tokens)) for rid, tokens, _ in step.calls[0]] == [("a", 8)]
+
+
+def test_stop_token_ends_without_being_returned_and_frees_at_once():
+    scheduler, _, _, cache = make(plan={"a": [5, 6, 99, 7]})
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=8, temperature=0.0), stop_ids=[99])
+    results = scheduler.run()
+    assert results[0].output_ids == [5, 6] and results[0].finish_reason == "eos"
+    assert cache.free_pages() == [16]
+    scheduler2, _, _, _ = make(plan={"a": [5, 99, 7]})
+    scheduler2.add("a", [1], SamplingParams(max_new_tokens=3, temperature=0.0, ignore_eos=True), stop_ids=[99])
+    assert scheduler2.run()[0].output_ids == [5, 99, 7]
+
+
+def test_admission_reserves_the_whole_life_and_later_requests_wait_for_pages():
+    # 6 pages of 4 tokens.  a needs ceil((6+6)/4) = 3 pages, b needs 3, c needs 2: c must wait.
+    plan = {"a": [1] * 6, "b": [1] * 6, "c": [1] * 2}
+    scheduler, step, _, cache = make(num_pages=6, plan=plan, admit_skip=0)
+    six = SamplingParams(max_new_tokens=6, temperature=0.0)
+    scheduler.add("a", list(range(6)), six)
+    scheduler.add("b", list(range(6)), six)
+    scheduler.add("c", list(range(6)), SamplingParams(max_new_tokens=2, temperature=0.0))
+    scheduler.tick()
+    assert [r.request_id for r in scheduler.active] == ["a", "b"] and [r.request_id for r in scheduler.waiting] == ["c"]
+    results = scheduler.run()
+    assert {r.request_id: r.finish_reason for r in results} == {"a": "length", "b": "length", "c": "length"}
+    assert cache.free_pages() == [6]
+    # c started only after a page reservation was released, and used pages again
+    assert cache.groups[0].pool.acquired_total > 6
+
+
+def test_a_request_larger_than_the_pool_is_refused_at_once():
+    scheduler, _, _, _ = make(num_pages=2)
+    with pytest.raises(ValueError, match="cache pages"):
+        scheduler.add("big", list(range(6)), SamplingParams(max_new_tokens=6, temperature=0.0))
+
+
+def test_skip_ahead_admission_and_its_100_ms_limit():
+    plan = {"a": [1] * 4, "big": [1] * 4, "small": [1]}
+    scheduler, _, clock, _ = make(num_pages=6, plan=plan, admit_skip=4)
+    scheduler.add("a", list(range(8)), SamplingParams(max_new_tokens=4, temperature=0.0))       # 3 pages
+    scheduler.add("big", list(range(12)), SamplingParams(max_new_tokens=4, temperature=0.0))    # 4 pages: does not fit beside a
+    scheduler.add("small", [1, 2], SamplingParams(max_new_tokens=1, temperature=0.0))            # 1 page
+    scheduler.admit()
+    assert [r.request_id for r in scheduler.active] == ["a", "small"] and scheduler.head_skips == 1
+    scheduler2, _, clock2, _ = make(num_pages=6, plan=plan, admit_skip=4)
+    scheduler2.add("a", list(range(8)), SamplingParams(max_new_tokens=4, temperature=0.0))
+    scheduler2.add("big", list(range(12)), SamplingParams(max_new_tokens=4, temperature=0.0))
+    scheduler2.add("small", [1, 2], SamplingParams(max_new_tokens=1, temperature=0.0))
+    clock2.now = 0.5                                       # the head has waited long enough: nobody passes it
+    scheduler2.admit()
+    assert [r.request_id for r in scheduler2.active] == ["a"]
+
+
+def test_free_page_floor_keeps_a_page_per_decoding_request():
+    plan = {"a": [1] * 4, "b": [1]}
+    scheduler, _, _, _ = make(num_pages=4, plan=plan, free_page_floor=True, admit_skip=0)
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=4, temperature=0.0))   # 2 pages
+    scheduler.tick()                                                                  # a decodes now
+    scheduler.add("b", list(range(7)), SamplingParams(max_new_tokens=1, temperature=0.0))   # 2 pages: would leave 0 < 1
+    scheduler.admit()
+    assert [r.request_id for r in scheduler.active] == ["a"]
+
+
+def test_slots_limit_the_batch_and_a_full_decoding_batch_holds_prompts_off_for_100_ms():
+    plan = {"a": [1] * 8, "b": [1] * 8, "c": [1]}
+    scheduler, step, clock, _ = make(slots=3, max_batch_size=2, plan=plan)
+    eight = SamplingParams(max_new_tokens=8, temperature=0.0)
+    scheduler.add("a", [1], eight)
+    scheduler.add("b", [1], eight)
+    scheduler.add("c", [1, 2], SamplingParams(max_new_tokens=1, temperature=0.0))
+    scheduler.tick()
+    assert [r.request_id for r in scheduler.active] == ["a", "b"] and len(scheduler.waiting) == 1
+
+
+def test_queue_limit_and_abort():
+    scheduler, _, _, cache = make(max_queue_size=2, plan={"a": [1] * 5})
+    scheduler.add("a", [1], SamplingParams(max_new_tokens=5, temperature=0.0))
+    scheduler.add("b", [1], GREEDY3)
+    with pytest.raises(QueueFullError):
+        scheduler.add("c", [1], GREEDY3)
+    assert scheduler.abort("b") and not scheduler.abort("zzz")
+    scheduler.tick()
+    assert scheduler.abort("a") and cache.free_pages() == [16] and not scheduler.has_work()
+    with pytest.raises(ValueError, match="at least one token"):
+        scheduler.add("d", [], GREEDY3)
+
+
+def test_a_failing_step_fails_its_requests_only_and_gives_their_pages_back():
+    plan = {"a": [1] * 3, "b": [1] * 3}
+    scheduler, step, _, cache = make(plan=plan, fail_on=1)
+    scheduler.add("a", [1, 2], GREEDY3)
+    scheduler.tick()                          # step 0: a prefills and gets its first token
+    scheduler.add("b", [3, 4], GREEDY3)
+    finished = scheduler.tick()               # step 1 fails: a (decoding) and b (prefilling) were in it
+    assert {r.request_id: r.finish_reason for r in finished} == {"a": "error", "b": "error"}
+    assert all(isinstance(r.error, RuntimeError) for r in finished)
+    assert cache.free_pages() == [16] and cache.free_slots() == 4 and not scheduler.has_work()
+    scheduler.sample = planned_sampler({"c": [7, 7, 7]})
+    scheduler.add("c", [5], GREEDY3)
+    assert scheduler.run()[0].output_ids == [7, 7, 7]   # the engine goes on
+
+
+def test_running_out_of_pages_inside_a_step_fails_that_step_only():
+    """Reservations make this impossible for admitted requests; a pool that someone else
+    drained shows what happens anyway."""
+    scheduler, _, _, cache = make(num_pages=4, plan={"a": [1, 1]})
+    scheduler.add("a", list(range(8)), SamplingParams(max_new_tokens=2, temperature=0.0))
+    thief = cache.open("thief", 12)
+    cache.prepare([(thief, 12)])
+    cache.commit(thief)
+    finished = scheduler.tick()
+    assert finished[0].finish_reason == "error" and isinstance(finished[0].error, OutOfPages)
+    cache.close(thief)
+    assert cache.free_pages() == [4]
+
+
+def test_sampling_options_are_checked():
+    with pytest.raises(ValueError):
+        SamplingParams(max_new_tokens=0)
+    with pytest.raises(ValueError):
+        SamplingParams(temperature=2.5)
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    defaults = SamplingParams()
+    assert (defaults.max_new_tokens, defaults.temperature, defaults.top_p) == (256, 0.2, 0.95)
