@@ -1,0 +1,369 @@
+// Paged causal attention on the tensor cores for bfloat16, for prefill portions and decoded
+// tokens in one launch: a flash-attention loop (scores, online softmax in float32, weighted
+// sum) over key/value tiles gathered from cache pages through the block table.
+//
+// Built for one head size per library: -DPYLON_HEAD_DIM=<multiple of 16, 16..256>.
+//
+// Work split.  Grid = (query tiles x splits, KV heads, rows).  The query rows of one
+// request and one KV head are packed token-major, the heads of the group inside: packed row
+// m is token m / G, query head kv_head * G + m % G, for any group size G.  A block takes 64
+// packed rows (4 warps x 16) and walks 64-key tiles aligned at absolute position multiples
+// of 64; tiles are double-buffered with cp.async.  With more than one split, each split
+// walks its share of the tiles and leaves a normalised partial result and its
+// log-sum-exp in scratch memory; a second kernel combines them.  Decode steps use splits to
+// fill the machine; prefill uses one.
+//
+// Semantics as raun6k/Pylon's attention call (src/pylon/kv/cache.py:462-476, restated
+// 483-491): key j of the same request is visible to the token at position p iff j <= p
+// (and j > p - window when a window is set); softmax scale 1/sqrt(d) unless given.
+#include "common.cuh"
+
+#ifndef PYLON_HEAD_DIM
+#define PYLON_HEAD_DIM 128
+#endif
+
+namespace pylon {
+
+constexpr int D = PYLON_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 in 16..256");
+constexpr int BLOCK_M = 64, BLOCK_N = 64, ATT_THREADS = 128;
+constexpr int LD = D + 8;              // padded row: ldmatrix rows fall on distinct banks
+constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
+constexpr int TILE_ELEMS = BLOCK_N * LD;
+
+struct AttentionParams {
+  const __nv_bfloat16* q;
+  long long q_stride;
+  const __nv_bfloat16* k_pages;
+  const __nv_bfloat16* v_pages;
+  __nv_bfloat16* out;
+  float* partial_out;   // [splits, tokens, nq, D]
+  float* partial_lse;   // [splits, tokens, nq]   (log2 domain)
+  const int* q_start;
+  const int* kv_len;
+  const int* block_table;
+  int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens;
+  float scale_log2;     // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ unsigned smem_address(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_address(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_address(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_address(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Gathers keys [tile * 64, tile * 64 + 64) of one KV head into a padded shared tile.  Keys
+// at or beyond kv_len, or without a page, are zero-filled.
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* pages, const int* table,
+                                             int tile, int kv_len, int kv_head, const AttentionParams& p) {
+  for (int c = threadIdx.x; c < BLOCK_N * CHUNKS; c += ATT_THREADS) {
+    const int r = c / CHUNKS, col = c % CHUNKS;
+    const int key = tile * BLOCK_N + r;
+    const __nv_bfloat16* src = pages;
+    bool valid = key < kv_len;
+    if (valid) {
+      const int page = table[key / p.page_size];
+      valid = page >= 0 && page < p.num_pages;
+      if (valid) src = pages + (((size_t)page * p.nkv + kv_head) * p.page_size + key % p.page_size) * D + col * 8;
+    }
+    cp_async_16(dst + r * LD + col * 8, src, valid);
+  }
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const AttentionParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][LD]
+  __nv_bfloat16* k_tiles = q_tile + BLOCK_M * LD;                         // [2][64][LD]
+  __nv_bfloat16* v_tiles = k_tiles + 2 * TILE_ELEMS;                      // [2][64][LD]
+
+  const int row = blockIdx.z, kv_head = blockIdx.y;
+  const int q_tile_index = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
+  const int q0 = p.q_start[row];
+  const int q_len = p.q_start[row + 1] - q0;
+  const int G = p.group;
+  const int packed_rows = q_len * G;
+  const int m0 = q_tile_index * BLOCK_M;
+  if (m0 >= packed_rows) return;
+  const int kv_len = p.kv_len[row];
+  const int pos0 = kv_len - q_len;   // position of the row's first new token
+  const int* table = p.block_table + (size_t)row * p.table_width;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int token_first = m0 / G;
+  const int last_packed = min(packed_rows, m0 + BLOCK_M) - 1;
+  const int token_last = last_packed / G;
+  const int hi = pos0 + token_last;                                                   // last visible key (inclusive)
+  const int lo = p.window > 0 ? max(0, pos0 + token_first - p.window + 1) : 0;        // first visible key
+  const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
+  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int tile_end = min(first_tile + tiles, tile_begin + per_split);
+
+  // This thread's two rows of the warp's 16: packed index, token position, validity.
+  int row_pos[2], row_token[2], row_head[2];
+  bool row_valid[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int m = m0 + warp * 16 + g + 8 * h;
+    row_valid[h] = m < packed_rows;
+    row_token[h] = row_valid[h] ? m / G : 0;
+    row_head[h] = kv_head * G + (row_valid[h] ? m % G : 0);
+    row_pos[h] = pos0 + row_token[h];
+  }
+
+  // A warp whose 16 rows lie past the end (decoded tokens fill only a few rows) helps with
+  // the loads and skips the arithmetic.
+  const bool warp_active = m0 + warp * 16 < packed_rows;
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+
+  if (tile_begin < tile_end) {
+    // Query tile: packed rows m0 .. m0+63, zero-filled past the end.
+    for (int c = threadIdx.x; c < BLOCK_M * CHUNKS; c += ATT_THREADS) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const int m = m0 + r;
+      const bool valid = m < packed_rows;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + (size_t)(q0 + m / G) * p.q_stride + (size_t)(kv_head * G + m % G) * D + col * 8;
+      cp_async_16(q_tile + r * LD + col * 8, src, valid);
+    }
+    load_kv_tile(k_tiles, p.k_pages, table, tile_begin, kv_len, kv_head, p);
+    load_kv_tile(v_tiles, p.v_pages, table, tile_begin, kv_len, kv_head, p);
+    cp_async_commit();
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      const int stage = (tile - tile_begin) & 1;
+      if (tile + 1 < tile_end) {
+        load_kv_tile(k_tiles + (stage ^ 1) * TILE_ELEMS, p.k_pages, table, tile + 1, kv_len, kv_head, p);
+        load_kv_tile(v_tiles + (stage ^ 1) * TILE_ELEMS, p.v_pages, table, tile + 1, kv_len, kv_head, p);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const __nv_bfloat16* ks = k_tiles + stage * TILE_ELEMS;
+      const __nv_bfloat16* vs = v_tiles + stage * TILE_ELEMS;
+      if (warp_active) {
+
+      // S = Q K^T for this warp's 16 rows and the tile's 64 keys.
+      float s[BLOCK_N / 8][4];
+#pragma unroll
+      for (int i = 0; i < BLOCK_N / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned a[4];
+        ldmatrix_x4(a, q_tile + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+        for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
+          unsigned b[4];
+          ldmatrix_x4(b, ks + (n2 * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+          mma_bf16(s[2 * n2], a, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+
+      // Mask: key visible iff key <= position (and > position - window) and the row exists.
+      const int key_base = tile * BLOCK_N + 2 * tq;
+#pragma unroll
+      for (int n = 0; n < BLOCK_N / 8; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int h = i >> 1;
+          const int key = key_base + n * 8 + (i & 1);
+          bool visible = row_valid[h] && key <= row_pos[h];
+          if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
+          if (!visible) s[n][i] = -INFINITY;
+        }
+      }
+
+      // Online softmax in float32 (base 2).
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < BLOCK_N / 8; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float new_max = fmaxf(row_max[h], mx);
+        const float use_max = new_max == -INFINITY ? 0.f : new_max;
+        const float alpha = exp2f((row_max[h] - use_max) * p.scale_log2);   // exp2(-inf) = 0 on the first tile
+        const float shift = use_max * p.scale_log2;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < BLOCK_N / 8; ++n) {
+          const float p0 = exp2f(s[n][2 * h] * p.scale_log2 - shift);
+          const float p1 = exp2f(s[n][2 * h + 1] * p.scale_log2 - shift);
+          s[n][2 * h] = p0;
+          s[n][2 * h + 1] = p1;
+          sum += p0 + p1;
+        }
+        row_sum[h] = row_sum[h] * alpha + sum;
+        row_max[h] = new_max;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][2 * h] *= alpha; o[i][2 * h + 1] *= alpha; }
+      }
+
+      // O += P V
+#pragma unroll
+      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2) {
+          unsigned b[4];
+          ldmatrix_x4_trans(b, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + d2 * 16 + 8 * (lane >> 4));
+          mma_bf16(o[2 * d2], a, b[0], b[1]);
+          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+      }  // warp_active
+      __syncthreads();   // the stage is overwritten by the load after next
+    }
+  }
+
+  // Epilogue: normalise and store (or leave a partial result for the combine kernel).
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = row_sum[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!row_valid[h]) continue;
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    const size_t token = (size_t)q0 + row_token[h];
+    if (p.num_splits == 1) {
+      __nv_bfloat16* dst = p.out + (token * p.nq + row_head[h]) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * tq) = __floats2bfloat162_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + token) * p.nq + row_head[h];
+      float* dst = p.partial_out + slot * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      if (tq == 0) p.partial_lse[slot] = sum > 0.f ? row_max[h] * p.scale_log2 + log2f(sum) : -INFINITY;
+    }
+  }
+}
+
+// out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
+// warp per (token, head).
+__global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
+                                      __nv_bfloat16* __restrict__ out, int num_splits, long long items) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, partial_lse[(size_t)s * items + item]);
+  float acc[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+  float total = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float lse = partial_lse[(size_t)s * items + item];
+    if (lse == -INFINITY) continue;
+    const float w = exp2f(lse - mx);
+    total += w;
+    const float* src = partial_out + ((size_t)s * items + item) * D;
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int e = lane + 32 * i;
+      if (e < D) acc[i] += w * src[e];
+    }
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) {
+    const int e = lane + 32 * i;
+    if (e < D) out[(size_t)item * D + e] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+constexpr size_t ATT_SMEM = (size_t)(BLOCK_M * LD + 4 * TILE_ELEMS) * sizeof(__nv_bfloat16);
+
+}  // namespace pylon
+
+using namespace pylon;
+
+extern "C" int pylon_attention_head_dim() { return D; }
+
+// Scratch floats needed for `num_splits` splits over `total_tokens` tokens (0 for one split).
+extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_tokens, int nq) {
+  if (num_splits <= 1) return 0;
+  return (long long)num_splits * total_tokens * nq * (D + 1);
+}
+
+// q: bfloat16 [tokens, >= nq*D] with q_stride elements between tokens; pages: bfloat16
+// [num_pages, nkv, page_size, D]; out: bfloat16 [tokens, nq, D]; q_start: int32 [rows + 1];
+// kv_len: int32 [rows]; block_table: int32 [rows, table_width]; max_q: the longest row (or an
+// upper bound); scratch: float32, pylon_attention_scratch_floats() long when num_splits > 1.
+extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                         void* out, float* scratch, const int* q_start, const int* kv_len,
+                                         const int* block_table, int table_width, int page_size, int num_pages,
+                                         int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
+                                         int max_q, int num_splits, cudaStream_t stream) {
+  if (num_rows <= 0 || total_tokens <= 0) return 0;
+  if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_mma: %d query heads over %d KV heads", nq, nkv);
+  if (page_size < 1 || table_width < 1 || window < 0 || max_q < 1 || num_splits < 1)
+    PYLON_REFUSE("paged_attention_mma: page size %d, table width %d, window %d, longest row %d, splits %d", page_size,
+                 table_width, window, max_q, num_splits);
+  if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 4) || (q_stride % 8))
+    PYLON_REFUSE("paged_attention_mma: q and pages must be 16-byte aligned and the token stride a multiple of 8");
+  if (!(scale > 0.f)) PYLON_REFUSE("paged_attention_mma: the softmax scale must be positive");
+  if (num_splits > 1 && scratch == nullptr) PYLON_REFUSE("paged_attention_mma: splits need scratch memory");
+  if (nkv > 65535 || num_rows > 65535) PYLON_REFUSE("paged_attention_mma: %d KV heads, %d rows", nkv, num_rows);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM);
+    if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  AttentionParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
+  p.out = (__nv_bfloat16*)out;
+  const long long items = (long long)total_tokens * nq;
+  p.partial_out = scratch; p.partial_lse = scratch ? scratch + (size_t)num_splits * items * D : nullptr;
+  p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
+  p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
+  p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const long long q_tiles = ((long long)max_q * p.group + BLOCK_M - 1) / BLOCK_M;
+  if (q_tiles * num_splits > 2147483647LL) PYLON_REFUSE("paged_attention_mma: too many query tiles");
+  dim3 grid((unsigned)(q_tiles * num_splits), nkv, num_rows);
+  paged_attention_mma_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(p);
+  if (num_splits > 1) {
+    const int warps = 4;
+    combine_splits_kernel<<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(p.partial_out, p.partial_lse, p.out, num_splits, items);
+  }
+  PYLON_CHECK_LAUNCH("paged_attention_mma");
+}

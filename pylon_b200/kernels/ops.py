@@ -78,6 +78,12 @@ _SIGNATURES = {
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                          c_int, c_int, c_void_p],
     },
+    "attention_mma.cu": {
+        "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                      c_int, c_int, c_void_p],
+        "pylon_attention_scratch_floats": [c_int, c_int, c_int],
+    },
     "sampling.cu": {
         "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
@@ -90,16 +96,18 @@ def _library(source: str, defines: Optional[dict[str, int]] = None) -> ctypes.CD
         for name, argtypes in _SIGNATURES.get(source, {}).items():
             function = getattr(library, name)
             function.argtypes = argtypes
-            function.restype = c_int
+            function.restype = c_longlong if name.endswith("_floats") else c_int
         library._pylon_typed = True
     return library
 
 
 def build_all() -> list[str]:
+    """Every library with its default sizes (the tensor-core attention for head size 128)."""
     names = []
     for source in _SIGNATURES:
-        _library(source)
-        names.append(build.library_name(source))
+        defines = {"PYLON_HEAD_DIM": 128} if source == "attention_mma.cu" else None
+        _library(source, defines)
+        names.append(build.library_name(source, defines))
     return names
 
 
@@ -252,26 +260,53 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 # ---------------------------------------------------------------------------------------
 # attention over the paged cache
 # ---------------------------------------------------------------------------------------
+def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:
+    """How many key/value splits a launch uses: one when the step has enough query tiles to
+    fill the GPU (prefill), else enough to give every SM about two blocks (decode)."""
+    q_tiles = -(-max_q * group // 64)
+    blocks = num_rows * nkv * q_tiles
+    kv_tiles = max(1, -(-max_kv // 64))
+    if blocks >= 2 * _SM_COUNT or kv_tiles == 1:
+        return 1
+    return int(max(1, min(kv_tiles, 64, (2 * _SM_COUNT + blocks - 1) // blocks)))
+
+
+_SM_COUNT = 148
+
+
 def paged_attention(
     q: torch.Tensor,
     k_pages: torch.Tensor,
     v_pages: torch.Tensor,
     positions: torch.Tensor,
     token_row: torch.Tensor,
+    q_start: torch.Tensor,
+    kv_len: torch.Tensor,
     block_table: torch.Tensor,
     nq: int,
+    max_q: int,
+    max_kv: int,
     window: Optional[int] = None,
     scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None,
+    num_splits: Optional[int] = None,
+    force_simple: bool = False,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
     ``q``: ``[T, >= nq * d]`` (only the first ``nq * d`` columns of each row are read, so
     the fused qkv buffer can be passed as it is); pages ``[P, nkv, page_size, d]``;
-    ``positions``/``token_row`` int32 ``[T]``; ``block_table`` int32 ``[rows, width]``.
-    Returns ``[T, nq * d]``.
+    ``positions``/``token_row`` int32 ``[T]``; ``q_start`` int32 ``[rows + 1]``; ``kv_len``
+    int32 ``[rows]`` (tokens each row holds after this step, so a row's first new token is
+    at position ``kv_len - (q_start[r + 1] - q_start[r])``); ``block_table`` int32
+    ``[rows, width]``; ``max_q``/``max_kv``: longest row and longest context (upper bounds
+    are fine).  Returns ``[T, nq * d]``.
+
+    bfloat16 with a head size that is a multiple of 16 up to 256 runs on the tensor cores
+    (built per head size on first use); float32, and other head sizes up to 512, take the
+    plain kernel.
     """
-    _need_cuda(q, k_pages, v_pages, positions, token_row, block_table, out)
+    _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out)
     _need(k_pages.dim() == 4 and k_pages.shape == v_pages.shape and k_pages.is_contiguous() and v_pages.is_contiguous(), "paged_attention: pages must be contiguous [P, nkv, page_size, d]")
     num_pages, nkv, page_size, d = k_pages.shape
     tokens = q.shape[0]
@@ -280,10 +315,26 @@ def paged_attention(
     for meta in (positions, token_row):
         _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "paged_attention: positions/token_row must be int32 [T]")
     _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "paged_attention: block_table must be contiguous int32 [rows, width]")
+    rows = block_table.shape[0]
+    _need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.shape[0] >= rows + 1, "paged_attention: q_start must be int32 [rows + 1]")
+    _need(kv_len.dtype == torch.int32 and kv_len.is_contiguous() and kv_len.shape[0] >= rows, "paged_attention: kv_len must be int32 [rows]")
     if out is None:
         out = torch.empty((tokens, nq * d), dtype=q.dtype, device=q.device)
     _need(out.shape == (tokens, nq * d) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
+    _need(scale > 0, "paged_attention: the softmax scale must be positive")
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple:
+        library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
+        splits = attention_splits(rows, nkv, nq // nkv, max_q, max_kv) if num_splits is None else int(num_splits)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty((library.pylon_attention_scratch_floats(splits, tokens, nq),), dtype=torch.float32, device=q.device)
+        _check(library, library.pylon_paged_attention_mma(
+            _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(q_start), _ptr(kv_len),
+            _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
+            int(max_q), splits, _stream()))
+        return out
+    _need(d <= 512, f"paged_attention: head size {d} is larger than 512")
     library = _library("attention_simple.cu")
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),

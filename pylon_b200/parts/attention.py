@@ -90,7 +90,7 @@ class GroupedQueryAttention(Mixer):
             cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
         )
         context = ops.paged_attention(
-            qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, cache.block_table, self.n_heads,
-            window=self.window, scale=self.scale,
+            qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
+            self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale,
         )
         return ops.linear(context, self.w_o)

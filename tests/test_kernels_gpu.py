@@ -1,0 +1,339 @@
+"""Each CUDA kernel alone against a plain PyTorch float32/float64 statement of the same
+operation, at sizes other than the engine's tiny models."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda"
+
+
+def tolerance(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(1234)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab, width, tokens", [(1000, 2560, 37), (77, 50, 5), (151_936, 96, 3)])
+def test_embed_gather(dtype, vocab, width, tokens):
+    from pylon_b200.kernels import ops
+
+    table = torch.randn(vocab, width, device=DEVICE).to(dtype)
+    ids = torch.randint(0, vocab, (tokens,), device=DEVICE, dtype=torch.int32)
+    ids[0], ids[-1] = vocab - 1, 0
+    out = ops.embed_gather(ids, table)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out, table[ids.long()].float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens, width, eps", [(19, 2560, 1e-6), (3, 100, 1e-5), (2, 5000, 1e-3), (1, 7, 1e-6)])
+def test_add_rmsnorm(dtype, tokens, width, eps):
+    from pylon_b200.kernels import ops
+
+    residual = torch.randn(tokens, width, device=DEVICE) * 3
+    delta = torch.randn(tokens, width, device=DEVICE).to(dtype)
+    weight = torch.rand(width, device=DEVICE) + 0.5
+    expected_sum = residual.double() + delta.double()
+    expected = expected_sum / torch.sqrt((expected_sum**2).mean(-1, keepdim=True) + eps) * weight.double()
+    work = residual.clone()
+    out = ops.add_rmsnorm(work, delta, weight, eps, dtype)
+    torch.testing.assert_close(work.double(), expected_sum, rtol=1e-6, atol=1e-6)      # the residual sum stays 32-bit
+    torch.testing.assert_close(out.double(), expected, **tolerance(dtype))
+    # without a delta the residual is left as it is
+    work2 = residual.clone()
+    out2 = ops.add_rmsnorm(work2, None, weight, eps, dtype)
+    plain = residual.double() / torch.sqrt((residual.double() ** 2).mean(-1, keepdim=True) + eps) * weight.double()
+    torch.testing.assert_close(out2.double(), plain, **tolerance(dtype))
+    assert torch.equal(work2, residual)
+    # a row selection normalises those rows of (residual + delta) and writes nothing back
+    rows = torch.tensor([tokens - 1, 0], device=DEVICE, dtype=torch.int32)
+    work3 = residual.clone()
+    out3 = ops.add_rmsnorm(work3, delta, weight, eps, dtype, rows=rows)
+    torch.testing.assert_close(out3.double(), expected[rows.long()], **tolerance(dtype))
+    assert torch.equal(work3, residual)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens, inter", [(5, 9728), (3, 100), (2, 7), (64, 24)])
+def test_swiglu(dtype, tokens, inter):
+    from pylon_b200.kernels import ops
+
+    gate_up = (torch.randn(tokens, 2 * inter, device=DEVICE) * 2).to(dtype)
+    out = ops.swiglu(gate_up)
+    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, **tolerance(dtype))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 300, 77), (5, 64, 64), (70, 130, 2560), (129, 1000, 33), (3, 151_936 // 8, 96)])
+def test_gemm_f32_is_true_32_bit(m, n, k):
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(m, k, device=DEVICE)
+    w = torch.randn(n, k, device=DEVICE)
+    y = ops.linear(x, w)
+    expected = x.double() @ w.double().T
+    # a TF32 product would be off by ~1e-3 relative; float32 accumulation stays near 1e-6
+    error = (y.double() - expected).abs().max() / expected.abs().max()
+    assert float(error) < 2e-6, float(error)
+    # a row's result does not depend on the other rows of the launch
+    alone = ops.linear(x[:1].contiguous(), w)
+    assert torch.equal(alone[0], y[0])
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 256, 128), (8, 6144, 2560), (40, 1000, 96), (300, 320, 224)])
+def test_linear_bf16(m, n, k):
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    expected = x.double() @ w.double().T
+    torch.testing.assert_close(ops.linear(x, w).double(), expected, rtol=2e-2, atol=2e-2)
+    wide = ops.linear(x, w, out_dtype=torch.float32)
+    assert wide.dtype == torch.float32
+    torch.testing.assert_close(wide.double(), expected, rtol=1e-3, atol=1e-3)
+
+
+# ---------------------------------------------------------------------------------------
+# a small paged cache for the kernels below
+# ---------------------------------------------------------------------------------------
+class Paged:
+    """Requests with given context lengths and new-token counts over shuffled pages."""
+
+    def __init__(self, kv_lens, q_lens, nkv, d, page_size, dtype, spare_pages=3, seed=0):
+        rng = np.random.default_rng(seed)
+        self.kv_lens, self.q_lens, self.page_size = list(kv_lens), list(q_lens), page_size
+        pages_needed = [-(-n // page_size) for n in kv_lens]
+        num_pages = sum(pages_needed) + spare_pages
+        order = rng.permutation(num_pages)
+        width = max(pages_needed) + 1
+        table = np.full((len(kv_lens), width), -1, dtype=np.int32)
+        cursor = 0
+        for r, need in enumerate(pages_needed):
+            table[r, :need] = order[cursor : cursor + need]
+            cursor += need
+        self.table = torch.tensor(table, device=DEVICE)
+        self.k_pages = torch.randn(num_pages, nkv, page_size, d, device=DEVICE).to(dtype)
+        self.v_pages = torch.randn(num_pages, nkv, page_size, d, device=DEVICE).to(dtype)
+        positions, token_row, q_start = [], [], [0]
+        for r, (kv, q) in enumerate(zip(kv_lens, q_lens)):
+            positions += list(range(kv - q, kv))
+            token_row += [r] * q
+            q_start.append(q_start[-1] + q)
+        as_int = lambda values: torch.tensor(values, device=DEVICE, dtype=torch.int32)
+        self.positions, self.token_row, self.q_start, self.kv_len = as_int(positions), as_int(token_row), as_int(q_start), as_int(kv_lens)
+        self.tokens = q_start[-1]
+
+    def gather(self, pages, r):
+        """[kv_len, nkv, d] float64 keys or values of request r."""
+        kv = self.kv_lens[r]
+        rows = [pages[int(self.table[r, j // self.page_size]), :, j % self.page_size] for j in range(kv)]
+        return torch.stack(rows).double()
+
+
+def attention_reference(q, cache: Paged, nq, nkv, d, window, scale):
+    out = torch.zeros(cache.tokens, nq, d, dtype=torch.float64, device=DEVICE)
+    group = nq // nkv
+    cursor = 0
+    for r, (kv, ql) in enumerate(zip(cache.kv_lens, cache.q_lens)):
+        k, v = cache.gather(cache.k_pages, r), cache.gather(cache.v_pages, r)
+        for i in range(ql):
+            position = kv - ql + i
+            low = 0 if not window else max(0, position - window + 1)
+            for h in range(nq):
+                scores = (k[low : position + 1, h // group] @ q[cursor + i, h].double()) * scale
+                out[cursor + i, h] = torch.softmax(scores, 0) @ v[low : position + 1, h // group]
+        cursor += ql
+    return out.reshape(cache.tokens, nq * d)
+
+
+ATTENTION_CASES = [
+    # kv_lens, q_lens, nq, nkv, d, page, window
+    ([1, 17, 130], [1, 17, 1], 4, 2, 16, 16, None),
+    ([300, 64, 65, 7], [1, 64, 2, 7], 6, 3, 32, 8, None),
+    ([200, 90], [70, 1], 8, 2, 64, 64, None),
+    ([150, 33], [1, 33], 10, 2, 128, 256, None),        # group of 5
+    ([97], [97], 2, 2, 256, 24, None),                    # no grouping, page size no power of two
+    ([120, 260], [9, 1], 4, 1, 48, 16, None),             # head size 48, one KV head
+    ([180, 75, 300], [40, 1, 1], 4, 2, 32, 16, 50),       # window
+    ([90], [90], 3, 1, 80, 32, 17),
+]
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: f"d{c[4]}_g{c[2] // c[3]}_p{c[5]}_w{c[6]}")
+@pytest.mark.parametrize("mode", ["float32", "bfloat16_simple", "bfloat16_mma", "bfloat16_mma_splits"])
+def test_paged_attention(case, mode):
+    from pylon_b200.kernels import ops
+
+    kv_lens, q_lens, nq, nkv, d, page, window = case
+    dtype = torch.float32 if mode == "float32" else torch.bfloat16
+    cache = Paged(kv_lens, q_lens, nkv, d, page, dtype)
+    # q sits inside a wider fused buffer, as in the engine
+    fused = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(dtype)
+    scale = 1.0 / math.sqrt(d)
+    expected = attention_reference(fused[:, : nq * d].reshape(cache.tokens, nq, d), cache, nq, nkv, d, window, scale)
+    out = ops.paged_attention(
+        fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table, nq,
+        max(q_lens), max(kv_lens), window=window, force_simple=mode in ("float32", "bfloat16_simple"),
+        num_splits=3 if mode == "bfloat16_mma_splits" else (1 if mode == "bfloat16_mma" else None),
+    )
+    torch.testing.assert_close(out.double(), expected, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)))
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16_mma", "bfloat16_mma_splits"])
+def test_attention_finds_one_far_key_among_hundreds(mode):
+    """Random keys would hide a wrong page: here one key far back dominates the softmax,
+    so the output must be that key's value."""
+    from pylon_b200.kernels import ops
+
+    dtype = torch.float32 if mode == "float32" else torch.bfloat16
+    nq, nkv, d, page = 4, 2, 64, 16
+    cache = Paged([700, 450], [1, 3], nkv, d, page, dtype, seed=5)
+    fused = (torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE) * 0.1).to(dtype)
+    targets = {0: 37, 1: 213}          # row -> position of the dominant key
+    cursor = 0
+    for r, ql in enumerate(cache.q_lens):
+        j = targets[r]
+        for kv_head in range(nkv):
+            direction = torch.randn(d, device=DEVICE)
+            direction = direction / direction.norm()
+            cache.k_pages[int(cache.table[r, j // page]), kv_head, j % page] = (direction * 40).to(dtype)
+            for i in range(ql):
+                for h in range(kv_head * 2, kv_head * 2 + 2):
+                    fused[cursor + i, h * d : (h + 1) * d] = (direction * 8).to(dtype)
+        cursor += ql
+    out = ops.paged_attention(
+        fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table, nq,
+        max(cache.q_lens), max(cache.kv_lens), force_simple=mode == "float32", num_splits=4 if mode.endswith("splits") else None,
+    ).reshape(cache.tokens, nq, d)
+    cursor = 0
+    for r, ql in enumerate(cache.q_lens):
+        j = targets[r]
+        for i in range(ql):
+            for h in range(nq):
+                want = cache.v_pages[int(cache.table[r, j // page]), h // 2, j % page].float()
+                torch.testing.assert_close(out[cursor + i, h].float(), want, rtol=2e-2, atol=2e-2)
+        cursor += ql
+
+
+def test_attention_refuses_what_it_cannot_do():
+    from pylon_b200.kernels import ops
+
+    cache = Paged([5], [5], 2, 16, 8, torch.bfloat16)
+    fused = torch.randn(5, 6 * 16, device=DEVICE).to(torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="query heads"):
+        ops.paged_attention(fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table, 3, 5, 5)
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.swiglu(torch.zeros(2, 4))
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, rotary, page, norm", [
+    (4, 2, 16, 16, 16, True), (6, 3, 32, 32, 8, True), (32, 8, 128, 128, 256, True), (5, 5, 64, 32, 4, True),
+    (2, 1, 80, 80, 24, False), (3, 1, 256, 64, 16, True),
+])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm):
+    from pylon_b200.kernels import ops
+
+    eps = 1e-5
+    cache = Paged([40, 9, 70], [13, 9, 1], nkv, d, page, dtype, seed=2)
+    k_before, v_before = cache.k_pages.clone(), cache.v_pages.clone()
+    qkv = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(dtype)
+    original = qkv.clone()
+    qw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    kw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    max_pos = 128
+    inv_freq = 1.0 / (10_000.0 ** (torch.arange(0, rotary, 2, dtype=torch.float32) / rotary))
+    angles = torch.arange(max_pos, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)
+    cos, sin = torch.cos(angles).to(DEVICE), torch.sin(angles).to(DEVICE)
+    ops.qk_norm_rope_kv_write(qkv, qw, kw, eps, cos, sin, rotary, cache.positions, cache.token_row, cache.table, page,
+                              cache.k_pages, cache.v_pages, nq, nkv, d)
+
+    def reference(x, weight, positions):          # x: [T, heads, d] float64
+        if weight is not None:
+            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+        c, s = cos[positions.long()].double().unsqueeze(1), sin[positions.long()].double().unsqueeze(1)
+        half = rotary // 2
+        first, second, rest = x[..., :half], x[..., half:rotary], x[..., rotary:]
+        return torch.cat((first * c - second * s, second * c + first * s, rest), dim=-1)
+
+    heads = original.double().reshape(cache.tokens, nq + 2 * nkv, d)
+    want_q = reference(heads[:, :nq], qw, cache.positions)
+    want_k = reference(heads[:, nq : nq + nkv], kw, cache.positions)
+    want_v = heads[:, nq + nkv :]
+    tol = tolerance(dtype)
+    torch.testing.assert_close(qkv.double().reshape(cache.tokens, -1, d)[:, :nq], want_q, **tol)
+    written = torch.zeros_like(cache.k_pages, dtype=torch.bool)
+    for t in range(cache.tokens):
+        r, pos = int(cache.token_row[t]), int(cache.positions[t])
+        p, slot = int(cache.table[r, pos // page]), pos % page
+        torch.testing.assert_close(cache.k_pages[p, :, slot].double(), want_k[t], **tol)
+        torch.testing.assert_close(cache.v_pages[p, :, slot].double(), want_v[t], rtol=0, atol=0)
+        written[p, :, slot] = True
+    # nothing else in the cache was touched
+    assert torch.equal(cache.k_pages[~written], k_before[~written]) and torch.equal(cache.v_pages[~written], v_before[~written])
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("vocab", [320, 151_936, 1000])
+def test_sample_argmax(vocab):
+    from pylon_b200.kernels import ops
+
+    logits = torch.randn(5, vocab, device=DEVICE)
+    logits[2, vocab - 1] = 50.0
+    logits[3, 7] = logits[3, 3] = 60.0          # a tie: the lower index wins
+    out = ops.sample(logits)
+    expected = logits.argmax(-1)
+    expected[3] = 3
+    assert out.tolist() == expected.tolist()
+
+
+@pytest.mark.parametrize("vocab, temperature, top_p", [(320, 0.8, 1.0), (151_936, 0.7, 0.9), (1000, 1.5, 0.5), (50, 0.3, 0.95)])
+def test_sample_temperature_and_top_p(vocab, temperature, top_p):
+    """The kernel's token is the one the plain definition picks for the same uniform number,
+    up to float32 rounding of the cumulative sums at a boundary."""
+    import plain_qwen3 as plain
+    from pylon_b200.kernels import ops
+
+    rows = 64
+    logits = torch.randn(rows, vocab, device=DEVICE) * 2
+    uniform = torch.rand(rows, device=DEVICE)
+    uniform[0], uniform[1] = 0.0, 0.99999
+    out = ops.sample(logits, torch.full((rows,), temperature, device=DEVICE), torch.full((rows,), top_p, device=DEVICE), uniform).tolist()
+    for r in range(rows):
+        probs = plain.sampling_distribution(logits[r].cpu(), temperature, top_p)
+        cdf = torch.cumsum(probs, 0)
+        token = out[r]
+        assert probs[token] > 0, f"row {r}: token {token} is outside the nucleus"
+        low = float(cdf[token] - probs[token])
+        high = float(cdf[token])
+        u = float(uniform[r])
+        assert low - 1e-4 <= u <= high + 1e-4, (r, token, low, u, high)
+
+
+def test_sample_mixed_rows_and_distribution():
+    from pylon_b200.kernels import ops
+
+    logits = torch.tensor([[0.0, 1.0, 2.0, 0.5]] * 3, device=DEVICE)
+    temperature = torch.tensor([0.0, 1.0, 1.0], device=DEVICE)
+    top_p = torch.tensor([1.0, 1.0, 0.5], device=DEVICE)
+    counts = torch.zeros(3, 4)
+    trials = 2000
+    big = logits.repeat(trials, 1)
+    out = ops.sample(big, temperature.repeat(trials), top_p.repeat(trials), torch.rand(3 * trials, device=DEVICE)).cpu().reshape(trials, 3)
+    for r in range(3):
+        counts[r] = torch.bincount(out[:, r].long(), minlength=4).float() / trials
+    assert counts[0].tolist() == [0, 0, 1, 0]                                   # temperature 0: arg-max
+    torch.testing.assert_close(counts[1], torch.softmax(logits[0].cpu(), 0), atol=0.04, rtol=0)
+    assert counts[2].tolist() == [0, 0, 1, 0]                                   # nucleus 0.5 keeps only the top token (p = 0.57)
