@@ -43,8 +43,11 @@ struct AttentionParams {
   const int* kv_len;
   const int* block_table;
   int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens;
+  int small_rows_elsewhere;   // rows of at most SMALL_ROWS packed query rows are left to the decode kernel
   float scale_log2;     // softmax scale * log2(e)
 };
+
+constexpr int SMALL_ROWS = 16;   // packed query rows (tokens x group) one MMA tile holds
 
 __device__ __forceinline__ unsigned smem_address(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -106,6 +109,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
   const int packed_rows = q_len * G;
   const int m0 = q_tile_index * BLOCK_M;
   if (m0 >= packed_rows) return;
+  if (p.small_rows_elsewhere && packed_rows <= SMALL_ROWS) return;   // the decode kernel takes this row
   const int kv_len = p.kv_len[row];
   const int pos0 = kv_len - q_len;   // position of the row's first new token
   const int* table = p.block_table + (size_t)row * p.table_width;
@@ -275,6 +279,212 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
   }
 }
 
+
+// -----------------------------------------------------------------------------------------
+// Decode form: rows with at most 16 packed query rows (one decoded token times the group, or
+// a few tokens).  All four warps share the one 16-row query tile and split every 64-key tile
+// between them (16 keys each), each with its own running softmax; the four partial results
+// are merged through shared memory at the end.  Key/value tiles run through a three-stage
+// cp.async pipeline.  When the page size is a multiple of 64 a tile is one contiguous run of
+// a page and is addressed with one table look-up; otherwise keys are gathered one by one.
+// -----------------------------------------------------------------------------------------
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_STAGE_ELEMS = 2 * TILE_ELEMS;   // keys then values
+constexpr size_t DEC_SMEM = (size_t)(SMALL_ROWS * LD + DEC_STAGES * DEC_STAGE_ELEMS) * sizeof(__nv_bfloat16);
+static_assert(DEC_STAGES * DEC_STAGE_ELEMS * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
+
+__device__ __forceinline__ void load_kv_tile_contiguous(__nv_bfloat16* dst, const __nv_bfloat16* pages, const int* table,
+                                                        int tile, int kv_len, int kv_head, const AttentionParams& p) {
+  const int key0 = tile * BLOCK_N;
+  const int page = key0 < kv_len ? table[key0 / p.page_size] : -1;
+  const bool page_ok = page >= 0 && page < p.num_pages;
+  const __nv_bfloat16* base = page_ok ? pages + (((size_t)page * p.nkv + kv_head) * p.page_size + key0 % p.page_size) * D : pages;
+#pragma unroll
+  for (int i = 0; i < BLOCK_N * CHUNKS / ATT_THREADS; ++i) {
+    const int c = threadIdx.x + i * ATT_THREADS;
+    const int r = c / CHUNKS, col = c % CHUNKS;
+    const bool valid = page_ok && key0 + r < kv_len;
+    cp_async_16(dst + r * LD + col * 8, valid ? base + (size_t)c * 8 : pages, valid);
+  }
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(const AttentionParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][LD]
+  __nv_bfloat16* stages = q_tile + SMALL_ROWS * LD;                      // [DEC_STAGES][2][64][LD]
+
+  const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+  const int q0 = p.q_start[row];
+  const int q_len = p.q_start[row + 1] - q0;
+  const int G = p.group;
+  const int packed_rows = q_len * G;
+  if (packed_rows <= 0 || packed_rows > SMALL_ROWS) return;   // larger rows belong to the tiled kernel
+  const int kv_len = p.kv_len[row];
+  const int pos0 = kv_len - q_len;
+  const int* table = p.block_table + (size_t)row * p.table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+
+  const int hi = pos0 + q_len - 1;
+  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
+  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int tile_end = min(first_tile + tiles, tile_begin + per_split);
+  const bool contiguous = p.page_size % BLOCK_N == 0;
+
+  int row_pos[2];
+  bool row_valid[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int m = g + 8 * h;
+    row_valid[h] = m < packed_rows;
+    row_pos[h] = pos0 + (row_valid[h] ? m / G : 0);
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+
+  auto issue = [&](int tile) {
+    if (tile < tile_end) {
+      __nv_bfloat16* dst = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS;
+      if (contiguous) {
+        load_kv_tile_contiguous(dst, p.k_pages, table, tile, kv_len, kv_head, p);
+        load_kv_tile_contiguous(dst + TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
+      } else {
+        load_kv_tile(dst, p.k_pages, table, tile, kv_len, kv_head, p);
+        load_kv_tile(dst + TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
+      }
+    }
+    cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
+  };
+
+  if (tile_begin < tile_end) {
+    for (int c = threadIdx.x; c < SMALL_ROWS * CHUNKS; c += ATT_THREADS) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const bool valid = r < packed_rows;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + (size_t)(q0 + r / G) * p.q_stride + (size_t)(kv_head * G + r % G) * D + col * 8;
+      cp_async_16(q_tile + r * LD + col * 8, src, valid);
+    }
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      issue(tile + DEC_STAGES - 1);
+      cp_async_wait<DEC_STAGES - 1>();
+      __syncthreads();
+      const __nv_bfloat16* ks = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS + warp * 16 * LD;
+      const __nv_bfloat16* vs = ks + TILE_ELEMS;
+
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned a[4], b[4];
+        ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+        mma_bf16(s[0], a, b[0], b[1]);
+        mma_bf16(s[1], a, b[2], b[3]);
+      }
+      const int key_base = tile * BLOCK_N + warp * 16 + 2 * tq;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int h = i >> 1;
+          const int key = key_base + n * 8 + (i & 1);
+          bool visible = row_valid[h] && key <= row_pos[h];
+          if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
+          if (!visible) s[n][i] = -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float new_max = fmaxf(row_max[h], mx);
+        const float use_max = new_max == -INFINITY ? 0.f : new_max;
+        const float alpha = exp2f((row_max[h] - use_max) * p.scale_log2);
+        const float shift = use_max * p.scale_log2;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const float p0 = exp2f(s[n][2 * h] * p.scale_log2 - shift);
+          const float p1 = exp2f(s[n][2 * h + 1] * p.scale_log2 - shift);
+          s[n][2 * h] = p0;
+          s[n][2 * h + 1] = p1;
+          sum += p0 + p1;
+        }
+        row_sum[h] = row_sum[h] * alpha + sum;
+        row_max[h] = new_max;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][2 * h] *= alpha; o[i][2 * h + 1] *= alpha; }
+      }
+      unsigned a[4];
+      a[0] = pack_bf16(s[0][0], s[0][1]);
+      a[1] = pack_bf16(s[0][2], s[0][3]);
+      a[2] = pack_bf16(s[1][0], s[1][1]);
+      a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int d2 = 0; d2 < D / 16; ++d2) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + d2 * 16 + 8 * (lane >> 4));
+        mma_bf16(o[2 * d2], a, b[0], b[1]);
+        mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+      }
+      __syncthreads();   // everyone is done with this stage before it is loaded again
+    }
+    cp_async_wait<0>();
+  }
+
+  // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
+  float* merge_o = reinterpret_cast<float*>(stages);                 // [4][16][D]
+  float* merge_max = merge_o + 4 * SMALL_ROWS * D;                   // [4][16]
+  float* merge_sum = merge_max + 4 * SMALL_ROWS;                     // [4][16]
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = row_sum[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int r = g + 8 * h;
+    if (tq == 0) {
+      merge_max[warp * SMALL_ROWS + r] = row_max[h];
+      merge_sum[warp * SMALL_ROWS + r] = sum;
+    }
+    float* dst = merge_o + ((size_t)warp * SMALL_ROWS + r) * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
+    const int r = e / D, col = e % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, merge_max[w * SMALL_ROWS + r]);
+    float total = 0.f, value = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float m = merge_max[w * SMALL_ROWS + r];
+      const float weight = m == -INFINITY ? 0.f : exp2f((m - mx) * p.scale_log2);
+      total += weight * merge_sum[w * SMALL_ROWS + r];
+      value += weight * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    const size_t token = (size_t)q0 + r / G;
+    const int head = kv_head * G + r % G;
+    if (p.num_splits == 1) {
+      p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(value * inv);
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + token) * p.nq + head;
+      p.partial_out[slot * D + col] = value * inv;
+      if (col == 0) p.partial_lse[slot] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;
+    }
+  }
+}
+
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
 // warp per (token, head).
 __global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
@@ -344,6 +554,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
   }
@@ -357,10 +568,20 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
   p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const long long q_tiles = ((long long)max_q * p.group + BLOCK_M - 1) / BLOCK_M;
-  if (q_tiles * num_splits > 2147483647LL) PYLON_REFUSE("paged_attention_mma: too many query tiles");
-  dim3 grid((unsigned)(q_tiles * num_splits), nkv, num_rows);
-  paged_attention_mma_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(p);
+  const long long packed_max = (long long)max_q * p.group;
+  const bool any_large = packed_max > SMALL_ROWS;
+  const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
+  p.small_rows_elsewhere = maybe_small ? 1 : 0;
+  if (any_large) {
+    const long long q_tiles = (packed_max + BLOCK_M - 1) / BLOCK_M;
+    if (q_tiles * num_splits > 2147483647LL) PYLON_REFUSE("paged_attention_mma: too many query tiles");
+    dim3 grid((unsigned)(q_tiles * num_splits), nkv, num_rows);
+    paged_attention_mma_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(p);
+  }
+  if (maybe_small) {
+    dim3 grid(num_splits, nkv, num_rows);
+    paged_attention_decode_kernel<<<grid, ATT_THREADS, DEC_SMEM, stream>>>(p);
+  }
   if (num_splits > 1) {
     const int warps = 4;
     combine_splits_kernel<<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(p.partial_out, p.partial_lse, p.out, num_splits, items);

@@ -59,6 +59,92 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   }
 }
 
+// Register-resident form for rows of up to 256 * 4 * ITEMS elements whose width is a
+// multiple of 4: every thread loads its ITEMS groups of 4 (all loads in flight at once),
+// the row is summed once and written once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&a);
+    raw.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+constexpr int NORM_THREADS = 256;
+
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                                                       const float* __restrict__ weight, const int* __restrict__ rows,
+                                                                       T* __restrict__ out, int width, float eps, int write_residual) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* res = residual + (size_t)row * width;
+  const T* del = delta ? delta + (size_t)row * width : nullptr;
+  T* dst = out + (size_t)r * width;
+  const int groups = width >> 2;
+  float4 x[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    x[k] = i < groups ? Vec4<float>::load(res + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (del) {
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const int i = threadIdx.x + k * NORM_THREADS;
+      if (i < groups) {
+        const float4 d = Vec4<T>::load(del + 4 * i);
+        x[k].x += d.x; x[k].y += d.y; x[k].z += d.z; x[k].w += d.w;
+      }
+    }
+  }
+  float sumsq = 0.f;
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) sumsq += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+  const float inv = rsqrtf(block_sum(sumsq, scratch) / (float)width + eps);
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    if (i < groups) {
+      if (del && write_residual) Vec4<float>::store(res + 4 * i, x[k]);
+      const float4 w = Vec4<float>::load(weight + 4 * i);
+      Vec4<T>::store(dst + 4 * i, make_float4(x[k].x * inv * w.x, x[k].y * inv * w.y, x[k].z * inv * w.z, x[k].w * inv * w.w));
+    }
+  }
+}
+
+template <typename T>
+static bool launch_add_rmsnorm_vec(float* residual, const T* delta, const float* weight, const int* rows, T* out, int n_rows,
+                                   int width, float eps, int write_residual, cudaStream_t stream) {
+  if (width % 4 || width > NORM_THREADS * 4 * 8) return false;
+  if (((uintptr_t)residual % 16) || ((uintptr_t)weight % 16) || ((uintptr_t)out % 8) || (delta && ((uintptr_t)delta % 8))) return false;
+  const int items = (width / 4 + NORM_THREADS - 1) / NORM_THREADS;
+#define PYLON_NORM_CASE(N)                                                                                     \
+  case N:                                                                                                      \
+    add_rmsnorm_vec_kernel<T, N><<<n_rows, NORM_THREADS, 0, stream>>>(residual, delta, weight, rows, out, width, eps, write_residual); \
+    return true;
+  switch (items) {
+    PYLON_NORM_CASE(1) PYLON_NORM_CASE(2) PYLON_NORM_CASE(3) PYLON_NORM_CASE(4)
+    PYLON_NORM_CASE(5) PYLON_NORM_CASE(6) PYLON_NORM_CASE(7) PYLON_NORM_CASE(8)
+  }
+#undef PYLON_NORM_CASE
+  return false;
+}
+
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -222,12 +308,15 @@ extern "C" int pylon_add_rmsnorm(float* residual, const void* delta, const float
   if (width <= 0) PYLON_REFUSE("add_rmsnorm: width %d", width);
   if (rows && write_residual) PYLON_REFUSE("add_rmsnorm: a row selection cannot update the residual");
   const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
-  if (dtype == PYLON_DTYPE_F32)
-    add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, rows, (float*)out, width, eps, write_residual);
-  else if (dtype == PYLON_DTYPE_BF16)
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, width, eps, write_residual);
-  else
+  if (dtype == PYLON_DTYPE_F32) {
+    if (!launch_add_rmsnorm_vec<float>(residual, (const float*)delta, weight, rows, (float*)out, n_rows, width, eps, write_residual, stream))
+      add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, rows, (float*)out, width, eps, write_residual);
+  } else if (dtype == PYLON_DTYPE_BF16) {
+    if (!launch_add_rmsnorm_vec<__nv_bfloat16>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, n_rows, width, eps, write_residual, stream))
+      add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, width, eps, write_residual);
+  } else {
     PYLON_REFUSE("add_rmsnorm: unknown dtype %d", dtype);
+  }
   PYLON_CHECK_LAUNCH("add_rmsnorm");
 }
 

@@ -69,7 +69,18 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
   const float* x = logits + (size_t)row * row_stride;
 
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int i = tid; i < vocab; i += blockDim.x) best = better(best, ArgMax{x[i], i});
+  {
+    // Four independent loads in flight per thread: a row is read in a few round trips.
+    int i = tid;
+    for (; i + 3 * SAMPLE_THREADS < vocab; i += 4 * SAMPLE_THREADS) {
+      const float v0 = x[i], v1 = x[i + SAMPLE_THREADS], v2 = x[i + 2 * SAMPLE_THREADS], v3 = x[i + 3 * SAMPLE_THREADS];
+      best = better(best, ArgMax{v0, i});
+      best = better(best, ArgMax{v1, i + SAMPLE_THREADS});
+      best = better(best, ArgMax{v2, i + 2 * SAMPLE_THREADS});
+      best = better(best, ArgMax{v3, i + 3 * SAMPLE_THREADS});
+    }
+    for (; i < vocab; i += SAMPLE_THREADS) best = better(best, ArgMax{x[i], i});
+  }
   best = block_argmax(best, arg_scratch);
   const float t = temperature ? temperature[row] : 0.f;
   if (!(t > 0.f) || best.index >= vocab) {  // greedy (or a row of NaN: index stays in range)

@@ -88,6 +88,8 @@ class Engine:
             )
         self.max_context = min(self.spec.max_positions, num_pages * page_size)
         self.step_function = StepFunction(self.model, self.cache)
+        if self.config.cuda_graphs:
+            self.step_function.enable_graphs()
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(
             self.cache, self.step_function, self.sampler,

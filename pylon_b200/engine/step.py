@@ -70,6 +70,15 @@ class StepFunction:
         self.dtype = model.dtype
         self.vocab_size = model.spec.vocab_size
         self.max_positions = model.spec.max_positions
+        self.graphs = None
+
+    def enable_graphs(self) -> None:
+        """Decode-only steps (one token per request, logits wanted for each) are replayed from
+        CUDA graphs from now on; the logits tensor such a step returns is reused by the next
+        graph step of the same batch size."""
+        from pylon_b200.engine.graphs import DecodeGraphs
+
+        self.graphs = DecodeGraphs(self)
 
     # -- host side ---------------------------------------------------------------------
     def fill(self, entries: Sequence[StepEntry], layout: StepLayout, buffer: np.ndarray) -> tuple[int, int]:
@@ -149,21 +158,11 @@ class StepFunction:
         batch = [(entry.request, len(entry.tokens)) for entry in entries]
         self.cache.prepare(batch)          # all pages of the step, or OutOfPages and nothing
         try:
-            requests = [entry.request for entry in entries]
-            widths = tuple(
-                max(1, max(len(request.tables[g]) for request in requests)) for g in range(len(self.cache.groups))
-            )
-            layout = StepLayout(
-                tokens=sum(len(entry.tokens) for entry in entries),
-                rows=len(entries),
-                logits=sum(len(entry.want) for entry in entries),
-                table_widths=widths,
-            )
-            host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
-            max_q, max_kv = self.fill(entries, layout, host.numpy())
-            device_buffer = host.to(self.device, non_blocking=True)
-            step, tables = self.view(device_buffer, layout, max_q, max_kv)
-            logits = self.model.forward(step, self.cache.layer_caches(tables))
+            logits = None
+            if self.graphs is not None and self.graphs.applies(entries):
+                logits = self.graphs.run(entries)
+            if logits is None:
+                logits = self._run_eager(entries)
         except BaseException:
             for request, _ in batch:
                 self.cache.rollback(request)
@@ -171,3 +170,20 @@ class StepFunction:
         for request, _ in batch:
             self.cache.commit(request)
         return logits
+
+    def _run_eager(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        requests = [entry.request for entry in entries]
+        widths = tuple(
+            max(1, max(len(request.tables[g]) for request in requests)) for g in range(len(self.cache.groups))
+        )
+        layout = StepLayout(
+            tokens=sum(len(entry.tokens) for entry in entries),
+            rows=len(entries),
+            logits=sum(len(entry.want) for entry in entries),
+            table_widths=widths,
+        )
+        host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
+        max_q, max_kv = self.fill(entries, layout, host.numpy())
+        device_buffer = host.to(self.device, non_blocking=True)
+        step, tables = self.view(device_buffer, layout, max_q, max_kv)
+        return self.model.forward(step, self.cache.layer_caches(tables))

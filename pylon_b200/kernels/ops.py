@@ -73,6 +73,9 @@ _SIGNATURES = {
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
+    "gemm_skinny.cu": {
+        "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
+    },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -229,12 +232,16 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
 # ---------------------------------------------------------------------------------------
 # matrix products: y = x @ w.T
 # ---------------------------------------------------------------------------------------
+SKINNY_MAX_ROWS = 8   # up to this many rows the weight-streaming kernel runs (it takes up to 64); above, the library
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x [M, K] @ w [N, K].T`` with float32 accumulation.
 
     float32 operands use the plain-FMA kernel (true 32-bit, no tensor cores).  bfloat16
-    operands go to the library matrix product, as raun6k/Pylon's ``nn.Linear`` layers do
-    (src/pylon/model/layers.py:17-23,95-106); ``out_dtype=torch.float32`` keeps the 32-bit
+    operands with up to ``SKINNY_MAX_ROWS`` rows use the weight-streaming kernel; with more
+    rows they go to the library matrix product, as raun6k/Pylon's ``nn.Linear`` layers do
+    (src/pylon/model/layers.py:17-23,95-106).  ``out_dtype=torch.float32`` keeps the 32-bit
     accumulator (used for logits).
     """
     _need_cuda(x, w)
@@ -251,9 +258,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _check(library, library.pylon_gemm_f32_nt(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), n, _stream()))
         return y
     _need(x.dtype == torch.bfloat16, f"linear: unsupported dtype {x.dtype}")
+    _need(out_dtype in (torch.bfloat16, torch.float32), f"linear: unsupported result dtype {out_dtype}")
+    if m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        # Few rows (decode): our weight-streaming kernel.
+        y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        library = _library("gemm_skinny.cu")
+        _check(library, library.pylon_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), n, _dtype_code(out_dtype), _stream()))
+        return y
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
-    _need(out_dtype == torch.float32, f"linear: unsupported result dtype {out_dtype}")
     return torch.mm(x, w.t(), out_dtype=torch.float32)
 
 
@@ -261,14 +275,28 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 # attention over the paged cache
 # ---------------------------------------------------------------------------------------
 def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:
-    """How many key/value splits a launch uses: one when the step has enough query tiles to
-    fill the GPU (prefill), else enough to give every SM about two blocks (decode)."""
-    q_tiles = -(-max_q * group // 64)
-    blocks = num_rows * nkv * q_tiles
+    """How many key/value splits an attention launch uses.
+
+    Steps with long rows (prefill) have enough query tiles to fill the GPU and use one.  For
+    rows of decoded tokens the blocks are (rows x KV heads x splits), two resident per SM:
+    the number of splits is the one with the least estimated time, waves x (tiles per split
+    + a fixed start-up cost), so that the last wave is not mostly empty.
+    """
     kv_tiles = max(1, -(-max_kv // 64))
-    if blocks >= 2 * _SM_COUNT or kv_tiles == 1:
-        return 1
-    return int(max(1, min(kv_tiles, 64, (2 * _SM_COUNT + blocks - 1) // blocks)))
+    slots = 2 * _SM_COUNT
+    if max_q * group > 16:
+        blocks = num_rows * nkv * -(-max_q * group // 64)
+        if blocks >= _SM_COUNT or kv_tiles == 1:
+            return 1
+        return int(max(1, min(kv_tiles, 64, slots // blocks)))
+    blocks = num_rows * nkv
+    best, best_cost = 1, None
+    for splits in range(1, min(kv_tiles, 64) + 1):
+        waves = -(-blocks * splits // slots)
+        cost = waves * (-(-kv_tiles // splits) + 4)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    return best
 
 
 _SM_COUNT = 148

@@ -31,13 +31,14 @@ def expected(tiny_folders):
     return out
 
 
-def make_engine(folder, name, dtype, steps, max_requests=4):
+def make_engine(folder, name, dtype, steps, max_requests=4, cuda_graphs=False):
     from pylon_b200.config import EngineConfig
     from pylon_b200.engine import Engine
 
     page = TINY_PAGE_SIZES[name]
     tokens = trace_tools.pool_tokens(steps, round_to=page)
-    config = EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=tokens, max_context=256, max_batch_size=max_requests)
+    config = EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=tokens, max_context=256, max_batch_size=max_requests,
+                          cuda_graphs=cuda_graphs)
     return Engine(folder, config)
 
 
@@ -68,6 +69,21 @@ def test_cuttings_match_plain(name, cutting, dtype, tiny_folders, expected):
     pool = engine.cache.groups[0].pool
     assert pool.free_count == pool.num_pages            # everything was given back
     assert pool.acquired_total > pool.num_pages          # and pages were used again
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["tail_one_by_one", "mixed"])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+def test_decode_steps_replayed_from_cuda_graphs(name, cutting, dtype, tiny_folders, expected):
+    """With graphs on, steps of single tokens come from captured graphs (one per batch size);
+    the logits must be the same as without."""
+    requests = make_requests(name)
+    steps = CUTTINGS[cutting](requests)
+    engine = make_engine(tiny_folders[name], name, dtype, steps, cuda_graphs=True)
+    got = trace_tools.run_in_process(engine, steps)
+    compare(got, expected[name], dtype)
+    graphs = engine.step_function.graphs
+    assert graphs.captured and not graphs.failed
 
 
 @pytest.mark.parametrize("name", ["tinyA", "tinyB"])
