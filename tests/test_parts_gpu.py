@@ -1,0 +1,301 @@
+"""Each part of a layer alone on the GPU against the plain implementation's function for it,
+and models put together in the test from registered parts — among them a toy mixer with a
+state of its own and a windowed attention — stepped through the engine without any change
+to the framework's files."""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass
+from typing import Mapping, Optional, Sequence
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import trace_tools
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda"
+
+
+def step_view(q_lens: Sequence[int], starts: Sequence[int], dtype):
+    """A StepView for rows that bring ``q_lens`` tokens at positions ``starts``."""
+    from pylon_b200.parts.base import StepView
+
+    positions, token_row, q_start = [], [], [0]
+    for r, (n, s) in enumerate(zip(q_lens, starts)):
+        positions += list(range(s, s + n))
+        token_row += [r] * n
+        q_start.append(q_start[-1] + n)
+    as_int = lambda v: torch.tensor(v, device=DEVICE, dtype=torch.int32)
+    step = StepView()
+    step.positions, step.token_row, step.q_start = as_int(positions), as_int(token_row), as_int(q_start)
+    step.kv_len = as_int([s + n for n, s in zip(q_lens, starts)])
+    step.slots = as_int(list(range(len(q_lens))))
+    step.token_ids = as_int([0] * q_start[-1])
+    step.logit_rows = as_int([])
+    step.num_tokens, step.num_rows, step.num_logits = q_start[-1], len(q_lens), 0
+    step.max_q, step.max_kv = max(q_lens), max(s + n for n, s in zip(q_lens, starts))
+    step.dtype, step.device = dtype, torch.device(DEVICE)
+    return step
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part_folds_the_pending_delta(dtype):
+    from pylon_b200.parts import NORMS, PartSpec, ResidualStream
+
+    width, eps = 200, 1e-5
+    norm = NORMS.build(PartSpec("rmsnorm", {"width": width, "eps": eps}))
+    weight = torch.rand(width) + 0.5
+    norm.load({"weight": weight.to(DEVICE)}, dtype, torch.device(DEVICE))
+    residual = torch.randn(6, width, device=DEVICE)
+    delta = torch.randn(6, width, device=DEVICE).to(dtype)
+    stream = ResidualStream(residual.clone())
+    stream.add(delta)
+    out = norm.apply(stream)
+    want_sum = residual.double() + delta.double()
+    torch.testing.assert_close(stream.residual.double(), want_sum, rtol=1e-6, atol=1e-6)
+    assert stream.pending is None
+    want = plain.rms_norm(want_sum.cpu(), weight.double(), eps)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(out.double().cpu(), want, **tol)
+
+
+def test_rotary_part_builds_the_reference_tables():
+    from pylon_b200.parts import POSITION_ENCODINGS, PartSpec
+
+    rope = POSITION_ENCODINGS.build(PartSpec("rope", {"head_dim": 48, "theta": 1_000_000.0, "max_positions": 300}))
+    cos, sin, rotary = rope.rotary_table(torch.device(DEVICE))
+    want_cos, want_sin = plain.rope_tables(48, 1_000_000.0, torch.arange(300), torch.float32)
+    assert rotary == 48 and cos.shape == (300, 24)
+    torch.testing.assert_close(cos.cpu(), want_cos[:, :24], rtol=0, atol=1e-6)
+    torch.testing.assert_close(sin.cpu(), want_sin[:, :24], rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from pylon_b200.parts import FEED_FORWARDS, PartSpec
+
+    width, inter, tokens = 72, 200, 11
+    part = FEED_FORWARDS.build(PartSpec("swiglu", {"width": width, "intermediate": inter}))
+    weights = {"gate_proj.weight": torch.randn(inter, width) * 0.1, "up_proj.weight": torch.randn(inter, width) * 0.1,
+               "down_proj.weight": torch.randn(width, inter) * 0.1}
+    weights = {k: v.to(dtype) for k, v in weights.items()}
+    part.load({k: v.to(DEVICE) for k, v in weights.items()}, dtype, torch.device(DEVICE))
+    h = torch.randn(tokens, width).to(dtype)
+    out = part.forward(h.to(DEVICE), None)
+    want = plain.swiglu_part(h.double(), {"mlp." + k: v.double() for k, v in weights.items()}, "")
+    tol = dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(out.double().cpu(), want, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, kv_heads, dim, window", [(4, 2, 16, None), (6, 3, 32, None), (10, 2, 64, None), (4, 1, 32, 7)])
+def test_attention_part_whole_and_in_two_steps(dtype, heads, kv_heads, dim, window):
+    """The attention mixer alone with a hand-made cache: a whole sequence in one step, and
+    the same sequence in two steps, against the plain attention part."""
+    from pylon_b200.parts import MIXERS, LayerCache, PartSpec
+
+    width, tokens, page, eps = 80, 37, 8, 1e-5
+    spec = PartSpec("gqa_attention", {
+        "width": width, "n_heads": heads, "n_kv_heads": kv_heads, "head_dim": dim, "qk_norm_eps": eps, "window": window,
+        "position": PartSpec("rope", {"head_dim": dim, "theta": 10_000.0, "max_positions": 64}),
+    })
+    torch.manual_seed(3)
+    raw = {"q_proj.weight": torch.randn(heads * dim, width) * 0.1, "k_proj.weight": torch.randn(kv_heads * dim, width) * 0.1,
+           "v_proj.weight": torch.randn(kv_heads * dim, width) * 0.1, "o_proj.weight": torch.randn(width, heads * dim) * 0.1}
+    raw = {k: v.to(dtype) for k, v in raw.items()}
+    norms = {"q_norm.weight": torch.rand(dim) + 0.5, "k_norm.weight": torch.rand(dim) + 0.5}
+    h = torch.randn(tokens, width).to(dtype)
+    cfg = {"num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim, "rms_norm_eps": eps}
+    cos, sin = plain.rope_tables(dim, 10_000.0, torch.arange(tokens), torch.float64)
+    weights64 = {"self_attn." + k: v.double() for k, v in {**raw, **norms}.items()}
+    want = plain.attention_part(h.double(), weights64, "", cfg, cos, sin, window)
+
+    def run(cuts):
+        part = MIXERS.build(spec)
+        part.load({**{k: v.to(DEVICE) for k, v in raw.items()}, **{k: v.to(DEVICE) for k, v in norms.items()}}, dtype, torch.device(DEVICE))
+        pages = -(-tokens // page)
+        cache = LayerCache(
+            k_pages=torch.zeros(pages + 2, kv_heads, page, dim, device=DEVICE, dtype=dtype),
+            v_pages=torch.zeros(pages + 2, kv_heads, page, dim, device=DEVICE, dtype=dtype),
+            block_table=torch.tensor([[p + 1 for p in range(pages)]], device=DEVICE, dtype=torch.int32), page_size=page,
+        )
+        outs, start = [], 0
+        for count in cuts:
+            step = step_view([count], [start], dtype)
+            outs.append(part.forward(h[start : start + count].to(DEVICE).contiguous(), step, cache))
+            start += count
+        return torch.cat(outs).double().cpu()
+
+    tol = dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(run([tokens]), want, **tol)
+    torch.testing.assert_close(run([20, 17]), want, **tol)
+    torch.testing.assert_close(run([30, 1, 1, 5]), want, **tol)
+
+
+# ---------------------------------------------------------------------------------------
+# models put together in the test
+# ---------------------------------------------------------------------------------------
+def register_toy_parts():
+    """A mixer with a state of its own (running mean of its inputs) — defined here, not in the
+    framework."""
+    from pylon_b200.parts import MIXERS, CacheNeed, Mixer, StateNeed, TensorDecl
+    from pylon_b200.kernels import ops
+
+    if "toy_running_mean" in MIXERS.kinds():
+        return
+
+    @MIXERS.register("toy_running_mean")
+    class RunningMean(Mixer):
+        """delta_t = W mean(h_0..h_t).  State per request: the running sum, float32 [width]."""
+
+        def __init__(self, width: int) -> None:
+            self.width = width
+            self.w = None
+
+        def tensors(self):
+            return (TensorDecl("mix.weight", (self.width, self.width)),)
+
+        def load(self, tensors, dtype, device):
+            self.w = tensors["mix.weight"].contiguous()
+
+        def cache_need(self):
+            return CacheNeed(state=StateNeed((self.width,), torch.float32))
+
+        def forward(self, h, step, cache):
+            starts = step.q_start.tolist()
+            slots = step.slots.tolist()
+            means = torch.empty_like(h, dtype=torch.float32)
+            for r in range(step.num_rows):
+                a, b = starts[r], starts[r + 1]
+                running = cache.state[slots[r]] + torch.cumsum(h[a:b].float(), dim=0)
+                cache.state[slots[r]] = running[-1]
+                means[a:b] = running / (step.positions[a:b].float() + 1.0).unsqueeze(1)
+            return ops.linear(means.to(h.dtype), self.w)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    """A made-up architecture for the tests: layer 0 mixes with the running mean, layer 1 with
+    windowed attention, layer 2 with full attention; the order runs layer 0 twice."""
+
+    architecture = "ToyForCausalLM"
+    vocab_size: int = 200
+    width: int = 48
+    heads: int = 4
+    kv_heads: int = 2
+    head_dim: int = 16
+    intermediate: int = 88
+    window: int = 11
+    eps: float = 1e-5
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: data[k] for k in ("vocab_size", "width", "heads", "kv_heads", "head_dim", "intermediate", "window", "eps")})
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], **self.__dict__}
+
+
+def toy_spec(config: ToyConfig, max_positions: Optional[int] = None):
+    from pylon_b200.parts import LayerSpec, ModelSpec, PartSpec
+    from pylon_b200.parts.spec import RunSpec
+
+    positions = max_positions or 512
+    norm = PartSpec("rmsnorm", {"width": config.width, "eps": config.eps})
+    ffn = PartSpec("swiglu", {"width": config.width, "intermediate": config.intermediate})
+
+    def attention(window):
+        return PartSpec("gqa_attention", {
+            "width": config.width, "n_heads": config.heads, "n_kv_heads": config.kv_heads, "head_dim": config.head_dim,
+            "qk_norm_eps": config.eps, "window": window,
+            "position": PartSpec("rope", {"head_dim": config.head_dim, "theta": 10_000.0, "max_positions": positions}),
+        })
+
+    def block(mixer):
+        return PartSpec("prenorm", {"mixer": mixer, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm})
+
+    layers = (
+        LayerSpec("layers.0.", block(PartSpec("toy_running_mean", {"width": config.width}))),
+        LayerSpec("layers.1.", block(attention(config.window))),
+        LayerSpec("layers.2.", block(attention(None))),
+    )
+    return ModelSpec(
+        width=config.width, vocab_size=config.vocab_size, max_positions=positions, embedding_name="embed.weight", lm_head_name="head.weight",
+        final_norm=norm, final_norm_prefix="norm.", layers=layers, order=(RunSpec(0), RunSpec(1), RunSpec(0), RunSpec(2)),
+    )
+
+
+def toy_plain_forward(config: ToyConfig, w: Mapping[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+    """The toy model on a whole sequence, from the plain implementation's functions."""
+    ids = torch.as_tensor(list(tokens))
+    x = w["embed.weight"][ids]
+    cos, sin = plain.rope_tables(config.head_dim, 10_000.0, torch.arange(len(ids)), x.dtype)
+    cfg = {"num_attention_heads": config.heads, "num_key_value_heads": config.kv_heads, "head_dim": config.head_dim, "rms_norm_eps": config.eps}
+
+    def running_mean(h, prefix):
+        means = torch.cumsum(h, dim=0) / torch.arange(1, len(h) + 1, dtype=h.dtype).unsqueeze(1)
+        return means @ w[prefix + "self_attn.mix.weight"].T
+
+    def run(x, layer, window):
+        prefix = f"layers.{layer}."
+        h = plain.rms_norm(x, w[prefix + "input_layernorm.weight"], config.eps)
+        x = x + (running_mean(h, prefix) if layer == 0 else plain.attention_part(h, w, prefix, cfg, cos, sin, window))
+        h = plain.rms_norm(x, w[prefix + "post_attention_layernorm.weight"], config.eps)
+        return x + plain.swiglu_part(h, w, prefix)
+
+    for layer, window in ((0, None), (1, config.window), (0, None), (2, None)):
+        x = run(x, layer, window)
+    return plain.rms_norm(x, w["norm.weight"], config.eps) @ w["head.weight"].T
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    from pylon_b200.config import register_architecture
+    from pylon_b200.config.registry import ARCHITECTURES
+    from pylon_b200.weights import write_random_model
+
+    register_toy_parts()
+    register_architecture(ToyConfig.architecture, ToyConfig, toy_spec)
+    folder = tmp_path_factory.mktemp("toy")
+    write_random_model(ToyConfig(), 11, folder)
+    yield folder
+    ARCHITECTURES.pop(ToyConfig.architecture, None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
+def test_toy_model_with_state_window_and_a_layer_run_twice(toy_folder, cutting, dtype):
+    """Registered, built from a model folder and stepped through the engine: the state of the
+    running-mean mixer lives in the request's slot (one per run of the layer), the windowed
+    layers have pages of their own and give back the ones the window has passed."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine
+
+    config = ToyConfig()
+    _, weights = plain.read_model(toy_folder)
+    rng = np.random.default_rng(5)
+    requests = {f"t{i}": rng.integers(0, config.vocab_size, size=n).tolist() for i, n in enumerate((61, 9, 44, 90, 25))}
+    expected = {rid: plain.as_numpy(toy_plain_forward(config, weights, tokens)) for rid, tokens in requests.items()}
+    builders = {"whole": trace_tools.whole, "tail_one_by_one": trace_tools.tail_one_by_one,
+                "changing_portions": trace_tools.changing_portions, "mixed": trace_tools.mixed}
+    steps = builders[cutting](requests)
+    page = 8
+    engine = Engine(toy_folder, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=trace_tools.pool_tokens(steps, page),
+                                             max_context=128, max_batch_size=4))
+    assert len(engine.cache.groups) == 2                        # windowed and full attention: pages of their own
+    assert engine.cache.state_bytes_per_request() == 2 * config.width * 4   # one state per run of layer 0
+    got = trace_tools.run_in_process(engine, steps)
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
+    for rid in requests:
+        np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, **tol)
+    windowed = next(g for g in engine.cache.groups if g.need.window is not None)
+    full = next(g for g in engine.cache.groups if g.need.window is None)
+    assert windowed.pool.free_count == windowed.pool.num_pages and full.pool.free_count == full.pool.num_pages
+    if cutting != "whole":
+        # the windowed group never needed as many pages at once as the full one
+        assert windowed.pool.acquired_total >= full.pool.acquired_total > 0
