@@ -26,7 +26,7 @@ namespace pylon {
 
 constexpr int D = PYLON_HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 in 16..256");
-constexpr int BLOCK_M = 64, BLOCK_N = 64, ATT_THREADS = 128;
+constexpr int BLOCK_N = 64, ATT_THREADS = 128;
 constexpr int LD = D + 8;              // padded row: ldmatrix rows fall on distinct banks
 constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
 constexpr int TILE_ELEMS = BLOCK_N * LD;
@@ -95,204 +95,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bflo
   }
 }
 
-__global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const AttentionParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][LD]
-  __nv_bfloat16* k_tiles = q_tile + BLOCK_M * LD;                         // [2][64][LD]
-  __nv_bfloat16* v_tiles = k_tiles + 2 * TILE_ELEMS;                      // [2][64][LD]
-
-  const int row = blockIdx.z, kv_head = blockIdx.y;
-  const int q_tile_index = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
-  const int q0 = p.q_start[row];
-  const int q_len = p.q_start[row + 1] - q0;
-  const int G = p.group;
-  const int packed_rows = q_len * G;
-  const int m0 = q_tile_index * BLOCK_M;
-  if (m0 >= packed_rows) return;
-  if (p.small_rows_elsewhere && packed_rows <= SMALL_ROWS) return;   // the decode kernel takes this row
-  const int kv_len = p.kv_len[row];
-  const int pos0 = kv_len - q_len;   // position of the row's first new token
-  const int* table = p.block_table + (size_t)row * p.table_width;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-  const int token_first = m0 / G;
-  const int last_packed = min(packed_rows, m0 + BLOCK_M) - 1;
-  const int token_last = last_packed / G;
-  const int hi = pos0 + token_last;                                                   // last visible key (inclusive)
-  const int lo = p.window > 0 ? max(0, pos0 + token_first - p.window + 1) : 0;        // first visible key
-  const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
-  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = first_tile + split * per_split;
-  const int tile_end = min(first_tile + tiles, tile_begin + per_split);
-
-  // This thread's two rows of the warp's 16: packed index, token position, validity.
-  int row_pos[2], row_token[2], row_head[2];
-  bool row_valid[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int m = m0 + warp * 16 + g + 8 * h;
-    row_valid[h] = m < packed_rows;
-    row_token[h] = row_valid[h] ? m / G : 0;
-    row_head[h] = kv_head * G + (row_valid[h] ? m % G : 0);
-    row_pos[h] = pos0 + row_token[h];
-  }
-
-  // A warp whose 16 rows lie past the end (decoded tokens fill only a few rows) helps with
-  // the loads and skips the arithmetic.
-  const bool warp_active = m0 + warp * 16 < packed_rows;
-
-  float o[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
-
-  if (tile_begin < tile_end) {
-    // Query tile: packed rows m0 .. m0+63, zero-filled past the end.
-    for (int c = threadIdx.x; c < BLOCK_M * CHUNKS; c += ATT_THREADS) {
-      const int r = c / CHUNKS, col = c % CHUNKS;
-      const int m = m0 + r;
-      const bool valid = m < packed_rows;
-      const __nv_bfloat16* src = p.q;
-      if (valid) src = p.q + (size_t)(q0 + m / G) * p.q_stride + (size_t)(kv_head * G + m % G) * D + col * 8;
-      cp_async_16(q_tile + r * LD + col * 8, src, valid);
-    }
-    load_kv_tile(k_tiles, p.k_pages, table, tile_begin, kv_len, kv_head, p);
-    load_kv_tile(v_tiles, p.v_pages, table, tile_begin, kv_len, kv_head, p);
-    cp_async_commit();
-
-    for (int tile = tile_begin; tile < tile_end; ++tile) {
-      const int stage = (tile - tile_begin) & 1;
-      if (tile + 1 < tile_end) {
-        load_kv_tile(k_tiles + (stage ^ 1) * TILE_ELEMS, p.k_pages, table, tile + 1, kv_len, kv_head, p);
-        load_kv_tile(v_tiles + (stage ^ 1) * TILE_ELEMS, p.v_pages, table, tile + 1, kv_len, kv_head, p);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
-      __syncthreads();
-      const __nv_bfloat16* ks = k_tiles + stage * TILE_ELEMS;
-      const __nv_bfloat16* vs = v_tiles + stage * TILE_ELEMS;
-      if (warp_active) {
-
-      // S = Q K^T for this warp's 16 rows and the tile's 64 keys.
-      float s[BLOCK_N / 8][4];
-#pragma unroll
-      for (int i = 0; i < BLOCK_N / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        unsigned a[4];
-        ldmatrix_x4(a, q_tile + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
-#pragma unroll
-        for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
-          unsigned b[4];
-          ldmatrix_x4(b, ks + (n2 * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
-          mma_bf16(s[2 * n2], a, b[0], b[1]);
-          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
-        }
-      }
-
-      // Mask: key visible iff key <= position (and > position - window) and the row exists.
-      const int key_base = tile * BLOCK_N + 2 * tq;
-#pragma unroll
-      for (int n = 0; n < BLOCK_N / 8; ++n) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int h = i >> 1;
-          const int key = key_base + n * 8 + (i & 1);
-          bool visible = row_valid[h] && key <= row_pos[h];
-          if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
-          if (!visible) s[n][i] = -INFINITY;
-        }
-      }
-
-      // Online softmax in float32 (base 2).
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int n = 0; n < BLOCK_N / 8; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float new_max = fmaxf(row_max[h], mx);
-        const float use_max = new_max == -INFINITY ? 0.f : new_max;
-        const float alpha = exp2f((row_max[h] - use_max) * p.scale_log2);   // exp2(-inf) = 0 on the first tile
-        const float shift = use_max * p.scale_log2;
-        float sum = 0.f;
-#pragma unroll
-        for (int n = 0; n < BLOCK_N / 8; ++n) {
-          const float p0 = exp2f(s[n][2 * h] * p.scale_log2 - shift);
-          const float p1 = exp2f(s[n][2 * h + 1] * p.scale_log2 - shift);
-          s[n][2 * h] = p0;
-          s[n][2 * h + 1] = p1;
-          sum += p0 + p1;
-        }
-        row_sum[h] = row_sum[h] * alpha + sum;
-        row_max[h] = new_max;
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) { o[i][2 * h] *= alpha; o[i][2 * h + 1] *= alpha; }
-      }
-
-      // O += P V
-#pragma unroll
-      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-        unsigned a[4];
-        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-        for (int d2 = 0; d2 < D / 16; ++d2) {
-          unsigned b[4];
-          ldmatrix_x4_trans(b, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + d2 * 16 + 8 * (lane >> 4));
-          mma_bf16(o[2 * d2], a, b[0], b[1]);
-          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
-        }
-      }
-      }  // warp_active
-      __syncthreads();   // the stage is overwritten by the load after next
-    }
-  }
-
-  // Epilogue: normalise and store (or leave a partial result for the combine kernel).
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float sum = row_sum[h];
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (!row_valid[h]) continue;
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    const size_t token = (size_t)q0 + row_token[h];
-    if (p.num_splits == 1) {
-      __nv_bfloat16* dst = p.out + (token * p.nq + row_head[h]) * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i)
-        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * tq) = __floats2bfloat162_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-    } else {
-      const size_t slot = ((size_t)split * p.total_tokens + token) * p.nq + row_head[h];
-      float* dst = p.partial_out + slot * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i)
-        *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-      if (tq == 0) p.partial_lse[slot] = sum > 0.f ? row_max[h] * p.scale_log2 + log2f(sum) : -INFINITY;
-    }
-  }
-}
-
-
-// -----------------------------------------------------------------------------------------
-// Decode form: rows with at most 16 packed query rows (one decoded token times the group, or
-// a few tokens).  All four warps share the one 16-row query tile and split every 64-key tile
-// between them (16 keys each), each with its own running softmax; the four partial results
-// are merged through shared memory at the end.  Key/value tiles run through a three-stage
-// cp.async pipeline.  When the page size is a multiple of 64 a tile is one contiguous run of
-// a page and is addressed with one table look-up; otherwise keys are gathered one by one.
-// -----------------------------------------------------------------------------------------
-constexpr int DEC_STAGES = 3;
-constexpr int DEC_STAGE_ELEMS = 2 * TILE_ELEMS;   // keys then values
-constexpr size_t DEC_SMEM = (size_t)(SMALL_ROWS * LD + DEC_STAGES * DEC_STAGE_ELEMS) * sizeof(__nv_bfloat16);
-static_assert(DEC_STAGES * DEC_STAGE_ELEMS * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
-
+// One contiguous run of a page holds the whole tile when the page size is a multiple of 64:
+// one table look-up, then plain 16-byte copies.
 __device__ __forceinline__ void load_kv_tile_contiguous(__nv_bfloat16* dst, const __nv_bfloat16* pages, const int* table,
                                                         int tile, int kv_len, int kv_head, const AttentionParams& p) {
   const int key0 = tile * BLOCK_N;
@@ -307,6 +111,256 @@ __device__ __forceinline__ void load_kv_tile_contiguous(__nv_bfloat16* dst, cons
     cp_async_16(dst + r * LD + col * 8, valid ? base + (size_t)c * 8 : pages, valid);
   }
 }
+
+// Tiled form for prompt portions.  MT = 16-row MMA tiles per warp: a block takes 64 * MT
+// packed query rows, so each key/value fragment read from shared memory serves MT tiles.
+template <int MT>
+__global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const AttentionParams p) {
+  constexpr int BM = 64 * MT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BM][LD]
+  __nv_bfloat16* k_tiles = q_tile + BM * LD;                              // [2][64][LD]
+  __nv_bfloat16* v_tiles = k_tiles + 2 * TILE_ELEMS;                      // [2][64][LD]
+
+  const int row = blockIdx.z, kv_head = blockIdx.y;
+  const int q0 = p.q_start[row];
+  const int q_len = p.q_start[row + 1] - q0;
+  const int G = p.group;
+  const int packed_rows = q_len * G;
+  if (p.small_rows_elsewhere && packed_rows <= SMALL_ROWS) return;   // the decode kernel takes this row
+  // Later query tiles see more keys: hand them out first so the longest blocks start first.
+  const int q_tiles_here = (packed_rows + BM - 1) / BM;
+  const int q_tile_slot = blockIdx.x / p.num_splits, split = blockIdx.x % p.num_splits;
+  if (q_tile_slot >= q_tiles_here) return;
+  const int m0 = (q_tiles_here - 1 - q_tile_slot) * BM;
+  const int kv_len = p.kv_len[row];
+  const int pos0 = kv_len - q_len;   // position of the row's first new token
+  const int* table = p.block_table + (size_t)row * p.table_width;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int token_first = m0 / G;
+  const int last_packed = min(packed_rows, m0 + BM) - 1;
+  const int token_last = last_packed / G;
+  const int hi = pos0 + token_last;                                                   // last visible key (inclusive)
+  const int lo = p.window > 0 ? max(0, pos0 + token_first - p.window + 1) : 0;        // first visible key
+  const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
+  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int tile_end = min(first_tile + tiles, tile_begin + per_split);
+  const bool contiguous = p.page_size % BLOCK_N == 0;
+
+  // This thread's rows: two per MMA tile.  Packed index, token position, validity.
+  int row_pos[MT][2], row_token[MT][2], row_head[MT][2];
+  bool row_valid[MT][2];
+  int warp_min_pos = 0x7fffffff;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = m0 + (warp * MT + mt) * 16 + g + 8 * h;
+      row_valid[mt][h] = m < packed_rows;
+      row_token[mt][h] = row_valid[mt][h] ? m / G : 0;
+      row_head[mt][h] = kv_head * G + (row_valid[mt][h] ? m % G : 0);
+      row_pos[mt][h] = pos0 + row_token[mt][h];
+    }
+  }
+  // Smallest position among the warp's rows (rows past the end count as the first row): tiles
+  // wholly at or below it need no mask.
+  {
+    const int m_first = m0 + warp * MT * 16;
+    warp_min_pos = pos0 + (m_first < packed_rows ? m_first / G : 0);
+  }
+  const bool warp_full = m0 + (warp * MT + MT) * 16 <= packed_rows;   // all rows of the warp exist
+  const bool warp_active = m0 + warp * MT * 16 < packed_rows;
+
+  float o[MT][D / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f; }
+  float row_max[MT][2], row_sum[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) { row_max[mt][0] = row_max[mt][1] = -INFINITY; row_sum[mt][0] = row_sum[mt][1] = 0.f; }
+
+  auto load_tile = [&](int stage, int tile) {
+    if (contiguous) {
+      load_kv_tile_contiguous(k_tiles + stage * TILE_ELEMS, p.k_pages, table, tile, kv_len, kv_head, p);
+      load_kv_tile_contiguous(v_tiles + stage * TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
+    } else {
+      load_kv_tile(k_tiles + stage * TILE_ELEMS, p.k_pages, table, tile, kv_len, kv_head, p);
+      load_kv_tile(v_tiles + stage * TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
+    }
+  };
+
+  if (tile_begin < tile_end) {
+    // Query tile: packed rows m0 .. m0+BM-1, zero-filled past the end.
+    for (int c = threadIdx.x; c < BM * CHUNKS; c += ATT_THREADS) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const int m = m0 + r;
+      const bool valid = m < packed_rows;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + (size_t)(q0 + m / G) * p.q_stride + (size_t)(kv_head * G + m % G) * D + col * 8;
+      cp_async_16(q_tile + r * LD + col * 8, src, valid);
+    }
+    load_tile(0, tile_begin);
+    cp_async_commit();
+
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+      const int stage = (tile - tile_begin) & 1;
+      if (tile + 1 < tile_end) {
+        load_tile(stage ^ 1, tile + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const __nv_bfloat16* ks = k_tiles + stage * TILE_ELEMS;
+      const __nv_bfloat16* vs = v_tiles + stage * TILE_ELEMS;
+      if (warp_active) {
+        // S = Q K^T for this warp's 16 * MT rows and the tile's 64 keys.
+        float s[MT][BLOCK_N / 8][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int i = 0; i < BLOCK_N / 8; ++i) { s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          unsigned a[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            ldmatrix_x4(a[mt], q_tile + ((warp * MT + mt) * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+          for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
+            unsigned b[4];
+            ldmatrix_x4(b, ks + (n2 * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16(s[mt][2 * n2], a[mt], b[0], b[1]);
+              mma_bf16(s[mt][2 * n2 + 1], a[mt], b[2], b[3]);
+            }
+          }
+        }
+
+        // Mask: key visible iff key <= position (and > position - window) and the row exists.
+        // A tile wholly at or below every row's position (and inside every window) needs none.
+        const int tile_last_key = tile * BLOCK_N + BLOCK_N - 1;
+        const bool no_mask = warp_full && tile_last_key <= warp_min_pos && p.window == 0;
+        if (!no_mask) {
+          const int key_base = tile * BLOCK_N + 2 * tq;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int n = 0; n < BLOCK_N / 8; ++n) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int h = i >> 1;
+                const int key = key_base + n * 8 + (i & 1);
+                bool visible = row_valid[mt][h] && key <= row_pos[mt][h];
+                if (p.window > 0) visible = visible && key > row_pos[mt][h] - p.window;
+                if (!visible) s[mt][n][i] = -INFINITY;
+              }
+            }
+          }
+        }
+
+        // Online softmax in float32 (base 2).
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < BLOCK_N / 8; ++n) mx = fmaxf(mx, fmaxf(s[mt][n][2 * h], s[mt][n][2 * h + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float new_max = fmaxf(row_max[mt][h], mx);
+            const float use_max = new_max == -INFINITY ? 0.f : new_max;
+            const float alpha = exp2f((row_max[mt][h] - use_max) * p.scale_log2);   // exp2(-inf) = 0 on the first tile
+            const float shift = use_max * p.scale_log2;
+            float sum = 0.f;
+#pragma unroll
+            for (int n = 0; n < BLOCK_N / 8; ++n) {
+              const float p0 = exp2f(s[mt][n][2 * h] * p.scale_log2 - shift);
+              const float p1 = exp2f(s[mt][n][2 * h + 1] * p.scale_log2 - shift);
+              s[mt][n][2 * h] = p0;
+              s[mt][n][2 * h + 1] = p1;
+              sum += p0 + p1;
+            }
+            row_sum[mt][h] = row_sum[mt][h] * alpha + sum;
+            row_max[mt][h] = new_max;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) { o[mt][i][2 * h] *= alpha; o[mt][i][2 * h + 1] *= alpha; }
+          }
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+          unsigned a[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+            a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+            a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+            a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+          }
+#pragma unroll
+          for (int d2 = 0; d2 < D / 16; ++d2) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + d2 * 16 + 8 * (lane >> 4));
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16(o[mt][2 * d2], a[mt], b[0], b[1]);
+              mma_bf16(o[mt][2 * d2 + 1], a[mt], b[2], b[3]);
+            }
+          }
+        }
+      }  // warp_active
+      __syncthreads();   // the stage is overwritten by the load after next
+    }
+  }
+
+  // Epilogue: normalise and store (or leave a partial result for the combine kernel).
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float sum = row_sum[mt][h];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (!row_valid[mt][h]) continue;
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      const size_t token = (size_t)q0 + row_token[mt][h];
+      if (p.num_splits == 1) {
+        __nv_bfloat16* dst = p.out + (token * p.nq + row_head[mt][h]) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * tq) = __floats2bfloat162_rn(o[mt][i][2 * h] * inv, o[mt][i][2 * h + 1] * inv);
+      } else {
+        const size_t slot = ((size_t)split * p.total_tokens + token) * p.nq + row_head[mt][h];
+        float* dst = p.partial_out + slot * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[mt][i][2 * h] * inv, o[mt][i][2 * h + 1] * inv);
+        if (tq == 0) p.partial_lse[slot] = sum > 0.f ? row_max[mt][h] * p.scale_log2 + log2f(sum) : -INFINITY;
+      }
+    }
+  }
+}
+
+// -----------------------------------------------------------------------------------------
+// Decode form: rows with at most 16 packed query rows (one decoded token times the group, or
+// a few tokens).  All four warps share the one 16-row query tile and split every 64-key tile
+// between them (16 keys each), each with its own running softmax; the four partial results
+// are merged through shared memory at the end.  Key/value tiles run through a three-stage
+// cp.async pipeline.  When the page size is a multiple of 64 a tile is one contiguous run of
+// a page and is addressed with one table look-up; otherwise keys are gathered one by one.
+// -----------------------------------------------------------------------------------------
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_STAGE_ELEMS = 2 * TILE_ELEMS;   // keys then values
+constexpr size_t DEC_SMEM = (size_t)(SMALL_ROWS * LD + DEC_STAGES * DEC_STAGE_ELEMS) * sizeof(__nv_bfloat16);
+static_assert(DEC_STAGES * DEC_STAGE_ELEMS * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
 
 __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(const AttentionParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -518,7 +572,9 @@ __global__ void combine_splits_kernel(const float* __restrict__ partial_out, con
   }
 }
 
-constexpr size_t ATT_SMEM = (size_t)(BLOCK_M * LD + 4 * TILE_ELEMS) * sizeof(__nv_bfloat16);
+constexpr size_t ATT_SMEM_1 = (size_t)(64 * LD + 4 * TILE_ELEMS) * sizeof(__nv_bfloat16);
+constexpr size_t ATT_SMEM_2 = (size_t)(128 * LD + 4 * TILE_ELEMS) * sizeof(__nv_bfloat16);
+constexpr bool WIDE_TILES = D <= 128;   // two MMA tiles per warp keep their accumulators in registers up to this head size
 
 }  // namespace pylon
 
@@ -553,7 +609,9 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   if (nkv > 65535 || num_rows > 65535) PYLON_REFUSE("paged_attention_mma: %d KV heads, %d rows", nkv, num_rows);
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM);
+    cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_1);
+    if (err == cudaSuccess && WIDE_TILES)
+      err = cudaFuncSetAttribute(paged_attention_mma_kernel<WIDE_TILES ? 2 : 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_2);
     if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
@@ -573,10 +631,16 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
   p.small_rows_elsewhere = maybe_small ? 1 : 0;
   if (any_large) {
-    const long long q_tiles = (packed_max + BLOCK_M - 1) / BLOCK_M;
+    // 128-row blocks when the rows are long enough to fill them and the accumulators fit.
+    const bool wide = WIDE_TILES && packed_max >= 256;
+    const int block_rows = wide ? 128 : 64;
+    const long long q_tiles = (packed_max + block_rows - 1) / block_rows;
     if (q_tiles * num_splits > 2147483647LL) PYLON_REFUSE("paged_attention_mma: too many query tiles");
     dim3 grid((unsigned)(q_tiles * num_splits), nkv, num_rows);
-    paged_attention_mma_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(p);
+    if (wide)
+      paged_attention_mma_kernel<WIDE_TILES ? 2 : 1><<<grid, ATT_THREADS, ATT_SMEM_2, stream>>>(p);
+    else
+      paged_attention_mma_kernel<1><<<grid, ATT_THREADS, ATT_SMEM_1, stream>>>(p);
   }
   if (maybe_small) {
     dim3 grid(num_splits, nkv, num_rows);

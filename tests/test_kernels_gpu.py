@@ -167,6 +167,9 @@ ATTENTION_CASES = [
     ([120, 260], [9, 1], 4, 1, 48, 16, None),             # head size 48, one KV head
     ([180, 75, 300], [40, 1, 1], 4, 2, 32, 16, 50),       # window
     ([90], [90], 3, 1, 80, 32, 17),
+    # rows long enough for the 128-row blocks, beside short ones
+    ([300, 40, 129], [300, 3, 1], 8, 2, 128, 256, None),
+    ([260], [260], 4, 1, 64, 16, 33),
     # decoded tokens only (the decode form of the kernel): contiguous pages, gathered pages, groups, windows
     ([300, 64, 65, 7, 1, 129], [1, 1, 1, 1, 1, 1], 8, 2, 128, 64, None),
     ([500, 70], [1, 1], 10, 2, 64, 128, None),
