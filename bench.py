@@ -155,12 +155,17 @@ def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng) ->
 
 
 def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
-    """The same decode through submit()/tick(): host tokens in, host tokens out."""
+    """The same decode through submit()/tick(): host tokens in, host tokens out.  Prompts are
+    sized so that every request is still decoding when the timed ticks end (requests finish
+    their prompts at different ticks), and the value counts the tokens the ticks returned."""
+    from pylon_b200.engine.step import StepLayout
     from pylon_b200.sampling import SamplingParams
 
     vocab = engine.spec.vocab_size
-    prompt_length = CONTEXT - (warmup + steps) - 1
-    params = SamplingParams(max_new_tokens=warmup + steps + 1, temperature=0.0, ignore_eos=True)
+    prompt_ticks = batch * -(-CONTEXT // PREFILL_TOKENS)          # ticks until the last prompt is in
+    new_tokens = warmup + steps + prompt_ticks + 8
+    prompt_length = CONTEXT - new_tokens
+    params = SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True)
     for _ in range(batch):
         engine.submit(rng.integers(0, vocab, size=prompt_length).tolist(), params)
     scheduler = engine.scheduler
@@ -169,22 +174,20 @@ def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
     for _ in range(warmup):
         engine.tick()
     torch.cuda.synchronize()
+    before = sum(len(r.output_ids) for r in scheduler.active)
     started = time.perf_counter()
-    produced = 0
+    finished = []
     for _ in range(steps):
-        before = sum(len(r.output_ids) for r in scheduler.active)
-        finished = engine.tick()
-        produced += sum(len(r.output_ids) for r in scheduler.active) + sum(len(f.output_ids) for f in finished) - before
+        finished += engine.tick()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - started
+    produced = sum(len(r.output_ids) for r in scheduler.active) + sum(len(f.output_ids) for f in finished) - before
+    assert not finished and produced == batch * steps, (len(finished), produced)
     while scheduler.has_work():
         engine.tick()
     # per step: the packed int32 metadata buffer goes up, one int32 token per request comes back
-    from pylon_b200.engine.step import StepLayout
-
     layout = StepLayout(tokens=batch, rows=batch, logits=batch, table_widths=(CONTEXT // PAGE_SIZE,))
-    return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4,
-            "d2h_bytes_per_step": batch * 4, "produced": produced}
+    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4, "d2h_bytes_per_step": batch * 4}
 
 
 def time_prefill(engine, torch, repeats: int, rng) -> dict:
@@ -292,7 +295,7 @@ def main() -> int:
             "peaks": peak["source"], "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
         },
         "clocks": clocks,
-        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items() if k != "produced"},
+        "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": decode["launches"],
         "prefill": {"value": round(PREFILL_TOKENS / (prefill["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
                     "frac": round(flops / (prefill["ms"] / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},

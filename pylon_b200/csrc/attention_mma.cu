@@ -44,6 +44,7 @@ struct AttentionParams {
   const int* block_table;
   int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens;
   int small_rows_elsewhere;   // rows of at most SMALL_ROWS packed query rows are left to the decode kernel
+  unsigned* counters;         // [rows * nkv], zero between launches: lets the last split of a decode row combine the splits itself
   float scale_log2;     // softmax scale * log2(e)
 };
 
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
 // cp.async pipeline.  When the page size is a multiple of 64 a tile is one contiguous run of
 // a page and is addressed with one table look-up; otherwise keys are gathered one by one.
 // -----------------------------------------------------------------------------------------
-constexpr int DEC_STAGES = 3;
+constexpr int DEC_STAGES = 2;   // two stages leave room for three blocks per SM: warps in flight matter more than depth
 constexpr int DEC_STAGE_ELEMS = 2 * TILE_ELEMS;   // keys then values
 constexpr size_t DEC_SMEM = (size_t)(SMALL_ROWS * LD + DEC_STAGES * DEC_STAGE_ELEMS) * sizeof(__nv_bfloat16);
 static_assert(DEC_STAGES * DEC_STAGE_ELEMS * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
@@ -367,6 +368,8 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
   __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][LD]
   __nv_bfloat16* stages = q_tile + SMALL_ROWS * LD;                      // [DEC_STAGES][2][64][LD]
 
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
   const int q0 = p.q_start[row];
   const int q_len = p.q_start[row + 1] - q0;
@@ -432,15 +435,26 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       const __nv_bfloat16* ks = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS + warp * 16 * LD;
       const __nv_bfloat16* vs = ks + TILE_ELEMS;
 
+      // Even and odd k-steps accumulate separately: four independent MMA chains instead of two.
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         unsigned a[4], b[4];
         ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
         ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
-        mma_bf16(s[0], a, b[0], b[1]);
-        mma_bf16(s[1], a, b[2], b[3]);
+        if (kk & 1) {
+          mma_bf16(s_odd[0], a, b[0], b[1]);
+          mma_bf16(s_odd[1], a, b[2], b[3]);
+        } else {
+          mma_bf16(s[0], a, b[0], b[1]);
+          mma_bf16(s[1], a, b[2], b[3]);
+        }
       }
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] += s_odd[n][i];
       const int key_base = tile * BLOCK_N + warp * 16 + 2 * tq;
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -537,12 +551,70 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       if (col == 0) p.partial_lse[slot] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;
     }
   }
+
+  if (p.num_splits > 1 && p.counters != nullptr) {
+    // The split that finishes last for this (row, KV head) combines all of them; the others
+    // have published their partial results (fence, then the counter).
+    __shared__ bool last_split;
+    __threadfence();
+    __syncthreads();
+    unsigned* counter = p.counters + (size_t)row * p.nkv + kv_head;
+    if (threadIdx.x == 0) last_split = atomicAdd(counter, 1u) == (unsigned)p.num_splits - 1u;
+    __syncthreads();
+    if (!last_split) return;
+    __threadfence();
+    const size_t items = (size_t)p.total_tokens * p.nq;
+    // The splits' weights first (one trip to L2 for all of them), then the weighted sum with
+    // several partial results in flight per thread.
+    float* weights = reinterpret_cast<float*>(stages);   // [SMALL_ROWS][splits]; the stages are idle now
+    __shared__ float row_total[SMALL_ROWS];
+    const int splits = p.num_splits;
+    __syncthreads();
+    for (int e = threadIdx.x; e < packed_rows * splits; e += ATT_THREADS) {
+      const int r = e / splits, s2 = e % splits;
+      const size_t item = ((size_t)q0 + r / G) * p.nq + kv_head * G + r % G;
+      weights[r * splits + s2] = __ldcg(p.partial_lse + (size_t)s2 * items + item);
+    }
+    __syncthreads();
+    if (threadIdx.x < packed_rows) {
+      const int r = threadIdx.x;
+      float mx = -INFINITY;
+      for (int s2 = 0; s2 < splits; ++s2) mx = fmaxf(mx, weights[r * splits + s2]);
+      float total = 0.f;
+      for (int s2 = 0; s2 < splits; ++s2) {
+        const float lse = weights[r * splits + s2];
+        const float weight = lse == -INFINITY ? 0.f : exp2f(lse - mx);
+        weights[r * splits + s2] = weight;
+        total += weight;
+      }
+      row_total[r] = total;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
+      const int r = e / D, col = e % D;
+      const size_t item = ((size_t)q0 + r / G) * p.nq + kv_head * G + r % G;
+      const float* src = p.partial_out + item * D + col;
+      float value = 0.f;
+      int s2 = 0;
+      for (; s2 + 4 <= splits; s2 += 4) {
+        const float v0 = __ldcg(src + (size_t)(s2 + 0) * items * D), v1 = __ldcg(src + (size_t)(s2 + 1) * items * D);
+        const float v2 = __ldcg(src + (size_t)(s2 + 2) * items * D), v3 = __ldcg(src + (size_t)(s2 + 3) * items * D);
+        value += weights[r * splits + s2] * v0 + weights[r * splits + s2 + 1] * v1 + weights[r * splits + s2 + 2] * v2 + weights[r * splits + s2 + 3] * v3;
+      }
+      for (; s2 < splits; ++s2) value += weights[r * splits + s2] * __ldcg(src + (size_t)s2 * items * D);
+      const float total = row_total[r];
+      p.out[item * D + col] = __float2bfloat16_rn(total > 0.f ? value / total : 0.f);
+    }
+    if (threadIdx.x == 0) *counter = 0u;   // ready for the next launch
+  }
 }
 
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
 // warp per (token, head).
 __global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
                                       __nv_bfloat16* __restrict__ out, int num_splits, long long items) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= items) return;
   const int lane = threadIdx.x & 31;
@@ -591,9 +663,12 @@ extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_to
 // q: bfloat16 [tokens, >= nq*D] with q_stride elements between tokens; pages: bfloat16
 // [num_pages, nkv, page_size, D]; out: bfloat16 [tokens, nq, D]; q_start: int32 [rows + 1];
 // kv_len: int32 [rows]; block_table: int32 [rows, table_width]; max_q: the longest row (or an
-// upper bound); scratch: float32, pylon_attention_scratch_floats() long when num_splits > 1.
+// upper bound); scratch: float32, pylon_attention_scratch_floats() long when num_splits > 1;
+// counters: null, or num_rows * nkv unsigned integers that are zero before the call (and zero
+// again after it): with them the splits of decoded rows are combined inside the attention
+// kernel instead of by a second launch.
 extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
-                                         void* out, float* scratch, const int* q_start, const int* kv_len,
+                                         void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
                                          const int* block_table, int table_width, int page_size, int num_pages,
                                          int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
                                          int max_q, int num_splits, cudaStream_t stream) {
@@ -622,6 +697,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.out = (__nv_bfloat16*)out;
   const long long items = (long long)total_tokens * nq;
   p.partial_out = scratch; p.partial_lse = scratch ? scratch + (size_t)num_splits * items * D : nullptr;
+  p.counters = counters;
   p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
   p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
@@ -644,11 +720,12 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   }
   if (maybe_small) {
     dim3 grid(num_splits, nkv, num_rows);
-    paged_attention_decode_kernel<<<grid, ATT_THREADS, DEC_SMEM, stream>>>(p);
+    launch_dependent(paged_attention_decode_kernel, grid, dim3(ATT_THREADS), DEC_SMEM, stream, p);
   }
-  if (num_splits > 1) {
+  if (num_splits > 1 && (any_large || counters == nullptr)) {
     const int warps = 4;
-    combine_splits_kernel<<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(p.partial_out, p.partial_lse, p.out, num_splits, items);
+    launch_dependent(combine_splits_kernel, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
+                     (const float*)p.partial_out, (const float*)p.partial_lse, p.out, num_splits, items);
   }
   PYLON_CHECK_LAUNCH("paged_attention_mma");
 }

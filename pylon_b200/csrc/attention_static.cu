@@ -75,6 +75,6 @@ extern "C" int pylon_paged_attention_mma_static(const void* q, long long q_strid
                  num_splits, total_tokens, nq, needed, PYLON_STATIC_SCRATCH_FLOATS);
   float* scratch = static_scratch_address();
   if (scratch == nullptr) return -2;
-  return pylon_paged_attention_mma(q, q_stride, k_pages, v_pages, out, scratch, q_start, kv_len, block_table, table_width,
+  return pylon_paged_attention_mma(q, q_stride, k_pages, v_pages, out, scratch, nullptr, q_start, kv_len, block_table, table_width,
                                    page_size, num_pages, nq, nkv, window, scale, num_rows, total_tokens, max_q, num_splits, stream);
 }

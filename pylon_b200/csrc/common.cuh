@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define PYLON_DTYPE_F32 0
 #define PYLON_DTYPE_BF16 1
@@ -98,6 +99,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// Programmatic dependent launch: a kernel launched with launch_dependent() may start while
+// the kernel before it in the stream is still running.  It must call grid_dependency_wait()
+// before it reads anything that kernel writes (and before it writes anything that kernel
+// reads); what it does before that - index arithmetic, loads of weights - overlaps the
+// predecessor's tail.  allow_dependents() lets the next kernel in the stream start early in
+// the same way.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+// Off unless PYLON_B200_PDL=1 is in the environment: measured on the decode step of the
+// Qwen3-4B shape it changed nothing (3.96 ms with, 3.89 ms without), so the ordinary launch
+// stays the default.
+inline bool dependent_launch_enabled() {
+  static const bool enabled = [] {
+    const char* value = getenv("PYLON_B200_PDL");
+    return value && value[0] == '1';
+  }();
+  return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
 }  // namespace pylon

@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __
                                                                        const float* __restrict__ weight, const int* __restrict__ rows,
                                                                        T* __restrict__ out, int width, float eps, int write_residual) {
   __shared__ float scratch[33];
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* res = residual + (size_t)row * width;
@@ -135,7 +137,7 @@ static bool launch_add_rmsnorm_vec(float* residual, const T* delta, const float*
   const int items = (width / 4 + NORM_THREADS - 1) / NORM_THREADS;
 #define PYLON_NORM_CASE(N)                                                                                     \
   case N:                                                                                                      \
-    add_rmsnorm_vec_kernel<T, N><<<n_rows, NORM_THREADS, 0, stream>>>(residual, delta, weight, rows, out, width, eps, write_residual); \
+    launch_dependent(add_rmsnorm_vec_kernel<T, N>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, residual, delta, weight, rows, out, width, eps, write_residual); \
     return true;
   switch (items) {
     PYLON_NORM_CASE(1) PYLON_NORM_CASE(2) PYLON_NORM_CASE(3) PYLON_NORM_CASE(4)
@@ -168,6 +170,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
     int d, int num_tokens) {
   extern __shared__ float exchange[];  // [warps per block][d]
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -244,15 +248,19 @@ __global__ void qk_norm_rope_kv_write_kernel(
 // -----------------------------------------------------------------------------------------
 // SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
 // -----------------------------------------------------------------------------------------
+// `interleaved`: gate and up columns alternate in groups of 8 ([g0..g7 u0..u7 g8..g15 ...])
+// instead of lying in two halves.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int interleaved) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
     const size_t t = i / inter;
     const int c = (int)(i - t * inter);
-    const float g = to_float<T>(gate_up[t * 2 * inter + c]);
-    const float u = to_float<T>(gate_up[t * 2 * inter + inter + c]);
+    const int gate_column = interleaved ? (c >> 3) * 16 + (c & 7) : c;
+    const int up_column = interleaved ? gate_column + 8 : inter + c;
+    const float g = to_float<T>(gate_up[t * 2 * inter + gate_column]);
+    const float u = to_float<T>(gate_up[t * 2 * inter + up_column]);
     // float storage is the true 32-bit path: full-precision exponential there
     const float e = sizeof(T) == 4 ? expf(-g) : __expf(-g);
     out[i] = from_float<T>(g / (1.f + e) * u);
@@ -261,14 +269,16 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 // Vector form for bfloat16 rows whose width is a multiple of 8 (16-byte accesses).
 __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int inter8,
-                                     size_t total8) {
+                                     size_t total8, int interleaved) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total8; i += stride) {
     const size_t t = i / inter8;
     const int c = (int)(i - t * inter8);
-    uint4 g4 = gate_up[t * 2 * inter8 + c];
-    uint4 u4 = gate_up[t * 2 * inter8 + inter8 + c];
+    uint4 g4 = gate_up[t * 2 * inter8 + (interleaved ? 2 * c : c)];
+    uint4 u4 = gate_up[t * 2 * inter8 + (interleaved ? 2 * c + 1 : inter8 + c)];
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
     uint4 o4;
@@ -344,7 +354,7 @@ static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float e
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
 #define PYLON_LAUNCH_QK(N)                                                                              \
-  qk_norm_rope_kv_write_kernel<T, N><<<blocks, warps * 32, smem, stream>>>(                             \
+  launch_dependent(qk_norm_rope_kv_write_kernel<T, N>, dim3(blocks), dim3(warps * 32), smem, stream,    \
       qkv, qw, kw, eps, cos_t, sin_t, rotary_dim, table_positions, positions, token_row, block_table,   \
       table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, num_tokens)
   if (d <= 32) PYLON_LAUNCH_QK(1);
@@ -380,19 +390,20 @@ extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, con
   PYLON_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
 }
 
-extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int dtype,
+extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int interleaved, int dtype,
                             cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (inter <= 0) PYLON_REFUSE("swiglu: intermediate size %d", inter);
+  if (interleaved && inter % 8) PYLON_REFUSE("swiglu: the interleaved layout needs an intermediate size that is a multiple of 8, not %d", inter);
   const size_t total = (size_t)num_tokens * inter;
   const int threads = 256;
   auto grid = [&](size_t n) { size_t b = (n + threads - 1) / threads; return (int)(b < 148 * 32 ? b : 148 * 32); };
   if (dtype == PYLON_DTYPE_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
-    swiglu_bf16x8_kernel<<<grid(total / 8), threads, 0, stream>>>((const uint4*)gate_up, (uint4*)out, inter / 8, total / 8);
+    launch_dependent(swiglu_bf16x8_kernel, dim3(grid(total / 8)), dim3(threads), 0, stream, (const uint4*)gate_up, (uint4*)out, inter / 8, total / 8, interleaved);
   } else if (dtype == PYLON_DTYPE_BF16) {
-    swiglu_kernel<__nv_bfloat16><<<grid(total), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    swiglu_kernel<__nv_bfloat16><<<grid(total), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total, interleaved);
   } else if (dtype == PYLON_DTYPE_F32) {
-    swiglu_kernel<float><<<grid(total), threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    swiglu_kernel<float><<<grid(total), threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, interleaved);
   } else {
     PYLON_REFUSE("swiglu: unknown dtype %d", dtype);
   }

@@ -129,6 +129,26 @@ class Engine:
     def close(self, request: RequestCache) -> None:
         self.cache.close(request)
 
+    def capture_decode_graphs(self, batch_sizes: Optional[Sequence[int]] = None) -> list[int]:
+        """Captures the decode graphs of the given batch sizes (default: every size up to
+        ``max_batch_size``) now instead of at their first use, as raun6k/Pylon does at start-up
+        (src/pylon/engine.py:823-836).  Needs ``cuda_graphs``; returns the sizes that have a graph."""
+        if self.step_function.graphs is None:
+            raise RuntimeError("cuda_graphs is off")
+        sizes = list(batch_sizes) if batch_sizes is not None else list(range(1, self.config.max_batch_size + 1))
+        with torch.cuda.device(self.device):
+            for size in sizes:
+                if size in self.step_function.graphs.captured or size > min(self.cache.free_slots(), min(self.cache.free_pages(), default=size)):
+                    continue
+                requests = [self.cache.open(("capture", size, i), 1) for i in range(size)]
+                try:
+                    self.step_function([StepEntry(request, [0], (0,)) for request in requests])
+                finally:
+                    for request in requests:
+                        self.cache.close(request)
+            torch.cuda.synchronize(self.device)
+        return sorted(self.step_function.graphs.captured)
+
     # -- generation --------------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, request_id: Optional[object] = None) -> object:
         """Queues one request (raun6k/Pylon's ``Engine.enqueue``, src/pylon/engine.py:241-253);

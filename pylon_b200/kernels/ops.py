@@ -68,13 +68,14 @@ _SIGNATURES = {
         "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
     "gemm_skinny.cu": {
         "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
+        "pylon_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -82,7 +83,7 @@ _SIGNATURES = {
                                          c_int, c_int, c_void_p],
     },
     "attention_mma.cu": {
-        "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                       c_int, c_int, c_void_p],
         "pylon_attention_scratch_floats": [c_int, c_int, c_int],
@@ -216,8 +217,11 @@ def qk_norm_rope_kv_write(
         k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up = [gate | up]`` of shape ``[T, 2 * inter]``."""
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` of shape ``[T, 2 * inter]``: ``[gate | up]`` in two
+    halves, or with ``interleaved`` in alternating groups of 8 columns
+    (``[g0..g7 u0..u7 g8..g15 u8..u15 ...]``, the layout :func:`interleave_gate_up` gives the
+    weights)."""
     _need_cuda(gate_up, out)
     _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "swiglu: gate_up must be contiguous [T, 2 * inter]")
     tokens, inter = gate_up.shape[0], gate_up.shape[1] // 2
@@ -225,7 +229,7 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
         out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
     _need(out.shape == (tokens, inter) and out.dtype == gate_up.dtype and out.is_contiguous(), "swiglu: out has the wrong shape or dtype")
     library = _library("elementwise.cu")
-    _check(library, library.pylon_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, _dtype_code(gate_up.dtype), _stream()))
+    _check(library, library.pylon_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, int(interleaved), _dtype_code(gate_up.dtype), _stream()))
     return out
 
 
@@ -261,14 +265,68 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     _need(out_dtype in (torch.bfloat16, torch.float32), f"linear: unsupported result dtype {out_dtype}")
     if m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
-        # Few rows (decode): our weight-streaming kernel.
-        y = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        library = _library("gemm_skinny.cu")
-        _check(library, library.pylon_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), n, _dtype_code(out_dtype), _stream()))
-        return y
+        return linear_skinny(x, w, out_dtype)   # few rows (decode): our weight-streaming kernel
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The weight-streaming kernel itself: bfloat16 ``x [M <= 64, K] @ w [N, K].T`` with ``K``
+    and the row strides multiples of 8 and 16-byte aligned operands; anything else is refused."""
+    _need_cuda(x, w)
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1],
+          "linear_skinny: bfloat16 x [M, K] and w [N, K]")
+    _need(x.stride(1) == 1 and w.stride(1) == 1, "linear_skinny: the reduced dimension must be contiguous")
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    library = _library("gemm_skinny.cu")
+    _check(library, library.pylon_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), n, _dtype_code(out_dtype), _stream()))
+    return y
+
+
+FUSED_MAX_ROWS = 8   # up to this many rows the gate/up product applies SwiGLU itself
+
+# Small integer buffers kernels use to find out which of their blocks finishes last.  They
+# are zero between launches (a kernel leaves its counters as it found them) and launches on
+# one stream follow each other, so one buffer per device and purpose is enough.
+_counter_buffers: dict[tuple, torch.Tensor] = {}
+
+
+def _zeroed_counters(device: torch.device, purpose: str, count: int) -> torch.Tensor:
+    key = (str(device), purpose)
+    buffer = _counter_buffers.get(key)
+    if buffer is None or buffer.numel() < count:
+        buffer = torch.zeros(max(count, 1 << 16), dtype=torch.int32, device=device)
+        _counter_buffers[key] = buffer
+    return buffer
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stacks the ``[inter, K]`` gate and up matrices in alternating groups of 8 rows (8 gate
+    rows, their 8 up rows, ...), so that one block of 16 weight rows holds both halves of 8
+    outputs.  ``inter`` must be a multiple of 8."""
+    inter, k = gate.shape
+    _need(up.shape == gate.shape and inter % 8 == 0, "interleave_gate_up: equal shapes with a row count that is a multiple of 8")
+    return torch.stack((gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)), dim=1).reshape(2 * inter, k).contiguous()
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ gate.T) * (x @ up.T)`` for weights stacked by :func:`interleave_gate_up`:
+    one kernel for few rows, the product and the SwiGLU kernel otherwise."""
+    _need_cuda(x, w_interleaved)
+    n, k = w_interleaved.shape
+    m = x.shape[0]
+    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and x.dim() == 2 and m <= FUSED_MAX_ROWS and x.shape[1] == k
+            and k % 8 == 0 and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w_interleaved.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):
+        y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+        library = _library("gemm_skinny.cu")
+        _check(library, library.pylon_gemm_skinny_swiglu(_ptr(x), _ptr(w_interleaved), _ptr(y), m, n, k, x.stride(0), w_interleaved.stride(0),
+                                                         n // 2, _stream()))
+        return y
+    return swiglu(linear(x, w_interleaved), interleaved=True)
 
 
 # ---------------------------------------------------------------------------------------
@@ -290,6 +348,7 @@ def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: in
             return 1
         return int(max(1, min(kv_tiles, 64, slots // blocks)))
     blocks = num_rows * nkv
+    slots = 3 * _SM_COUNT      # the decode kernel fits three blocks on an SM
     best, best_cost = 1, None
     for splits in range(1, min(kv_tiles, 64) + 1):
         waves = -(-blocks * splits // slots)
@@ -357,8 +416,9 @@ def paged_attention(
         scratch = None
         if splits > 1:
             scratch = torch.empty((library.pylon_attention_scratch_floats(splits, tokens, nq),), dtype=torch.float32, device=q.device)
+        counters = _zeroed_counters(q.device, "attention", rows * nkv) if splits > 1 else None
         _check(library, library.pylon_paged_attention_mma(
-            _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(q_start), _ptr(kv_len),
+            _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(counters), _ptr(q_start), _ptr(kv_len),
             _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
             int(max_q), splits, _stream()))
         return out

@@ -162,11 +162,13 @@ class Mixer(Part):
         return CacheNeed()
 
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        """Returns the delta for the residual stream, ``[T, width]`` in the activation dtype."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
+        """Returns the delta for the residual stream, ``[T, width]`` in the activation dtype."""
         raise NotImplementedError
 
 

@@ -19,6 +19,7 @@ class SwiGLU(FeedForward):
         self.width, self.intermediate = int(width), int(intermediate)
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.w_gate_up = self.w_down = None
+        self.interleaved = False
 
     def tensors(self) -> Sequence[TensorDecl]:
         n = self.names
@@ -30,11 +31,21 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
         n = self.names
-        self.w_gate_up = torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous()
+        # gate and up share one product.  In bfloat16 their rows alternate in groups of 8, so that
+        # the product's kernel can apply silu(gate) * up itself; otherwise they lie in two halves.
+        self.interleaved = dtype == torch.bfloat16 and self.intermediate % 8 == 0
+        if self.interleaved:
+            self.w_gate_up = ops.interleave_gate_up(tensors[n["gate"]], tensors[n["up"]])
+        else:
+            self.w_gate_up = torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous()
         self.w_down = tensors[n["down"]].contiguous()
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
-        return ops.linear(ops.swiglu(ops.linear(h, self.w_gate_up)), self.w_down)
+        if self.interleaved:
+            activation = ops.linear_swiglu(h, self.w_gate_up)
+        else:
+            activation = ops.swiglu(ops.linear(h, self.w_gate_up))
+        return ops.linear(activation, self.w_down)

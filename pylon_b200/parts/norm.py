@@ -35,7 +35,5 @@ class RMSNorm(Norm):
 
     def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         delta, stream.pending = stream.pending, None
-        if rows is not None and delta is not None:
-            # A row selection leaves the residual untouched; the delta is added on the fly.
-            return ops.add_rmsnorm(stream.residual, delta, self.weight, self.eps, self.dtype, rows=rows)
+        # With a row selection the residual stays untouched and the delta is added on the fly.
         return ops.add_rmsnorm(stream.residual, delta, self.weight, self.eps, self.dtype, rows=rows)

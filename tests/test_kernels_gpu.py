@@ -104,6 +104,57 @@ def test_linear_bf16(m, n, k):
     torch.testing.assert_close(wide.double(), expected, rtol=1e-3, atol=1e-3)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("n, k", [(100, 64), (2560, 4096), (77, 1000), (333, 264)])
+def test_skinny_gemm_every_row_count(m, n, k):
+    """The weight-streaming kernel on its own, for every tile configuration it has, with row
+    and k counts that do not fill its tiles."""
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    expected = x.double() @ w.double().T
+    torch.testing.assert_close(ops.linear_skinny(x, w, torch.float32).double(), expected, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(ops.linear_skinny(x, w).double(), expected, rtol=2e-2, atol=2e-2)
+    # a strided view of a wider buffer works too (row stride a multiple of 8)
+    wide = torch.randn(m, k + 16, device=DEVICE).to(torch.bfloat16)
+    view = wide[:, 8 : 8 + k]
+    torch.testing.assert_close(ops.linear_skinny(view, w, torch.float32).double(), view.double() @ w.double().T, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("m", [1, 7, 8, 20])
+@pytest.mark.parametrize("inter, k", [(9728, 2560), (224, 96), (24, 64)])
+def test_linear_swiglu_with_interleaved_weights(m, inter, k):
+    """silu(x gate^T) * (x up^T) from weights stacked in alternating groups of 8 rows: fused in
+    the product's kernel for few rows, product plus SwiGLU kernel for more."""
+    from pylon_b200.kernels import ops
+
+    gate = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    up = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    stacked = ops.interleave_gate_up(gate, up)
+    assert torch.equal(stacked[:8], gate[:8]) and torch.equal(stacked[8:16], up[:8]) and torch.equal(stacked[16:24], gate[8:16])
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g * torch.sigmoid(g) * u
+    torch.testing.assert_close(ops.linear_swiglu(x, stacked).double(), want, rtol=2e-2, atol=2e-2)
+    # the SwiGLU kernel alone on interleaved columns, both dtypes
+    for dtype in (torch.bfloat16, torch.float32):
+        columns = torch.randn(m, 2 * inter, device=DEVICE).to(dtype)
+        pairs = columns.double().reshape(m, inter // 8, 2, 8)
+        g2, u2 = pairs[:, :, 0].reshape(m, inter), pairs[:, :, 1].reshape(m, inter)
+        torch.testing.assert_close(ops.swiglu(columns, interleaved=True).double(), g2 * torch.sigmoid(g2) * u2, **tolerance(dtype))
+
+
+def test_skinny_gemm_refuses():
+    from pylon_b200.kernels import ops
+
+    w = torch.zeros(16, 20, device=DEVICE, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.linear_skinny(torch.zeros(2, 20, device=DEVICE, dtype=torch.bfloat16), w)
+    with pytest.raises(ops.KernelError, match="64 rows"):
+        ops.linear_skinny(torch.zeros(65, 24, device=DEVICE, dtype=torch.bfloat16), torch.zeros(16, 24, device=DEVICE, dtype=torch.bfloat16))
+
+
 # ---------------------------------------------------------------------------------------
 # a small paged cache for the kernels below
 # ---------------------------------------------------------------------------------------
