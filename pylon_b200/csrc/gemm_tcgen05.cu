@@ -1,0 +1,336 @@
+// C[M, N] = A[M, K] * B[N, K]^T for bfloat16 on the fifth-generation tensor cores: operands
+// staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), multiplied by
+// tcgen05.mma issued from one thread, accumulated in float32 in tensor memory, read back with
+// tcgen05.ld for the epilogue.  For the products of prompt portions (many rows).
+//
+// One persistent block per SM walks 128 x BN output tiles.  Six warps with fixed roles:
+//   warp 0      TMA producer: fills a ring of STAGES shared-memory stages (A 128 x 64, B BN x 64)
+//   warp 1      MMA issuer: four tcgen05.mma (K = 16 each) per stage into one of two
+//               accumulator buffers in tensor memory; tcgen05.commit frees the stage and, after
+//               the last stage of a tile, hands the accumulator to the epilogue
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its quarter of the 128 lanes),
+//               convert and store; with SWIGLU the columns hold gate and up values in
+//               alternating groups of 8 and silu(gate) * up is stored, half as wide
+// so the epilogue of one tile overlaps the products of the next.  All waits on mbarriers are
+// bounded: a wait that runs out sets an error word for the host and the block winds down
+// (frees its tensor memory and returns) instead of hanging.
+//
+// No TMA load here uses cluster multicast.
+//
+// Stands in for the library product behind raun6k/Pylon's nn.Linear at prefill
+// (src/pylon/model/layers.py:26-27,126,138).
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace pylon {
+
+constexpr int TC_BM = 128, TC_BK = 64, TC_THREADS = 192;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;   // try_wait calls before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Waits for the phase with the given parity to complete; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate == 0 overwrites D.
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive float32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tc_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16)
+// in the 128-byte swizzle TMA wrote: start address, 1024 bytes between groups of 8 rows,
+// descriptor version 1, swizzle mode 128B.
+__device__ __forceinline__ uint64_t tc_smem_desc(const void* tile) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address, 16-byte units
+  desc |= (uint64_t)(1024 >> 4) << 32;                   // stride between 8-row groups
+  desc |= (uint64_t)1 << 46;                             // descriptor version (sm_100)
+  desc |= (uint64_t)2 << 61;                             // 128-byte swizzle
+  return desc;
+}
+
+// Instruction descriptor for kind::f16: bfloat16 A and B, float32 D, both K-major, M x N.
+__host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int BN>
+struct TcShared {
+  static constexpr int STAGES = BN == 256 ? 4 : (BN >= 160 ? 5 : 6);
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// error: 0 = fine; otherwise 1 producer, 2 MMA issuer, 3 epilogue gave up waiting.
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                      const __grid_constant__ CUtensorMap map_b,
+                                                                      __nv_bfloat16* __restrict__ c, int M, int N, int K,
+                                                                      long long ldc, int* __restrict__ error) {
+  using S = TcShared<BN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* a_tiles = smem;
+  unsigned char* b_tiles = smem + (size_t)STAGES * S::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * S::B_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;      // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  constexpr int TMEM_COLUMNS = 2 * BN <= 256 ? 256 : 512;   // both accumulator buffers; allocations are powers of two
+  if (warp == 1) {   // the whole warp allocates
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLUMNS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;   // neighbours in the grid share their B tile
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); alive = false; break; }
+          mbar_expect_tx(&full[stage], S::A_BYTES + S::B_BYTES);
+          tma_load_2d(a_tiles + (size_t)stage * S::A_BYTES, &map_a, &full[stage], kb * TC_BK, m0);
+          tma_load_2d(b_tiles + (size_t)stage * S::B_BYTES, &map_b, &full[stage], kb * TC_BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
+      uint32_t stage = 0, phase = 0;
+      uint32_t round = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++round) {
+        const uint32_t buffer = round & 1, buffer_phase = (round >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buffer], buffer_phase ^ 1)) { atomicExch(error, 2); break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buffer * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) { atomicExch(error, 2); alive = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = tc_smem_desc(a_tiles + (size_t)stage * S::A_BYTES);
+          const uint64_t b_desc = tc_smem_desc(b_tiles + (size_t)stage * S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)   // 16 k-values = 32 bytes further along the swizzled row: +2 in 16-byte units
+            tc_mma(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(&empty[stage]);   // the stage is free once these products have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (alive) tc_commit(&acc_full[buffer]);   // the accumulator is complete once all products are
+      }
+    }
+  } else {
+    // Epilogue: warp w reads the quarter (w % 4) of the 128 lanes; lane = output row.
+    const int quarter = warp & 3;
+    uint32_t round = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
+      const uint32_t buffer = round & 1, buffer_phase = (round >> 1) & 1;
+      if (!mbar_wait(&acc_full[buffer], buffer_phase)) { atomicExch(error, 3); break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t raw[32];
+        tc_load_32(taddr + c0, raw);
+        const int col = n0 + c0;
+        if (row < M && col < N) {
+          if (SWIGLU) {
+            // [g0..g7 u0..u7 g8..g15 u8..u15] -> 16 outputs at column col / 2
+            uint32_t packed[8];
+#pragma unroll
+            for (int group = 0; group < 2; ++group)
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const float g0 = __uint_as_float(raw[group * 16 + j]), g1 = __uint_as_float(raw[group * 16 + j + 1]);
+                const float u0 = __uint_as_float(raw[group * 16 + 8 + j]), u1 = __uint_as_float(raw[group * 16 + 8 + j + 1]);
+                packed[group * 4 + j / 2] = pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              }
+            __nv_bfloat16* dst = c + (size_t)row * ldc + col / 2;
+            if (col + 32 <= N) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {   // N is a multiple of 16: only the first group is inside
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+          } else {
+            __nv_bfloat16* dst = c + (size_t)row * ldc + col;
+            if (col + 32 <= N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(
+                    pack2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), pack2(__uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3])),
+                    pack2(__uint_as_float(raw[j + 4]), __uint_as_float(raw[j + 5])), pack2(__uint_as_float(raw[j + 6]), __uint_as_float(raw[j + 7])));
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(raw[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buffer]);   // four warps: the buffer may be overwritten
+    }
+  }
+
+  // Wind down: every role comes here, also after a wait that ran out.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLUMNS));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) != cudaSuccess || result != cudaDriverEntryPointSuccess)
+      symbol = nullptr;
+    return (EncodeTiled)symbol;
+  }();
+  return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (row stride ld elements) with boxes of box_rows x 64 columns.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (!encode) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWIGLU>
+static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __nv_bfloat16* c, int M, int N, int K, long long ldc,
+                          int* error, int sm_count, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<BN, SWIGLU>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShared<BN>::BYTES);
+    if (err != cudaSuccess) PYLON_REFUSE("gemm_tcgen05: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+  const int blocks = tiles < sm_count ? tiles : sm_count;
+  kernel<<<blocks, TC_THREADS, TcShared<BN>::BYTES, stream>>>(map_a, map_b, c, M, N, K, ldc, error);
+  PYLON_CHECK_LAUNCH("gemm_tcgen05");
+}
+
+}  // namespace pylon
+
+// x: bfloat16 [M, K] (row stride ldx), w: bfloat16 [N, K] (row stride ldw), y: bfloat16 [M, N], or [M, N / 2] with swiglu
+// (row stride ldy).  K and the strides multiples of 8, N a multiple of 8 (16 with swiglu), x, w and y 16-byte aligned.
+// swiglu != 0: w's rows alternate in groups of 8 between gate and up rows and y receives silu(gate) * up.
+// error: one int in device memory; the kernel sets it non-zero if one of its waits ran out (the result is then void).
+extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                       long long ldy, int swiglu, int* error, int sm_count, cudaStream_t stream) {
+  using namespace pylon;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldy % 8) PYLON_REFUSE("gemm_tcgen05: K = %d and the row strides must be multiples of 8", K);
+  if (N % (swiglu ? 16 : 8)) PYLON_REFUSE("gemm_tcgen05: N = %d must be a multiple of %d", N, swiglu ? 16 : 8);
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 16)) PYLON_REFUSE("gemm_tcgen05: x, w and y must be 16-byte aligned");
+  if (ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N)) PYLON_REFUSE("gemm_tcgen05: a row stride is shorter than its row");
+  if (!error || sm_count < 1) PYLON_REFUSE("gemm_tcgen05: an error word and the SM count are needed");
+  // Tile width: the one whose rounds over the SMs cover the fewest columns (a persistent block
+  // takes ceil(tiles / SMs) tiles; the last round is often nearly empty with wide tiles).
+  const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+  int bn = 128;
+  long long best = -1;
+  for (int candidate : {256, 192, 160, 128}) {
+    const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
+    const long long cost = ((tiles + sm_count - 1) / sm_count) * (candidate + 16);   // + a per-tile overhead
+    if (best < 0 || cost < best) { best = cost; bn = candidate; }
+  }
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, N, K, ldw, bn))
+    PYLON_REFUSE("gemm_tcgen05: the tensor maps could not be made");
+  __nv_bfloat16* out = (__nv_bfloat16*)y;
+#define PYLON_TC_CASE(BN_)                                                                                          \
+  if (bn == BN_) {                                                                                                  \
+    if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);         \
+    return launch_tcgen05<BN_, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);                    \
+  }
+  PYLON_TC_CASE(256) PYLON_TC_CASE(192) PYLON_TC_CASE(160)
+#undef PYLON_TC_CASE
+  if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+  return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+}

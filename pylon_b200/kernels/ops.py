@@ -77,6 +77,10 @@ _SIGNATURES = {
         "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
         "pylon_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
+    "gemm_tcgen05.cu": {
+        "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                                    c_void_p, c_int, c_void_p],
+    },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -287,6 +291,35 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = tor
 
 
 FUSED_MAX_ROWS = 8   # up to this many rows the gate/up product applies SwiGLU itself
+TCGEN05_MIN_ROWS = 128   # from this many rows the gate/up product runs on our tcgen05 kernel, SwiGLU in its epilogue
+
+_tcgen05_error: dict[str, torch.Tensor] = {}
+
+
+def tcgen05_error_word(device: torch.device) -> torch.Tensor:
+    """The int32 word the tcgen05 kernels set when one of their bounded waits ran out
+    (0 = never).  Reading it synchronises; tests and the benchmark look at it."""
+    key = str(device)
+    if key not in _tcgen05_error:
+        _tcgen05_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tcgen05_error[key]
+
+
+def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """bfloat16 ``x [M, K] @ w [N, K].T`` on the tcgen05 tensor cores (TMA-fed, accumulators in
+    tensor memory).  With ``swiglu`` the rows of ``w`` are interleaved by
+    :func:`interleave_gate_up` and the result is ``silu(gate) * up``, ``[M, N / 2]``."""
+    _need_cuda(x, w)
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1],
+          "linear_tcgen05: bfloat16 x [M, K] and w [N, K]")
+    _need(x.stride(1) == 1 and w.stride(1) == 1, "linear_tcgen05: the reduced dimension must be contiguous")
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
+    library = _library("gemm_tcgen05.cu")
+    _check(library, library.pylon_gemm_tcgen05_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), int(swiglu),
+                                                    _ptr(tcgen05_error_word(x.device)), _SM_COUNT, _stream()))
+    return y
 
 # Small integer buffers kernels use to find out which of their blocks finishes last.  They
 # are zero between launches (a kernel leaves its counters as it found them) and launches on
@@ -326,6 +359,10 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
         _check(library, library.pylon_gemm_skinny_swiglu(_ptr(x), _ptr(w_interleaved), _ptr(y), m, n, k, x.stride(0), w_interleaved.stride(0),
                                                          n // 2, _stream()))
         return y
+    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and k % 8 == 0
+            and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0 and w_interleaved.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):
+        return linear_tcgen05(x, w_interleaved, swiglu=True)   # many rows: our tcgen05 kernel with SwiGLU in its epilogue
     return swiglu(linear(x, w_interleaved), interleaved=True)
 
 

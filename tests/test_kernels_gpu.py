@@ -145,6 +145,36 @@ def test_linear_swiglu_with_interleaved_weights(m, inter, k):
         torch.testing.assert_close(ops.swiglu(columns, interleaved=True).double(), g2 * torch.sigmoid(g2) * u2, **tolerance(dtype))
 
 
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (256, 512, 128), (300, 320, 224), (2048, 2560, 4096), (1000, 6144, 2560), (129, 136, 72)])
+def test_tcgen05_gemm(m, n, k):
+    """The TMA + tcgen05 product against float64, with row, column and k counts that do not
+    fill its tiles; its bounded waits must never have run out."""
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    y = ops.linear_tcgen05(x, w)
+    torch.testing.assert_close(y.double(), x.double() @ w.double().T, rtol=2e-2, atol=2e-2)
+    assert int(ops.tcgen05_error_word(x.device).item()) == 0
+
+
+@pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (2048, 9728, 2560), (130, 104, 96), (500, 224, 96)])
+def test_tcgen05_gemm_with_swiglu_epilogue(m, inter, k):
+    from pylon_b200.kernels import ops
+
+    gate = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    up = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    stacked = ops.interleave_gate_up(gate, up)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g * torch.sigmoid(g) * u
+    torch.testing.assert_close(ops.linear_tcgen05(x, stacked, swiglu=True).double(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(ops.linear_swiglu(x, stacked).double(), want, rtol=2e-2, atol=2e-2)   # the dispatch the feed-forward uses
+    assert int(ops.tcgen05_error_word(x.device).item()) == 0
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.linear_tcgen05(torch.zeros(128, 20, device=DEVICE, dtype=torch.bfloat16), torch.zeros(64, 20, device=DEVICE, dtype=torch.bfloat16))
+
+
 def test_skinny_gemm_refuses():
     from pylon_b200.kernels import ops
 
