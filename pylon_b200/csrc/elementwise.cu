@@ -245,6 +245,110 @@ __global__ void qk_norm_rope_kv_write_kernel(
   }
 }
 
+// Vector form for head sizes 64, 128 and 256 with the rotation over the whole head: lane l holds
+// the CHUNK = d / 32 consecutive elements l * CHUNK .., loaded and stored as one vector; its
+// rotation partners (d / 2 further) sit in lane l ^ 16 and come by shuffle.
+template <typename T, int CHUNK>
+struct HeadChunk;
+template <int CHUNK>
+struct HeadChunk<__nv_bfloat16, CHUNK> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[CHUNK]) {
+    if constexpr (CHUNK == 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+      v[0] = f.x; v[1] = f.y;
+    } else {
+      uint32_t raw[CHUNK / 2];
+      if constexpr (CHUNK == 4) { const uint2 r = *reinterpret_cast<const uint2*>(p); raw[0] = r.x; raw[1] = r.y; }
+      else { const uint4 r = *reinterpret_cast<const uint4*>(p); raw[0] = r.x; raw[1] = r.y; raw[2] = r.z; raw[3] = r.w; }
+#pragma unroll
+      for (int i = 0; i < CHUNK / 2; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[i]));
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+      }
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[CHUNK]) {
+    uint32_t raw[CHUNK / 2];
+#pragma unroll
+    for (int i = 0; i < CHUNK / 2; ++i) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      raw[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    if constexpr (CHUNK == 2) *reinterpret_cast<uint32_t*>(p) = raw[0];
+    else if constexpr (CHUNK == 4) *reinterpret_cast<uint2*>(p) = make_uint2(raw[0], raw[1]);
+    else *reinterpret_cast<uint4*>(p) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+  }
+};
+template <int CHUNK>
+struct HeadChunk<float, CHUNK> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[CHUNK]) {
+#pragma unroll
+    for (int i = 0; i < CHUNK; i += 2) { const float2 f = *reinterpret_cast<const float2*>(p + i); v[i] = f.x; v[i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[CHUNK]) {
+#pragma unroll
+    for (int i = 0; i < CHUNK; i += 2) *reinterpret_cast<float2*>(p + i) = make_float2(v[i], v[i + 1]);
+  }
+};
+
+template <typename T, int CHUNK>
+__global__ void qk_norm_rope_kv_write_vec_kernel(
+    T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+    const int* __restrict__ positions, const int* __restrict__ token_row, const int* __restrict__ block_table,
+    int table_width, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
+    int num_tokens) {
+  constexpr int d = CHUNK * 32, half = d / 2;
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)num_tokens * heads) return;
+  const int t = (int)(item / heads), head = (int)(item % heads);
+  T* src = qkv + ((size_t)t * heads + head) * d + lane * CHUNK;
+  const int pos = positions[t];
+  T* page_dst = nullptr;
+  if (head >= nq) {
+    const int row = token_row[t];
+    const int page = block_table[(size_t)row * table_width + pos / page_size];
+    if (page < 0 || page >= num_pages) return;   // never for a prepared step; keeps memory safe
+    const int kv_head = (head - nq) % nkv;
+    T* pages = head < nq + nkv ? k_pages : v_pages;
+    page_dst = pages + (((size_t)page * nkv + kv_head) * page_size + pos % page_size) * d + lane * CHUNK;
+  }
+  float x[CHUNK];
+  HeadChunk<T, CHUNK>::load(src, x);
+  if (head >= nq + nkv) {   // value: plain copy
+    HeadChunk<T, CHUNK>::store(page_dst, x);
+    return;
+  }
+  const float* weight = head < nq ? q_weight : k_weight;
+  if (weight) {
+    float sumsq = 0.f;
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) sumsq += x[i] * x[i];
+    sumsq = warp_sum(sumsq);
+    const float inv = rsqrtf(sumsq / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) x[i] = x[i] * inv * weight[lane * CHUNK + i];
+  }
+  if (cos_table) {
+    const int p = pos < table_positions ? pos : table_positions - 1;   // the host checks the range
+    const int column = (lane & 15) * CHUNK;                            // both halves share their angles
+    const float* c = cos_table + (size_t)p * half + column;
+    const float* s = sin_table + (size_t)p * half + column;
+    const bool upper = lane >= 16;
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+      x[i] = upper ? x[i] * c[i] + partner * s[i] : x[i] * c[i] - partner * s[i];
+    }
+  }
+  HeadChunk<T, CHUNK>::store(head < nq ? src : page_dst, x);
+}
+
 // -----------------------------------------------------------------------------------------
 // SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
 // -----------------------------------------------------------------------------------------
@@ -353,6 +457,21 @@ static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float e
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
+  // Head sizes 64, 128, 256 rotated over the whole head (or not at all), aligned: the vector form.
+  const bool whole = (rotary_dim == d && cos_t) || (rotary_dim == 0 || !cos_t);
+  const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0);
+  if (whole && aligned && (d == 64 || d == 128 || d == 256)) {
+    const float* cos_used = rotary_dim == d ? cos_t : nullptr;
+#define PYLON_LAUNCH_QK_VEC(C)                                                                              \
+    launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C>, dim3(blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps, cos_used, \
+                     sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, v_pages,  \
+                     num_pages, nq, nkv, num_tokens)
+    if (d == 64) PYLON_LAUNCH_QK_VEC(2);
+    else if (d == 128) PYLON_LAUNCH_QK_VEC(4);
+    else PYLON_LAUNCH_QK_VEC(8);
+#undef PYLON_LAUNCH_QK_VEC
+    PYLON_CHECK_LAUNCH("qk_norm_rope_kv_write");
+  }
 #define PYLON_LAUNCH_QK(N)                                                                              \
   launch_dependent(qk_norm_rope_kv_write_kernel<T, N>, dim3(blocks), dim3(warps * 32), smem, stream,    \
       qkv, qw, kw, eps, cos_t, sin_t, rotary_dim, table_positions, positions, token_row, block_table,   \

@@ -122,7 +122,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
   };
 
   // The weights do not depend on the kernel before this one: the first fragments are on
-  // their way before this kernel waits for its activations.
+  // their way before this kernel waits for its activations.  (Asking L2 for the block's whole
+  // weight slab up front with cp.async.bulk.prefetch.L2 was measured slower: 22 against 18
+  // microseconds on the 19456 x 2560 product.)
   int ks0 = warp;
   load_weights(wa, ks0);
   grid_dependency_wait();

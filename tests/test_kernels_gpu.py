@@ -332,6 +332,7 @@ def test_attention_refuses_what_it_cannot_do():
 @pytest.mark.parametrize("nq, nkv, d, rotary, page, norm", [
     (4, 2, 16, 16, 16, True), (6, 3, 32, 32, 8, True), (32, 8, 128, 128, 256, True), (5, 5, 64, 32, 4, True),
     (2, 1, 80, 80, 24, False), (3, 1, 256, 64, 16, True),
+    (4, 2, 64, 64, 16, True), (2, 2, 256, 256, 8, True), (8, 4, 128, 128, 64, False),     # the vector form
 ])
 def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm):
     from pylon_b200.kernels import ops
