@@ -211,6 +211,40 @@ def time_prefill(engine, torch, repeats: int, rng) -> dict:
     return {"ms": best}
 
 
+def profile_steps(engine, torch, ops, kind: str, batch: int, rng) -> None:
+    """Warm up, then run two steps of ``kind`` inside the profiler's range (eagerly, so that a
+    profiler sees every kernel as its own launch)."""
+    from pylon_b200.engine import StepEntry
+
+    vocab = engine.spec.vocab_size
+    if kind == "decode":
+        requests = fill_caches(engine, torch, batch, CONTEXT - 8, rng, PREFILL_TOKENS)
+        tokens = [1] * batch
+
+        def step():
+            nonlocal tokens
+            logits = engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])
+            tokens = ops.sample(logits).cpu().tolist()
+    else:
+        counter = [0]
+
+        def step():
+            request = engine.open(("profile", counter[0]), PREFILL_TOKENS)
+            counter[0] += 1
+            engine.step([StepEntry(request, rng.integers(0, vocab, size=PREFILL_TOKENS).tolist(), (PREFILL_TOKENS - 1,))])
+            torch.cuda.synchronize()
+            engine.close(request)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {CONTEXT}")
+
+
 def prefill_flops(cfg: dict, tokens: int) -> float:
     h, q, kv, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"]
     per_layer = 2 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * inter)
@@ -229,6 +263,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
                         help="run fewer layers than the configuration has (named in the output)")
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    parser.add_argument("--profile", choices=["decode", "prefill"],
+                        help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -256,7 +292,15 @@ def main() -> int:
         max_batch_size=largest, max_queue_size=largest, prefill_chunk_size=PREFILL_TOKENS,
         cuda_graphs=os.environ.get("PYLON_CUDA_GRAPHS", "true").lower() in ("1", "true"),
     )
+    if args.profile:
+        engine_config = EngineConfig(
+            dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=max(args.batch, 2) * CONTEXT, max_context=CONTEXT,
+            max_batch_size=max(args.batch, 2), prefill_chunk_size=PREFILL_TOKENS, cuda_graphs=False,
+        )
     engine = Engine(None, engine_config, device="cuda:0", model_config=model_config, random_seed=0)
+    if args.profile:
+        profile_steps(engine, torch, ops, args.profile, args.batch, rng)
+        return 0
     peak = peaks()
 
     prefill = time_prefill(engine, torch, 5, rng)

@@ -428,20 +428,32 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
 
+    // The query fragments stay in registers when the head is small enough to leave room.
+    constexpr bool Q_IN_REGISTERS = D <= 128;
+    unsigned q_frag[Q_IN_REGISTERS ? D / 16 : 1][4];
+    bool q_loaded = false;
+
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       issue(tile + DEC_STAGES - 1);
       cp_async_wait<DEC_STAGES - 1>();
       __syncthreads();
       const __nv_bfloat16* ks = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS + warp * 16 * LD;
       const __nv_bfloat16* vs = ks + TILE_ELEMS;
+      if (Q_IN_REGISTERS && !q_loaded) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ldmatrix_x4(q_frag[Q_IN_REGISTERS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        q_loaded = true;
+      }
 
       // Even and odd k-steps accumulate separately: four independent MMA chains instead of two.
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        unsigned a[4], b[4];
-        ldmatrix_x4(a, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        unsigned a_loaded[4], b[4];
+        if (!Q_IN_REGISTERS) ldmatrix_x4(a_loaded, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        const unsigned (&a)[4] = Q_IN_REGISTERS ? q_frag[Q_IN_REGISTERS ? kk : 0] : a_loaded;
         ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
         if (kk & 1) {
           mma_bf16(s_odd[0], a, b[0], b[1]);
@@ -455,16 +467,19 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[n][i] += s_odd[n][i];
-      const int key_base = tile * BLOCK_N + warp * 16 + 2 * tq;
+      // Tiles that end at or before the row's first new token, with no window, are visible whole.
+      if (p.window > 0 || tile * BLOCK_N + BLOCK_N - 1 > pos0) {
+        const int key_base = tile * BLOCK_N + warp * 16 + 2 * tq;
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+        for (int n = 0; n < 2; ++n) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int h = i >> 1;
-          const int key = key_base + n * 8 + (i & 1);
-          bool visible = row_valid[h] && key <= row_pos[h];
-          if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
-          if (!visible) s[n][i] = -INFINITY;
+          for (int i = 0; i < 4; ++i) {
+            const int h = i >> 1;
+            const int key = key_base + n * 8 + (i & 1);
+            bool visible = row_valid[h] && key <= row_pos[h];
+            if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
+            if (!visible) s[n][i] = -INFINITY;
+          }
         }
       }
 #pragma unroll
