@@ -85,17 +85,20 @@ template <> struct Vec4<__nv_bfloat16> {
 
 constexpr int NORM_THREADS = 256;
 
-template <typename T, int ITEMS>
-__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+// DT: type of the delta (the activation type, or float when the delta comes as `delta_parts`
+// float32 partial sums, each [all rows, width], `part_stride` elements apart).
+template <typename T, typename DT, int ITEMS>
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __restrict__ residual, const DT* __restrict__ delta,
                                                                        const float* __restrict__ weight, const int* __restrict__ rows,
-                                                                       T* __restrict__ out, int width, float eps, int write_residual) {
+                                                                       T* __restrict__ out, int width, float eps, int write_residual,
+                                                                       int delta_parts, long long part_stride) {
   __shared__ float scratch[33];
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* res = residual + (size_t)row * width;
-  const T* del = delta ? delta + (size_t)row * width : nullptr;
+  const DT* del = delta ? delta + (size_t)row * width : nullptr;
   T* dst = out + (size_t)r * width;
   const int groups = width >> 2;
   float4 x[ITEMS];
@@ -109,8 +112,10 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __
     for (int k = 0; k < ITEMS; ++k) {
       const int i = threadIdx.x + k * NORM_THREADS;
       if (i < groups) {
-        const float4 d = Vec4<T>::load(del + 4 * i);
-        x[k].x += d.x; x[k].y += d.y; x[k].z += d.z; x[k].w += d.w;
+        for (int part = 0; part < delta_parts; ++part) {   // in order: the sum does not depend on who wrote which part first
+          const float4 d = Vec4<DT>::load(del + (size_t)part * part_stride + 4 * i);
+          x[k].x += d.x; x[k].y += d.y; x[k].z += d.z; x[k].w += d.w;
+        }
       }
     }
   }
@@ -129,15 +134,17 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __
   }
 }
 
-template <typename T>
-static bool launch_add_rmsnorm_vec(float* residual, const T* delta, const float* weight, const int* rows, T* out, int n_rows,
-                                   int width, float eps, int write_residual, cudaStream_t stream) {
+template <typename T, typename DT>
+static bool launch_add_rmsnorm_vec(float* residual, const DT* delta, const float* weight, const int* rows, T* out, int n_rows,
+                                   int width, float eps, int write_residual, int delta_parts, long long part_stride,
+                                   cudaStream_t stream) {
   if (width % 4 || width > NORM_THREADS * 4 * 8) return false;
-  if (((uintptr_t)residual % 16) || ((uintptr_t)weight % 16) || ((uintptr_t)out % 8) || (delta && ((uintptr_t)delta % 8))) return false;
+  if (((uintptr_t)residual % 16) || ((uintptr_t)weight % 16) || ((uintptr_t)out % 8) || (delta && ((uintptr_t)delta % 16))) return false;
+  if (part_stride % 4) return false;
   const int items = (width / 4 + NORM_THREADS - 1) / NORM_THREADS;
 #define PYLON_NORM_CASE(N)                                                                                     \
   case N:                                                                                                      \
-    launch_dependent(add_rmsnorm_vec_kernel<T, N>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, residual, delta, weight, rows, out, width, eps, write_residual); \
+    launch_dependent(add_rmsnorm_vec_kernel<T, DT, N>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, residual, delta, weight, rows, out, width, eps, write_residual, delta_parts, part_stride); \
     return true;
   switch (items) {
     PYLON_NORM_CASE(1) PYLON_NORM_CASE(2) PYLON_NORM_CASE(3) PYLON_NORM_CASE(4)
@@ -423,15 +430,27 @@ extern "C" int pylon_add_rmsnorm(float* residual, const void* delta, const float
   if (rows && write_residual) PYLON_REFUSE("add_rmsnorm: a row selection cannot update the residual");
   const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
   if (dtype == PYLON_DTYPE_F32) {
-    if (!launch_add_rmsnorm_vec<float>(residual, (const float*)delta, weight, rows, (float*)out, n_rows, width, eps, write_residual, stream))
+    if (!launch_add_rmsnorm_vec<float, float>(residual, (const float*)delta, weight, rows, (float*)out, n_rows, width, eps, write_residual, 1, 0, stream))
       add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, rows, (float*)out, width, eps, write_residual);
   } else if (dtype == PYLON_DTYPE_BF16) {
-    if (!launch_add_rmsnorm_vec<__nv_bfloat16>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, n_rows, width, eps, write_residual, stream))
+    if (!launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, n_rows, width, eps, write_residual, 1, 0, stream))
       add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, rows, (__nv_bfloat16*)out, width, eps, write_residual);
   } else {
     PYLON_REFUSE("add_rmsnorm: unknown dtype %d", dtype);
   }
   PYLON_CHECK_LAUNCH("add_rmsnorm");
+}
+
+// The same with the delta given as `parts` float32 partial sums [parts, all rows, width] (contiguous): bfloat16 output,
+// width a multiple of 4 and at most 8192, no row selection.
+extern "C" int pylon_add_parts_rmsnorm(float* residual, const float* delta_parts, int parts, const float* weight, void* out,
+                                       int n_rows, int width, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (parts < 1 || !delta_parts) PYLON_REFUSE("add_parts_rmsnorm: %d parts", parts);
+  if (!launch_add_rmsnorm_vec<__nv_bfloat16, float>(residual, delta_parts, weight, nullptr, (__nv_bfloat16*)out, n_rows, width, eps, 1, parts,
+                                                     (long long)n_rows * width, stream))
+    PYLON_REFUSE("add_parts_rmsnorm: width %d must be a multiple of 4, at most 8192, with 16-byte aligned buffers", width);
+  PYLON_CHECK_LAUNCH("add_parts_rmsnorm");
 }
 
 extern "C" int pylon_residual_add(float* residual, const void* delta, long long n, int dtype, cudaStream_t stream) {

@@ -54,7 +54,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
   extern __shared__ float reduce[];   // [WARPS][NT * 16][MT * 8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NT * 16);
-  const int k_steps = (K + 31) / 32;
+  // blockIdx.y splits k (gridDim.y parts): each part writes its own float32 partial result
+  // [M, N] at y + part * M * ldy, and whoever consumes them adds them up.
+  const int all_steps = (K + 31) / 32;
+  const int share = (all_steps + gridDim.y - 1) / gridDim.y;
+  const int step_begin = blockIdx.y * share;
+  const int k_steps = min(all_steps, step_begin + share);
+  y += (size_t)blockIdx.y * M * ldy;
 
   const __nv_bfloat16* w_rows[NT][2];
 #pragma unroll
@@ -88,7 +94,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (ks0 + u * WARPS) * 32;
-      const bool in_range = k + t * 8 < K;     // K is a multiple of 8: a lane's 8 elements are all in or all out
+      // K is a multiple of 8: a lane's 8 elements are all in or all out; steps past this block's share load nothing
+      const bool in_range = k + t * 8 < K && ks0 + u * WARPS < k_steps;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         wf[u][nt][0] = in_range ? load_stream_16(w_rows[nt][0] + k) : zero;
@@ -100,7 +107,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (ks0 + u * WARPS) * 32;
-      const bool in_range = k + t * 8 < K;
+      const bool in_range = k + t * 8 < K && ks0 + u * WARPS < k_steps;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) xf[u][mt] = (in_range && x_valid[mt]) ? load_cached_16(x_rows[mt] + k) : zero;
     }
@@ -125,7 +132,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
   // their way before this kernel waits for its activations.  (Asking L2 for the block's whole
   // weight slab up front with cp.async.bulk.prefetch.L2 was measured slower: 22 against 18
   // microseconds on the 19456 x 2560 product.)
-  int ks0 = warp;
+  int ks0 = step_begin + warp;
   load_weights(wa, ks0);
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
@@ -181,7 +188,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
 
 template <int MT, int NT, int WARPS, int UNROLL, bool SWIGLU, typename OutT>
 static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y, int M, int N, int K, long long ldx,
-                         long long ldw, long long ldy, cudaStream_t stream) {
+                         long long ldw, long long ldy, cudaStream_t stream, int k_splits = 1) {
   constexpr size_t smem = (size_t)WARPS * NT * 16 * MT * 8 * sizeof(float);
   auto kernel = gemm_skinny_kernel<MT, NT, WARPS, UNROLL, SWIGLU, OutT>;
   if (smem > 48 * 1024) {
@@ -193,7 +200,7 @@ static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y
     }
   }
   const int blocks = (N + NT * 16 - 1) / (NT * 16);
-  launch_dependent(kernel, dim3(blocks), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
+  launch_dependent(kernel, dim3(blocks, k_splits), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
   PYLON_CHECK_LAUNCH("gemm_skinny");
 }
 
@@ -223,6 +230,19 @@ extern "C" int pylon_gemm_skinny_bf16(const void* x, const void* w, void* y, int
   if (out_dtype == PYLON_DTYPE_F32)
     return pylon::dispatch_skinny<float>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)y, M, N, K, ldx, ldw, ldy, stream);
   PYLON_REFUSE("gemm_skinny: unknown result dtype %d", out_dtype);
+}
+
+// The product as k_splits float32 partial sums: y [k_splits, M, N] contiguous, whose sum over the first dimension is
+// x @ w.T.  For products with few weight rows (M <= 8): more blocks, more loads in flight; the reader adds the parts.
+extern "C" int pylon_gemm_skinny_partial(const void* x, const void* w, float* y, int M, int N, int K, long long ldx, long long ldw,
+                                         int k_splits, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 8) PYLON_REFUSE("gemm_skinny_partial: M = %d is more than 8 rows", M);
+  if (k_splits < 1 || k_splits > 16) PYLON_REFUSE("gemm_skinny_partial: %d parts", k_splits);
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("gemm_skinny_partial: K = %d and the row strides must be multiples of 8", K);
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16)) PYLON_REFUSE("gemm_skinny_partial: x and w must be 16-byte aligned");
+  if (ldx < K || ldw < K) PYLON_REFUSE("gemm_skinny_partial: a row stride is shorter than its row");
+  return pylon::launch_skinny<1, 1, 8, 2, false, float>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, y, M, N, K, ldx, ldw, N, stream, k_splits);
 }
 
 // silu(x gate^T) * (x up^T) in one kernel (M <= 16, bfloat16): w's rows are interleaved in groups of 8 (rows 16b..16b+7

@@ -65,6 +65,7 @@ _SIGNATURES = {
         "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "pylon_residual_add": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+        "pylon_add_parts_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
         "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -75,6 +76,7 @@ _SIGNATURES = {
     },
     "gemm_skinny.cu": {
         "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
+        "pylon_gemm_skinny_partial": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p],
         "pylon_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
     "gemm_tcgen05.cu": {
@@ -146,8 +148,19 @@ def add_rmsnorm(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``residual += delta`` (float32, in place, skipped when ``rows`` selects rows), then
-    RMSNorm of the selected rows with the float32 ``weight``; returns ``out_dtype [n, width]``."""
+    RMSNorm of the selected rows with the float32 ``weight``; returns ``out_dtype [n, width]``.
+    ``delta`` may also be float32 partial sums ``[parts, T, width]`` (see
+    :func:`linear_for_residual`): their sum is the delta."""
     _need_cuda(residual, delta, weight, rows, out)
+    if delta is not None and delta.dim() == 3:
+        if rows is None and out is None and out_dtype == torch.bfloat16 and delta.dtype == torch.float32 and delta.is_contiguous() \
+                and delta.shape[1:] == residual.shape and residual.is_contiguous() and residual.shape[1] % 4 == 0 and residual.shape[1] <= 8192:
+            normed = torch.empty(residual.shape, dtype=torch.bfloat16, device=residual.device)
+            library = _library("elementwise.cu")
+            _check(library, library.pylon_add_parts_rmsnorm(_ptr(residual), _ptr(delta), delta.shape[0], _ptr(weight), _ptr(normed),
+                                                            residual.shape[0], residual.shape[1], float(eps), _stream()))
+            return normed
+        delta = delta.sum(dim=0).to(out_dtype)
     _need(residual.dtype == torch.float32 and residual.dim() == 2 and residual.is_contiguous(), "add_rmsnorm: residual must be contiguous float32 [T, width]")
     tokens, width = residual.shape
     _need(weight.dtype == torch.float32 and weight.shape == (width,) and weight.is_contiguous(), "add_rmsnorm: weight must be float32 [width]")
@@ -168,6 +181,10 @@ def add_rmsnorm(
 
 def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     _need_cuda(residual, delta)
+    if delta.dim() == 3:   # partial sums
+        for part in delta:
+            residual_add(residual, part)
+        return
     _need(residual.dtype == torch.float32 and residual.is_contiguous() and delta.is_contiguous() and delta.shape == residual.shape, "residual_add: shapes differ or tensors are not contiguous")
     library = _library("elementwise.cu")
     _check(library, library.pylon_residual_add(_ptr(residual), _ptr(delta), residual.numel(), _dtype_code(delta.dtype), _stream()))
@@ -273,6 +290,28 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+PARTIAL_MAX_BLOCKS = 2 * 148   # products with fewer 16-row blocks than this are split over k as well
+
+
+def linear_for_residual(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` for a result that goes straight into the residual stream: either the
+    product ``[M, N]`` in the activation dtype, or - for few rows and a matrix with too few
+    rows of its own to keep the GPU busy - float32 partial sums ``[parts, M, N]`` over slices
+    of k, which the stream's next norm adds up (no extra kernel, no atomics)."""
+    m, k = x.shape
+    n = w.shape[0]
+    blocks = -(-n // 16)
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and m <= SKINNY_MAX_ROWS and blocks < PARTIAL_MAX_BLOCKS
+            and k >= 2048 and k % 8 == 0 and n % 4 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        parts = int(min(4, max(2, (3 * 148) // blocks)))
+        y = torch.empty((parts, m, n), dtype=torch.float32, device=x.device)
+        library = _library("gemm_skinny.cu")
+        _check(library, library.pylon_gemm_skinny_partial(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), parts, _stream()))
+        return y
+    return linear(x, w)
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

@@ -93,4 +93,4 @@ class GroupedQueryAttention(Mixer):
             qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale,
         )
-        return ops.linear(context, self.w_o)
+        return ops.linear_for_residual(context, self.w_o)

@@ -162,13 +162,13 @@ class Mixer(Part):
         return CacheNeed()
 
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
-        """Returns the delta for the residual stream, ``[T, width]`` in the activation dtype."""
+        """Returns the delta for the residual stream (see :class:`ResidualStream`)."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
-        """Returns the delta for the residual stream, ``[T, width]`` in the activation dtype."""
+        """Returns the delta for the residual stream (see :class:`ResidualStream`)."""
         raise NotImplementedError
 
 
@@ -184,7 +184,9 @@ class ResidualStream:
     """The residual sum in float32 ``[T, width]`` plus the delta not yet added to it.
 
     Parts hand their output to ``add``; the next norm folds it in (one fused kernel reads
-    the delta once, updates the 32-bit sum and writes the normalised activations).
+    the delta once, updates the 32-bit sum and writes the normalised activations).  A delta
+    is ``[T, width]`` in the activation dtype, or float32 partial sums ``[parts, T, width]``
+    whose sum is the delta (what :func:`pylon_b200.kernels.ops.linear_for_residual` may return).
     """
 
     def __init__(self, residual: torch.Tensor) -> None:

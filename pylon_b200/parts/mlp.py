@@ -48,4 +48,4 @@ class SwiGLU(FeedForward):
             activation = ops.linear_swiglu(h, self.w_gate_up)
         else:
             activation = ops.swiglu(ops.linear(h, self.w_gate_up))
-        return ops.linear(activation, self.w_down)
+        return ops.linear_for_residual(activation, self.w_down)

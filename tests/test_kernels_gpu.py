@@ -175,6 +175,39 @@ def test_tcgen05_gemm_with_swiglu_epilogue(m, inter, k):
         ops.linear_tcgen05(torch.zeros(128, 20, device=DEVICE, dtype=torch.bfloat16), torch.zeros(64, 20, device=DEVICE, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("m", [1, 8])
+@pytest.mark.parametrize("n, k", [(2560, 4096), (2560, 9728), (96, 2048)])
+def test_partial_sums_for_the_residual(m, n, k):
+    """Products with few weight rows come back as float32 partial sums over slices of k; the
+    add + RMSNorm kernel adds them to the residual in order."""
+    from pylon_b200.kernels import ops
+
+    eps = 1e-5
+    x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    parts = ops.linear_for_residual(x, w)
+    assert parts.dim() == 3 and parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
+    product = x.double() @ w.double().T
+    torch.testing.assert_close(parts.double().sum(0), product, rtol=1e-3, atol=1e-3)
+    residual = torch.randn(m, n, device=DEVICE)
+    weight = torch.rand(n, device=DEVICE) + 0.5
+    want_residual = residual.double() + product
+    want = want_residual / torch.sqrt((want_residual**2).mean(-1, keepdim=True) + eps) * weight.double()
+    work = residual.clone()
+    normed = ops.add_rmsnorm(work, parts, weight, eps, torch.bfloat16)
+    torch.testing.assert_close(work.double(), want_residual, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(normed.double(), want, rtol=2e-2, atol=2e-2)
+    work2 = residual.clone()
+    ops.residual_add(work2, parts)
+    torch.testing.assert_close(work2.double(), want_residual, rtol=1e-3, atol=2e-3)
+    # a row selection (the final norm) takes the sum of the parts as its delta
+    rows = torch.tensor([m - 1], device=DEVICE, dtype=torch.int32)
+    picked = ops.add_rmsnorm(residual.clone(), parts, weight, eps, torch.bfloat16, rows=rows)
+    torch.testing.assert_close(picked.double(), want[m - 1 :], rtol=3e-2, atol=3e-2)
+    # many rows, or a matrix with many rows of its own: the plain product
+    assert ops.linear_for_residual(torch.zeros(9, k, device=DEVICE, dtype=torch.bfloat16), w).dim() == 2
+
+
 def test_skinny_gemm_refuses():
     from pylon_b200.kernels import ops
 
