@@ -79,8 +79,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     k = k.repeat_interleave(group, dim=0)
     v = v.repeat_interleave(group, dim=0)
     scores = q @ k.transpose(1, 2) / math.sqrt(dim)
-    i = torch.arange(tokens).unsqueeze(1)
-    j = torch.arange(tokens).unsqueeze(0)
+    i = torch.arange(tokens, device=q.device).unsqueeze(1)
+    j = torch.arange(tokens, device=q.device).unsqueeze(0)
     visible = j <= i
     if window is not None:
         visible &= (i - j) < window
@@ -126,10 +126,12 @@ def forward(cfg: dict, w: dict, token_ids) -> torch.Tensor:
     src/pylon/model/model.py:124-144: embedding, blocks, final norm, LM head (the embedding
     table when ``tie_word_embeddings``, else ``lm_head.weight``).
     """
-    ids = torch.as_tensor(list(token_ids), dtype=torch.long)
+    device = w["model.embed_tokens.weight"].device   # the weights may have been moved to a GPU for large shapes
+    ids = torch.as_tensor(list(token_ids), dtype=torch.long, device=device)
     dtype = w["model.embed_tokens.weight"].dtype
     x = w["model.embed_tokens.weight"][ids]
     cos, sin = rope_tables(cfg["head_dim"], float(cfg["rope_theta"]), torch.arange(len(ids)), dtype)
+    cos, sin = cos.to(device), sin.to(device)
     for layer in range(cfg["num_hidden_layers"]):
         x = block(x, w, f"model.layers.{layer}.", cfg, cos, sin)
     x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])

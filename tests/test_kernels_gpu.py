@@ -349,6 +349,40 @@ def test_attention_finds_one_far_key_among_hundreds(mode):
         cursor += ql
 
 
+@pytest.mark.parametrize("mode", ["float32", "bfloat16_mma", "bfloat16_mma_splits"])
+@pytest.mark.parametrize("q_len", [1, 40])
+def test_attention_window_edge(mode, q_len):
+    """The key just outside the window is made overwhelming: if the mask were off by one, it
+    would take all the weight.  The key just inside must win instead."""
+    from pylon_b200.kernels import ops
+
+    dtype = torch.float32 if mode == "float32" else torch.bfloat16
+    nq, nkv, d, page, window, kv = 2, 1, 64, 16, 37, 300
+    cache = Paged([kv], [q_len], nkv, d, page, dtype, seed=8)
+    direction = torch.randn(d, device=DEVICE)
+    direction = direction / direction.norm()
+    fused = (torch.randn(q_len, (nq + 2) * d, device=DEVICE) * 0.05).to(dtype)
+    fused[:, : nq * d] = (direction * 6).to(dtype).repeat(nq)
+    last = kv - 1                               # the last token's position; its window is (last - 37, last]
+    outside, inside = last - window, last - window + 1
+
+    def set_key(position, scale):
+        cache.k_pages[int(cache.table[0, position // page]), 0, position % page] = (direction * scale).to(dtype)
+
+    set_key(outside, 60.0)
+    set_key(inside, 30.0)
+    out = ops.paged_attention(
+        fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table, nq,
+        q_len, kv, window=window, force_simple=mode == "float32", num_splits=3 if mode.endswith("splits") else None,
+    ).reshape(q_len, nq, d)
+    want = cache.v_pages[int(cache.table[0, inside // page]), 0, inside % page].float()
+    torch.testing.assert_close(out[-1, 0].float(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[-1, 1].float(), want, rtol=2e-2, atol=2e-2)
+    if q_len > 1:   # the token before still has the big key inside its window
+        big = cache.v_pages[int(cache.table[0, outside // page]), 0, outside % page].float()
+        torch.testing.assert_close(out[-2, 0].float(), big, rtol=2e-2, atol=2e-2)
+
+
 def test_attention_refuses_what_it_cannot_do():
     from pylon_b200.kernels import ops
 
