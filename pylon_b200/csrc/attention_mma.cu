@@ -428,6 +428,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
 
+    const bool upper_rows_unused = packed_rows <= 8;
     // The query fragments stay in registers when the head is small enough to leave room.
     constexpr bool Q_IN_REGISTERS = D <= 128;
     unsigned q_frag[Q_IN_REGISTERS ? D / 16 : 1][4];
@@ -484,6 +485,9 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        // One decoded token times a group of up to 8 fills rows 0..7 only: rows 8..15 hold zero
+        // queries, their scores stay zero and nothing of them is stored.
+        if (h == 1 && upper_rows_unused) continue;
         float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
