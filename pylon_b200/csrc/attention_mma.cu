@@ -73,6 +73,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (relative error about 2^-22, exact 0 for -infinity); the
+// library's exp2f wraps the same instruction in range handling the softmax does not need.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -277,21 +284,25 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float new_max = fmaxf(row_max[mt][h], mx);
             const float use_max = new_max == -INFINITY ? 0.f : new_max;
-            const float alpha = exp2f((row_max[mt][h] - use_max) * p.scale_log2);   // exp2(-inf) = 0 on the first tile
+            const float alpha = fast_exp2((row_max[mt][h] - use_max) * p.scale_log2);   // 2^-inf = 0 on the first tile
             const float shift = use_max * p.scale_log2;
             float sum = 0.f;
 #pragma unroll
             for (int n = 0; n < BLOCK_N / 8; ++n) {
-              const float p0 = exp2f(s[mt][n][2 * h] * p.scale_log2 - shift);
-              const float p1 = exp2f(s[mt][n][2 * h + 1] * p.scale_log2 - shift);
+              const float p0 = fast_exp2(s[mt][n][2 * h] * p.scale_log2 - shift);
+              const float p1 = fast_exp2(s[mt][n][2 * h + 1] * p.scale_log2 - shift);
               s[mt][n][2 * h] = p0;
               s[mt][n][2 * h + 1] = p1;
               sum += p0 + p1;
             }
             row_sum[mt][h] = row_sum[mt][h] * alpha + sum;
             row_max[mt][h] = new_max;
+            // Once a row's maximum has settled alpha is exactly 1: the accumulators are left alone
+            // unless some row of the warp moved.
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) { o[mt][i][2 * h] *= alpha; o[mt][i][2 * h + 1] *= alpha; }
+              for (int i = 0; i < D / 8; ++i) { o[mt][i][2 * h] *= alpha; o[mt][i][2 * h + 1] *= alpha; }
+            }
           }
         }
 
@@ -493,13 +504,13 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float new_max = fmaxf(row_max[h], mx);
         const float use_max = new_max == -INFINITY ? 0.f : new_max;
-        const float alpha = exp2f((row_max[h] - use_max) * p.scale_log2);
+        const float alpha = fast_exp2((row_max[h] - use_max) * p.scale_log2);
         const float shift = use_max * p.scale_log2;
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
-          const float p0 = exp2f(s[n][2 * h] * p.scale_log2 - shift);
-          const float p1 = exp2f(s[n][2 * h + 1] * p.scale_log2 - shift);
+          const float p0 = fast_exp2(s[n][2 * h] * p.scale_log2 - shift);
+          const float p1 = fast_exp2(s[n][2 * h + 1] * p.scale_log2 - shift);
           s[n][2 * h] = p0;
           s[n][2 * h + 1] = p1;
           sum += p0 + p1;

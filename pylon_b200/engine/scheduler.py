@@ -28,6 +28,7 @@ Policies follow raun6k/Pylon:
 """
 from __future__ import annotations
 
+import logging
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -37,6 +38,8 @@ from pylon_b200.cache.manager import CacheManager, RequestCache
 from pylon_b200.engine.step import StepEntry
 from pylon_b200.sampling.params import SamplingParams
 from pylon_b200.sampling.sampler import RequestRandom
+
+logger = logging.getLogger("pylon_b200")   # key=value lines, as raun6k/Pylon logs its scheduler (src/pylon/scheduler/admit.py:16-57)
 
 PREFILL_MAX_WAIT_SECONDS = 0.1
 ADMIT_SKIP_WAIT_SECONDS = 0.1
@@ -205,10 +208,13 @@ class Scheduler:
         return None
 
     def admit(self) -> None:
+        if self.waiting and len(self.active) >= self.max_batch_size:
+            logger.debug("admission_blocked request_id=%s reason=slots", self.waiting[0].request_id)
         while self.waiting and len(self.active) < self.max_batch_size:
             now = self.clock()
             selected = self._select_waiting(now)
             if selected is None:
+                logger.debug("admission_blocked request_id=%s reason=memory", self.waiting[0].request_id)
                 return
             request, skipped_head = selected
             self.waiting.remove(request)
@@ -219,6 +225,7 @@ class Scheduler:
             self.active.append(request)
             if skipped_head:
                 self.head_skips += 1
+                logger.info("admission_skipped_head request_id=%s admitted=%s head_skips=%s", self.waiting[0].request_id, request.request_id, self.head_skips)
 
     # -- building a step -------------------------------------------------------------------
     def _choose_prefill(self, pending: list[Request], budget: int, now: float) -> Request:
@@ -290,6 +297,7 @@ class Scheduler:
             logits = self.run_step(entries)
             tokens = self.sample(logits, [r.sampling for r in ready], [r.random for r in ready]) if ready else []
         except Exception as error:   # the step's requests fail; the others go on
+            logger.exception("model_batch_failed requests=%s", [request.request_id for request in selected])
             for request in selected:
                 self._finish(request, "error", error)
             return

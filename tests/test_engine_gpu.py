@@ -163,6 +163,22 @@ def test_first_tokens_of_a_sequence(name, dtype, tiny_folders):
             np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, **tol)
 
 
+def test_graphs_can_be_captured_ahead_of_use(tiny_folders):
+    from pylon_b200.sampling import SamplingParams
+
+    name = "tinyA"
+    engine = engine_for(tiny_folders[name], name, "bfloat16", cuda_graphs=True)
+    assert engine.capture_decode_graphs([1, 2, 3]) == [1, 2, 3]
+    engine.cache.check()
+    assert engine.cache.free_slots() == 4 and engine.cache.free_pages() == [g.pool.num_pages for g in engine.cache.groups]
+    before = dict(engine.step_function.graphs.captured)
+    results = engine.generate(prompts_for(name), SamplingParams(max_new_tokens=4, temperature=0.0))
+    assert all(len(r.output_ids) == 4 for r in results)
+    assert all(engine.step_function.graphs.captured[size] is graph for size, graph in before.items())   # reused, not recaptured
+    with pytest.raises(RuntimeError, match="cuda_graphs"):
+        engine_for(tiny_folders[name], name, "bfloat16").capture_decode_graphs([1])
+
+
 def test_command_line(tiny_folders, tmp_path):
     name = "tinyA"
     cfg, weights = plain.read_model(tiny_folders[name])
