@@ -30,6 +30,16 @@ QWEN3_4B = dict(
     head_dim=128, intermediate_size=9_728, max_position_embeddings=262_144, rope_theta=5_000_000.0,
     rms_norm_eps=1e-6, tie_word_embeddings=True,
 )
+QWEN3_8B = dict(
+    vocab_size=151_936, hidden_size=4_096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, intermediate_size=12_288, max_position_embeddings=40_960, rope_theta=1_000_000.0,
+    rms_norm_eps=1e-6, tie_word_embeddings=False,
+)
+QWEN3_14B = dict(
+    vocab_size=151_936, hidden_size=5_120, num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=8,
+    head_dim=128, intermediate_size=17_408, max_position_embeddings=40_960, rope_theta=1_000_000.0,
+    rms_norm_eps=1e-6, tie_word_embeddings=False,
+)
 CONTEXT = 4_096
 PAGE_SIZE = 256
 PREFILL_TOKENS = 2_048
@@ -245,6 +255,68 @@ def profile_steps(engine, torch, ops, kind: str, batch: int, rng) -> None:
     print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {CONTEXT}")
 
 
+def run_serving_workload(name: str, torch) -> dict:
+    """The two serving workloads beside the headline one, through submit()/tick() from the first
+    request to the last token:
+
+    ``mixed8b``     Qwen3-8B shape, 64 requests with 2,048-token prompts and 128 new tokens each, greedy, batch 64,
+                    prefill portions of 2,048 tokens beside the decoding requests (continuous batching)
+    ``sampled14b``  Qwen3-14B shape, 16 requests with prompt lengths uniform in [64, 4096] and 256 new tokens each,
+                    temperature 0.7 with a fixed seed
+    """
+    import numpy as np
+
+    from pylon_b200.config import EngineConfig, Qwen3Config
+    from pylon_b200.engine import Engine
+    from pylon_b200.sampling import SamplingParams
+
+    rng = np.random.default_rng(0)
+    if name == "mixed8b":
+        fields, requests, new_tokens = QWEN3_8B, 64, 128
+        lengths = [2_048] * requests
+        params = [SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True)] * requests
+    else:
+        fields, requests, new_tokens = QWEN3_14B, 16, 256
+        lengths = rng.integers(64, 4_097, size=requests).tolist()
+        params = [SamplingParams(max_new_tokens=new_tokens, temperature=0.7, top_p=1.0, seed=1_000 + i, ignore_eos=True) for i in range(requests)]
+    longest = max(lengths) + new_tokens
+    config = EngineConfig(
+        dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=requests * (-(-longest // PAGE_SIZE) * PAGE_SIZE), max_context=longest,
+        max_batch_size=requests, max_queue_size=requests, prefill_chunk_size=PREFILL_TOKENS, cuda_graphs=True,
+    )
+    engine = Engine(None, config, device="cuda:0", model_config=Qwen3Config(**fields), random_seed=0)
+    prompts = [rng.integers(0, fields["vocab_size"], size=n).tolist() for n in lengths]
+    engine.generate(prompts[:2], [SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True)] * 2)   # warm up: libraries, allocator
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    for prompt, sampling in zip(prompts, params):
+        engine.submit(prompt, sampling)
+    ticks = mixed_ticks = 0
+    results = []
+    scheduler = engine.scheduler
+    while scheduler.has_work():
+        results += engine.tick()
+        ticks += 1
+        mixed_ticks += any(count > 1 for _, count in scheduler.last_step)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    produced = sum(len(r.output_ids) for r in results)
+    assert len(results) == requests and produced == requests * new_tokens and all(r.error is None for r in results)
+    first_token = sorted(r.first_token_seconds for r in results)
+    return {
+        "metric": f"output tokens/s, {name}", "value": round(produced / seconds, 1), "unit": "tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "seconds": round(seconds, 3), "prompt_tokens": int(sum(lengths)), "output_tokens": produced,
+        "all_tokens_per_second": round((sum(lengths) + produced) / seconds, 1), "ticks": ticks, "ticks_with_prompt_portions": mixed_ticks,
+        "first_token_seconds_median": round(first_token[len(first_token) // 2], 4),
+        "config": {"model": "Qwen3-8B shape" if name == "mixed8b" else "Qwen3-14B shape", "layers": fields["num_hidden_layers"],
+                   "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
+                   "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
+                   "requests": requests, "new_tokens": new_tokens, "page_size": PAGE_SIZE, "prefill_chunk": PREFILL_TOKENS,
+                   "temperature": params[0].temperature, "cuda_graphs": True},
+    }
+
+
 def prefill_flops(cfg: dict, tokens: int) -> float:
     h, q, kv, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"]
     per_layer = 2 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * inter)
@@ -263,6 +335,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
                         help="run fewer layers than the configuration has (named in the output)")
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b"], default="decode4b",
+                        help="decode4b: the headline measurement (default); the others are the serving workloads of the 8B and 14B shapes")
     parser.add_argument("--profile", choices=["decode", "prefill"],
                         help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = parser.parse_args()
@@ -283,6 +357,9 @@ def main() -> int:
     from pylon_b200.engine import Engine
     from pylon_b200.kernels import ops
 
+    if args.workload != "decode4b":
+        print(json.dumps(run_serving_workload(args.workload, torch)))
+        return 0
     fields = dict(QWEN3_4B, num_hidden_layers=args.layers)
     model_config = Qwen3Config(**fields)
     rng = np.random.default_rng(0)
