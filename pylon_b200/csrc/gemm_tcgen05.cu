@@ -9,7 +9,10 @@
 //               accumulator buffers in tensor memory; tcgen05.commit frees the stage and, after
 //               the last stage of a tile, hands the accumulator to the epilogue
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its quarter of the 128 lanes),
-//               convert and store; with SWIGLU the columns hold gate and up values in
+//               convert, lay 32 rows x 32 or 64 columns out in shared memory in the swizzle a
+//               TMA store expects and let TMA write them (whole sectors, clipped at the
+//               matrix's edge; a lane storing its own row left half-written sectors and cost a
+//               fifth of the time); with SWIGLU the columns hold gate and up values in
 //               alternating groups of 8 and silu(gate) * up is stored, half as wide
 // so the epilogue of one tile overlaps the products of the next.  All waits on mbarriers are
 // bounded: a wait that runs out sets an error word for the host and the block winds down
@@ -53,6 +56,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// Shared memory -> global through a tensor map; the rows and columns outside the matrix are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+               ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+// Until all but the newest `Pending` stores of this thread have read their shared memory.
+template <int Pending>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(Pending) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -99,26 +113,41 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+constexpr int TC_STAGING_BYTES = 4 * 2 * 32 * 128;   // four epilogue warps x two buffers x 32 rows x up to 128 bytes
+
 template <int BN>
 struct TcShared {
-  static constexpr int STAGES = BN == 256 ? 4 : (BN >= 160 ? 5 : 6);
   static constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
-  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int FIT = (227 * 1024 - 1024 /* alignment slack */ - 256 /* barriers */ - TC_STAGING_BYTES) / (A_BYTES + B_BYTES);
+  static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+  static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + TC_STAGING_BYTES + 1024 + 256;
+};
+
+// Columns of the output that one TMA store writes: 64 (128-byte rows, 128-byte swizzle) where the tile's width divides
+// into such groups, else 32 (64-byte rows, 64-byte swizzle).  With SWIGLU an output column takes two of the accumulator.
+template <int BN, bool SWIGLU>
+struct TcStore {
+  static constexpr int COLUMNS = BN % (SWIGLU ? 128 : 64) == 0 ? 64 : 32;
+  static constexpr int ACCUMULATOR_COLUMNS = COLUMNS * (SWIGLU ? 2 : 1);
+  static constexpr int ROW_BYTES = COLUMNS * 2;
+  static constexpr uint32_t SWIZZLE_MASK = ROW_BYTES == 128 ? 7 : 3;   // the 16-byte unit index is XORed with these bits of (offset / 128)
+  static_assert(BN % ACCUMULATOR_COLUMNS == 0, "the tile's width must divide into whole stores");
 };
 
 // error: 0 = fine; otherwise 1 producer, 2 MMA issuer, 3 epilogue gave up waiting.
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       const __grid_constant__ CUtensorMap map_b,
-                                                                      __nv_bfloat16* __restrict__ c, int M, int N, int K,
-                                                                      long long ldc, int* __restrict__ error) {
+                                                                      const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
+                                                                      int* __restrict__ error) {
   using S = TcShared<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* a_tiles = smem;
   unsigned char* b_tiles = smem + (size_t)STAGES * S::A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * S::B_BYTES);
+  unsigned char* staging = b_tiles + (size_t)STAGES * S::B_BYTES;   // 1024-byte aligned: every stage is a multiple of that
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + TC_STAGING_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;      // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
@@ -186,24 +215,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
     }
   } else {
     // Epilogue: warp w reads the quarter (w % 4) of the 128 lanes; lane = output row.
+    using Store = TcStore<BN, SWIGLU>;
     const int quarter = warp & 3;
-    uint32_t round = 0;
+    unsigned char* my_staging = staging + (size_t)quarter * 2 * 32 * 128;
+    const int out_columns = SWIGLU ? N / 2 : N;
+    uint32_t round = 0, staged = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
       const uint32_t buffer = round & 1, buffer_phase = (round >> 1) & 1;
       if (!mbar_wait(&acc_full[buffer], buffer_phase)) { atomicExch(error, 3); break; }
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
+      const int row0 = m0 + quarter * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t raw[32];
-        tc_load_32(taddr + c0, raw);
-        const int col = n0 + c0;
-        if (row < M && col < N) {
-          if (SWIGLU) {
-            // [g0..g7 u0..u7 g8..g15 u8..u15] -> 16 outputs at column col / 2
-            uint32_t packed[8];
+      for (int c0 = 0; c0 < BN; c0 += Store::ACCUMULATOR_COLUMNS, ++staged) {
+        unsigned char* stage_rows = my_staging + (staged & 1) * (32 * 128);
+        if (lane == 0) tma_store_wait_read<1>();   // the store that last read this buffer is two stores back
+        __syncwarp();
+#pragma unroll
+        for (int part = 0; part < Store::ACCUMULATOR_COLUMNS / 32; ++part) {
+          uint32_t raw[32];
+          tc_load_32(taddr + c0 + part * 32, raw);
+          uint32_t packed[16];
+          if (SWIGLU) {   // [g0..g7 u0..u7 g8..g15 u8..u15] -> 16 outputs
 #pragma unroll
             for (int group = 0; group < 2; ++group)
 #pragma unroll
@@ -212,31 +246,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
                 const float u0 = __uint_as_float(raw[group * 16 + 8 + j]), u1 = __uint_as_float(raw[group * 16 + 8 + j + 1]);
                 packed[group * 4 + j / 2] = pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
               }
-            __nv_bfloat16* dst = c + (size_t)row * ldc + col / 2;
-            if (col + 32 <= N) {
-              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-            } else {   // N is a multiple of 16: only the first group is inside
-              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
           } else {
-            __nv_bfloat16* dst = c + (size_t)row * ldc + col;
-            if (col + 32 <= N) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                *reinterpret_cast<uint4*>(dst + j) = make_uint4(
-                    pack2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), pack2(__uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3])),
-                    pack2(__uint_as_float(raw[j + 4]), __uint_as_float(raw[j + 5])), pack2(__uint_as_float(raw[j + 6]), __uint_as_float(raw[j + 7])));
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(raw[j]));
-            }
+            for (int j = 0; j < 16; ++j) packed[j] = pack2(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]));
+          }
+          constexpr int UNITS = SWIGLU ? 2 : 4;   // 16-byte units this part adds to the row
+#pragma unroll
+          for (int unit = 0; unit < UNITS; ++unit) {
+            uint32_t offset = (uint32_t)lane * Store::ROW_BYTES + (uint32_t)(part * UNITS + unit) * 16;
+            offset ^= ((offset >> 7) & Store::SWIZZLE_MASK) << 4;
+            *reinterpret_cast<uint4*>(stage_rows + offset) = make_uint4(packed[unit * 4], packed[unit * 4 + 1], packed[unit * 4 + 2], packed[unit * 4 + 3]);
           }
         }
+        fence_async_shared();   // the writes above, before the TMA engine reads them
+        __syncwarp();
+        const int out_column = (n0 + c0) / (SWIGLU ? 2 : 1);
+        if (lane == 0 && row0 < M && out_column < out_columns) tma_store_2d(&map_c, stage_rows, out_column, row0);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buffer]);   // four warps: the buffer may be overwritten
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   // Wind down: every role comes here, also after a wait that ran out.
@@ -266,16 +297,17 @@ static EncodeTiled encode_tiled() {
   return fn;
 }
 
-// Tensor map of a row-major bfloat16 matrix [rows, cols] (row stride ld elements) with boxes of box_rows x 64 columns.
-static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (row stride ld elements) with boxes of box_rows x box_cols
+// (64 columns: 128-byte swizzle; 32: 64-byte swizzle).
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows, int box_cols = TC_BK) {
   EncodeTiled encode = encode_tiled();
   if (!encode) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t element_strides[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -289,13 +321,23 @@ static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __
     if (err != cudaSuccess) PYLON_REFUSE("gemm_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
+  CUtensorMap map_c;
+  if (!make_map(&map_c, c, M, SWIGLU ? N / 2 : N, ldc, 32, TcStore<BN, SWIGLU>::COLUMNS)) PYLON_REFUSE("gemm_tcgen05: the output's tensor map could not be made");
   const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   const int blocks = tiles < sm_count ? tiles : sm_count;
-  kernel<<<blocks, TC_THREADS, TcShared<BN>::BYTES, stream>>>(map_a, map_b, c, M, N, K, ldc, error);
+  kernel<<<blocks, TC_THREADS, TcShared<BN>::BYTES, stream>>>(map_a, map_b, map_c, M, N, K, error);
   PYLON_CHECK_LAUNCH("gemm_tcgen05");
 }
 
+static int forced_columns = 0;
+
 }  // namespace pylon
+
+// For measurements: every later product uses tiles of 128 x columns (256, 192, 160 or 128); 0 returns to the choice by size.
+extern "C" int pylon_gemm_tcgen05_force_tile(int columns) {
+  pylon::forced_columns = columns;
+  return 0;
+}
 
 // x: bfloat16 [M, K] (row stride ldx), w: bfloat16 [N, K] (row stride ldw), y: bfloat16 [M, N], or [M, N / 2] with swiglu
 // (row stride ldy).  K and the strides multiples of 8, N a multiple of 8 (16 with swiglu), x, w and y 16-byte aligned.
@@ -316,6 +358,8 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
   int bn = 128;
   long long best = -1;
   for (int candidate : {256, 192, 160, 128}) {
+    if (forced_columns && candidate != forced_columns) continue;
+    if (swiglu && candidate == 160) continue;   // 160 accumulator columns do not divide into stores of 32 output columns
     const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
     const long long cost = ((tiles + sm_count - 1) / sm_count) * (candidate + 16);   // + a per-tile overhead
     if (best < 0 || cost < best) { best = cost; bn = candidate; }
@@ -329,8 +373,9 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
     if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);         \
     return launch_tcgen05<BN_, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);                    \
   }
-  PYLON_TC_CASE(256) PYLON_TC_CASE(192) PYLON_TC_CASE(160)
+  PYLON_TC_CASE(256) PYLON_TC_CASE(192)
 #undef PYLON_TC_CASE
+  if (bn == 160) return launch_tcgen05<160, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
 }

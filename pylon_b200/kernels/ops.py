@@ -82,6 +82,7 @@ _SIGNATURES = {
     "gemm_tcgen05.cu": {
         "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                                     c_void_p, c_int, c_void_p],
+        "pylon_gemm_tcgen05_force_tile": [c_int],
     },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -264,8 +265,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """``x [M, K] @ w [N, K].T`` with float32 accumulation.
 
     float32 operands use the plain-FMA kernel (true 32-bit, no tensor cores).  bfloat16
-    operands with up to ``SKINNY_MAX_ROWS`` rows use the weight-streaming kernel; with more
-    rows they go to the library matrix product, as raun6k/Pylon's ``nn.Linear`` layers do
+    operands with up to ``SKINNY_MAX_ROWS`` rows use the weight-streaming kernel; many rows
+    whose 128 x 256 tiles fill whole rounds over the SMs use our tcgen05 kernel; the rest go to
+    the library matrix product, as raun6k/Pylon's ``nn.Linear`` layers do
     (src/pylon/model/layers.py:17-23,95-106).  ``out_dtype=torch.float32`` keeps the 32-bit
     accumulator (used for logits).
     """
@@ -288,8 +290,22 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
         return linear_skinny(x, w, out_dtype)   # few rows (decode): our weight-streaming kernel
     if out_dtype == torch.bfloat16:
+        if _tcgen05_fills_the_sms(m, n) and k % 8 == 0 and n % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            return linear_tcgen05(x, w)
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+def _tcgen05_fills_the_sms(m: int, n: int) -> bool:
+    """Whether a persistent block per SM over 128 x 256 tiles wastes under a fifth of its
+    rounds: there our kernel is level with the library's, elsewhere the library (which
+    splits such products differently) is ahead."""
+    if m < TCGEN05_MIN_ROWS:
+        return False
+    tiles = -(-m // 128) * -(-n // 256)
+    rounds = -(-tiles // _SM_COUNT)
+    return tiles >= 0.8 * rounds * _SM_COUNT
 
 
 PARTIAL_MAX_BLOCKS = 2 * 148   # products with fewer 16-row blocks than this are split over k as well
@@ -342,6 +358,12 @@ def tcgen05_error_word(device: torch.device) -> torch.Tensor:
     if key not in _tcgen05_error:
         _tcgen05_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _tcgen05_error[key]
+
+
+def tcgen05_force_tile(columns: int = 0) -> None:
+    """For measurements: later ``linear_tcgen05`` calls use ``128 x columns`` output tiles
+    (256, 192, 160 or 128); 0 restores the choice by size."""
+    _library("gemm_tcgen05.cu").pylon_gemm_tcgen05_force_tile(columns)
 
 
 def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:

@@ -158,6 +158,31 @@ def test_tcgen05_gemm(m, n, k):
     assert int(ops.tcgen05_error_word(x.device).item()) == 0
 
 
+@pytest.mark.parametrize("columns", [256, 192, 160, 128])
+def test_tcgen05_gemm_every_tile_width(columns):
+    """Each tile width on its own (the choice by size would never take some of them here),
+    with edges inside a tile in both directions, plain and with the SwiGLU epilogue, and
+    with strided views as operands."""
+    from pylon_b200.kernels import ops
+
+    ops.tcgen05_force_tile(columns)
+    try:
+        for m, n, k in [(128, 256, 64), (300, 328, 224), (130, 72, 64), (700, 1224, 512)]:
+            x = torch.randn(m, k + 8, device=DEVICE).to(torch.bfloat16)[:, :k]
+            w = (torch.randn(n, k + 16, device=DEVICE) * 0.05).to(torch.bfloat16)[:, 8:8 + k]
+            torch.testing.assert_close(ops.linear_tcgen05(x, w).double(), x.double() @ w.double().T, rtol=2e-2, atol=2e-2)
+        for m, inter, k in [(256, 128, 64), (300, 104, 96), (600, 1000, 512)]:
+            gate = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+            up = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+            x = torch.randn(m, k, device=DEVICE).to(torch.bfloat16)
+            g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+            got = ops.linear_tcgen05(x, ops.interleave_gate_up(gate, up), swiglu=True)
+            torch.testing.assert_close(got.double(), g * torch.sigmoid(g) * u, rtol=2e-2, atol=2e-2)
+        assert int(ops.tcgen05_error_word(torch.device(DEVICE)).item()) == 0
+    finally:
+        ops.tcgen05_force_tile(0)
+
+
 @pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (2048, 9728, 2560), (130, 104, 96), (500, 224, 96)])
 def test_tcgen05_gemm_with_swiglu_epilogue(m, inter, k):
     from pylon_b200.kernels import ops
