@@ -18,6 +18,10 @@
 // (and j > p - window when a window is set); softmax scale 1/sqrt(d) unless given.
 #include "common.cuh"
 
+#include <cuda.h>
+
+#include <mutex>
+
 #ifndef PYLON_HEAD_DIM
 #define PYLON_HEAD_DIM 128
 #endif
@@ -37,14 +41,17 @@ struct AttentionParams {
   const __nv_bfloat16* k_pages;
   const __nv_bfloat16* v_pages;
   __nv_bfloat16* out;
-  float* partial_out;   // [splits, tokens, nq, D]
+  float* partial_out;   // [splits, tokens, nq, D]: the tiled kernel's splits
   float* partial_lse;   // [splits, tokens, nq]   (log2 domain)
+  float* decode_out;    // [rows * nkv + decode blocks, SMALL_ROWS, D]: the decode kernel's segments
+  float* decode_lse;    // [rows * nkv + decode blocks, SMALL_ROWS]
   const int* q_start;
   const int* kv_len;
   const int* block_table;
-  int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens;
+  int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens, num_rows;
   int small_rows_elsewhere;   // rows of at most SMALL_ROWS packed query rows are left to the decode kernel
-  unsigned* counters;         // [rows * nkv], zero between launches: lets the last split of a decode row combine the splits itself
+  unsigned* counters;         // [rows * nkv], zero between launches: the last block of a decoded (row, KV head) combines its segments
+  int* error;                 // set non-zero when a bounded wait for a TMA copy ran out (the output is then void)
   float scale_log2;     // softmax scale * log2(e)
 };
 
@@ -370,65 +377,211 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
 // a page and is addressed with one table look-up; otherwise keys are gathered one by one.
 // -----------------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 2;   // two stages leave room for three blocks per SM: warps in flight matter more than depth
-constexpr int DEC_STAGE_ELEMS = 2 * TILE_ELEMS;   // keys then values
-constexpr size_t DEC_SMEM = (size_t)(SMALL_ROWS * LD + DEC_STAGES * DEC_STAGE_ELEMS) * sizeof(__nv_bfloat16);
-static_assert(DEC_STAGES * DEC_STAGE_ELEMS * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
 
-__global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(const AttentionParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][LD]
-  __nv_bfloat16* stages = q_tile + SMALL_ROWS * LD;                      // [DEC_STAGES][2][64][LD]
+// Two ways to bring a 64-key tile into shared memory.  With a head size that is a multiple of
+// 64 and pages that are multiples of 64 keys, TMA copies the tile (one elected thread, boxes of
+// 64 keys x 64 values in the 128-byte swizzle, completion on an mbarrier): streaming the cache
+// this way reaches 5.9 TB/s where per-thread 16-byte cp.async copies reached 3.4.  Otherwise
+// every thread gathers 16-byte pieces with cp.async into rows padded by 8 values.
+constexpr bool TMA_HEAD = D % 64 == 0;
+template <bool TMA>
+struct DecodeTiles {
+  static constexpr int ROW = TMA ? D : LD;                        // values between two keys of a box / a padded row
+  static constexpr int TILE = BLOCK_N * ROW;                      // one 64-key tile of keys or of values
+  static constexpr int STAGE = 2 * TILE;                          // keys then values
+  static constexpr size_t STAGE_BYTES = (size_t)DEC_STAGES * STAGE * sizeof(__nv_bfloat16);
+  // stages (1024-byte aligned for the swizzle), query tile, two mbarriers
+  static constexpr size_t SMEM = (TMA ? 1024 : 0) + STAGE_BYTES + (size_t)SMALL_ROWS * LD * sizeof(__nv_bfloat16) + (TMA ? 64 : 0);
+  static_assert(STAGE_BYTES >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
+  // Element offset of the 16-byte piece `chunk` (8 values) of key `row` within a tile.
+  static __device__ __forceinline__ int offset(int row, int chunk) {
+    if (TMA) return (chunk >> 3) * (BLOCK_N * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+    return row * LD + chunk * 8;
+  }
+};
 
-  grid_dependency_wait();
-  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
-  const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+constexpr unsigned ATT_WAIT_LIMIT = 1u << 22;   // try_wait calls before a wait for a TMA copy gives up
+__device__ __forceinline__ void att_mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_address(bar)), "r"(count));
+}
+__device__ __forceinline__ void att_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_address(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, unsigned parity) {
+  for (unsigned tries = 0; tries < ATT_WAIT_LIMIT; ++tries) {
+    unsigned done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(smem_address(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// One box of 64 keys x 64 values; no cluster multicast.
+__device__ __forceinline__ void att_tma_load(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_address(dst)), "l"((unsigned long long)map), "r"(smem_address(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Tiles of 64 keys that a row of decoded tokens (at most SMALL_ROWS packed query rows) walks
+// per KV head, and the first of them; 0 for every other row.
+__device__ __forceinline__ int decode_row_tiles(const AttentionParams& p, int row, int* first_tile) {
   const int q0 = p.q_start[row];
   const int q_len = p.q_start[row + 1] - q0;
-  const int G = p.group;
-  const int packed_rows = q_len * G;
-  if (packed_rows <= 0 || packed_rows > SMALL_ROWS) return;   // larger rows belong to the tiled kernel
-  const int kv_len = p.kv_len[row];
-  const int pos0 = kv_len - q_len;
-  const int* table = p.block_table + (size_t)row * p.table_width;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-
+  const int packed_rows = q_len * p.group;
+  *first_tile = 0;
+  if (packed_rows <= 0 || packed_rows > SMALL_ROWS) return 0;
+  const int pos0 = p.kv_len[row] - q_len;
   const int hi = pos0 + q_len - 1;
   const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
-  const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = first_tile + split * per_split;
-  const int tile_end = min(first_tile + tiles, tile_begin + per_split);
-  const bool contiguous = p.page_size % BLOCK_N == 0;
+  if (hi < lo) return 0;
+  *first_tile = lo / BLOCK_N;
+  return hi / BLOCK_N - lo / BLOCK_N + 1;
+}
 
-  int row_pos[2];
-  bool row_valid[2];
+constexpr int DEC_MIN_TILES = 2;   // a block takes at least this many tiles: below it the merging costs more than the walk
+
+// Decoded rows.  All (row, KV head, tile) triples of the launch form one sequence, row-major,
+// and the blocks cut it into equal runs, so every block reads the same number of bytes however
+// the requests' lengths differ.  A run may end inside a (row, KV head) pair and go on into
+// the next: each piece ("segment") is walked by the block's four warps, 16 keys of every tile
+// each, and merged.  A pair that lies in one block is written out at once; the segments of a
+// pair that spans blocks leave normalised partial results in scratch slot (pair + block), and
+// the block that finishes last (a counter per pair) combines them.
+//
+// map_k, map_v (TMA form only): the page pools as matrices [pages x KV heads x page size, D]
+// with boxes of 64 rows x 64 values.
+template <bool TMA>
+__global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                              const __grid_constant__ CUtensorMap map_v) {
+  using Tiles = DecodeTiles<TMA>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* smem_base = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023) : smem_raw;
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_base);                 // [DEC_STAGES][2][64 keys]
+  __nv_bfloat16* q_tile = stages + DEC_STAGES * Tiles::STAGE;                          // [16][LD]
+  uint64_t* tile_full = reinterpret_cast<uint64_t*>(q_tile + SMALL_ROWS * LD);         // [DEC_STAGES], TMA form
+  __shared__ int plan[3];   // tiles of the launch; the row this block starts in; tiles before that row
+  __shared__ bool last_segment;
+  __shared__ float row_total[SMALL_ROWS];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int G = p.group;
+  if (TMA && threadIdx.x == 0) {
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int m = g + 8 * h;
-    row_valid[h] = m < packed_rows;
-    row_pos[h] = pos0 + (row_valid[h] ? m / G : 0);
+    for (int s = 0; s < DEC_STAGES; ++s) att_mbar_init(&tile_full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-
-  float o[D / 8][4];
+  // The rows' lengths were written long before the kernel ahead of this one started, so the plan
+  // can be made while that kernel finishes; the queries and the newest keys are its work.
+  if (warp == 0) {
+    int unused;
+    const int first_chunk = lane < p.num_rows ? decode_row_tiles(p, lane, &unused) : 0;   // kept: most launches have at most 32 rows
+    int total = first_chunk;
+    for (int base = 32; base < p.num_rows; base += 32) total += base + lane < p.num_rows ? decode_row_tiles(p, base + lane, &unused) : 0;
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
-
-  auto issue = [&](int tile) {
-    if (tile < tile_end) {
-      __nv_bfloat16* dst = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS;
-      if (contiguous) {
-        load_kv_tile_contiguous(dst, p.k_pages, table, tile, kv_len, kv_head, p);
-        load_kv_tile_contiguous(dst + TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
-      } else {
-        load_kv_tile(dst, p.k_pages, table, tile, kv_len, kv_head, p);
-        load_kv_tile(dst + TILE_ELEMS, p.v_pages, table, tile, kv_len, kv_head, p);
+    for (int offset = 16; offset; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+    total *= p.nkv;
+    const int per_block = max(DEC_MIN_TILES, (total + (int)gridDim.x - 1) / (int)gridDim.x);
+    const int begin = blockIdx.x * per_block;
+    int found_row = -1, found_before = 0;
+    if (begin < total) {
+      int before = 0;
+      for (int base = 0; base < p.num_rows && found_row < 0; base += 32) {
+        const int tiles = (base == 0 ? first_chunk : (base + lane < p.num_rows ? decode_row_tiles(p, base + lane, &unused) : 0)) * p.nkv;
+        int inclusive = tiles;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+          const int below = __shfl_up_sync(0xffffffffu, inclusive, offset);
+          if (lane >= offset) inclusive += below;
+        }
+        const int exclusive = before + inclusive - tiles;
+        const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && exclusive <= begin && begin < exclusive + tiles);
+        if (hit) {
+          found_row = base + __ffs(hit) - 1;
+          found_before = __shfl_sync(0xffffffffu, exclusive, __ffs(hit) - 1);
+        }
+        before += __shfl_sync(0xffffffffu, inclusive, 31);
       }
     }
-    cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
-  };
+    if (lane == 0) { plan[0] = total; plan[1] = found_row; plan[2] = found_before; }
+  }
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
+  __syncthreads();
+  const int total_tiles = plan[0];
+  if (plan[1] < 0) return;
+  const int per_block = max(DEC_MIN_TILES, (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x);
+  const int run_end = min(total_tiles, ((int)blockIdx.x + 1) * per_block);
+  const bool contiguous = p.page_size % BLOCK_N == 0;
+  int position = blockIdx.x * per_block, row = plan[1], before = plan[2];
+  unsigned issued = 0, consumed = 0;   // tiles of this block so far: stage = count % DEC_STAGES
 
-  if (tile_begin < tile_end) {
+  while (position < run_end && row < p.num_rows) {
+    int first_tile;
+    const int row_tiles = decode_row_tiles(p, row, &first_tile);
+    if (row_tiles == 0) { ++row; continue; }
+    const int within = position - before;
+    const int kv_head = within / row_tiles;
+    const int tile_begin = first_tile + within % row_tiles;
+    const int tile_end = tile_begin + min(run_end - position, row_tiles - within % row_tiles);
+    const int pair_start = before + kv_head * row_tiles;
+    const int first_block = pair_start / per_block;
+    const int segments = (pair_start + row_tiles - 1) / per_block - first_block + 1;   // blocks this pair lies in
+    const int pair = row * p.nkv + kv_head;
+    position += tile_end - tile_begin;
+
+    const int q0 = p.q_start[row];
+    const int q_len = p.q_start[row + 1] - q0;
+    const int packed_rows = q_len * G;
+    const int kv_len = p.kv_len[row];
+    const int pos0 = kv_len - q_len;
+    const int* table = p.block_table + (size_t)row * p.table_width;
+    if (position - before == row_tiles * p.nkv) { before += row_tiles * p.nkv; ++row; }   // the next segment starts the next row
+
+    int row_pos[2];
+    bool row_valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = g + 8 * h;
+      row_valid[h] = m < packed_rows;
+      row_pos[h] = pos0 + (row_valid[h] ? m / G : 0);
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+
+    auto issue = [&](int tile) {
+      if (tile < tile_end) {
+        __nv_bfloat16* dst = stages + (issued % DEC_STAGES) * Tiles::STAGE;
+        if (TMA) {
+          if (threadIdx.x == 0) {
+            // A tile lies in one page.  Without a page for it the row coordinate points past the
+            // pool and TMA fills the boxes with zeros.
+            const int key0 = tile * BLOCK_N;
+            const int page = table[key0 / p.page_size];
+            const bool page_ok = page >= 0 && page < p.num_pages;
+            const int y = page_ok ? (page * p.nkv + kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
+            uint64_t* bar = &tile_full[issued % DEC_STAGES];
+            att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
+#pragma unroll
+            for (int box = 0; box < D / 64; ++box) {
+              att_tma_load(dst + box * (BLOCK_N * 64), &map_k, bar, box * 64, y);
+              att_tma_load(dst + Tiles::TILE + box * (BLOCK_N * 64), &map_v, bar, box * 64, y);
+            }
+          }
+        } else if (contiguous) {
+          load_kv_tile_contiguous(dst, p.k_pages, table, tile, kv_len, kv_head, p);
+          load_kv_tile_contiguous(dst + Tiles::TILE, p.v_pages, table, tile, kv_len, kv_head, p);
+        } else {
+          load_kv_tile(dst, p.k_pages, table, tile, kv_len, kv_head, p);
+          load_kv_tile(dst + Tiles::TILE, p.v_pages, table, tile, kv_len, kv_head, p);
+        }
+        ++issued;
+      }
+      if (!TMA) cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
+    };
+
     for (int c = threadIdx.x; c < SMALL_ROWS * CHUNKS; c += ATT_THREADS) {
       const int r = c / CHUNKS, col = c % CHUNKS;
       const bool valid = r < packed_rows;
@@ -436,6 +589,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       if (valid) src = p.q + (size_t)(q0 + r / G) * p.q_stride + (size_t)(kv_head * G + r % G) * D + col * 8;
       cp_async_16(q_tile + r * LD + col * 8, src, valid);
     }
+    if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
 
@@ -447,10 +601,34 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
 
     for (int tile = tile_begin; tile < tile_end; ++tile) {
       issue(tile + DEC_STAGES - 1);
-      cp_async_wait<DEC_STAGES - 1>();
-      __syncthreads();
-      const __nv_bfloat16* ks = stages + ((tile - tile_begin) % DEC_STAGES) * DEC_STAGE_ELEMS + warp * 16 * LD;
-      const __nv_bfloat16* vs = ks + TILE_ELEMS;
+      const __nv_bfloat16* ks = stages + (consumed % DEC_STAGES) * Tiles::STAGE;
+      const __nv_bfloat16* vs = ks + Tiles::TILE;
+      if (TMA) {
+        if (tile == tile_begin) {
+          cp_async_wait<0>();
+          __syncthreads();   // the query tile is in
+        }
+        if (!att_mbar_wait(&tile_full[consumed % DEC_STAGES], (consumed / DEC_STAGES) & 1)) {
+          if (p.error) atomicExch(p.error, 1);
+          return;   // every thread of the block gives up on the same copy
+        }
+        if (tile * BLOCK_N + BLOCK_N > kv_len) {
+          // Keys past the row's length are masked, but their values (whatever the page held) still
+          // meet a weight of zero in the product: make them zero, as the gathering form does.
+          const int first_unused = kv_len - tile * BLOCK_N;
+          for (int c = threadIdx.x; c < BLOCK_N * CHUNKS; c += ATT_THREADS) {
+            const int r = c / CHUNKS;
+            if (r >= first_unused) *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vs) + Tiles::offset(r, c % CHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // before TMA writes this stage again
+          __syncthreads();
+        }
+      } else {
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncthreads();
+      }
+      ++consumed;
+      const int key_row = warp * 16 + (lane & 7);   // the key this lane addresses in ldmatrix, before the 8-row offsets
       if (Q_IN_REGISTERS && !q_loaded) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
@@ -466,7 +644,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
         unsigned a_loaded[4], b[4];
         if (!Q_IN_REGISTERS) ldmatrix_x4(a_loaded, q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
         const unsigned (&a)[4] = Q_IN_REGISTERS ? q_frag[Q_IN_REGISTERS ? kk : 0] : a_loaded;
-        ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+        ldmatrix_x4(b, ks + Tiles::offset(key_row + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
         if (kk & 1) {
           mma_bf16(s_odd[0], a, b[0], b[1]);
           mma_bf16(s_odd[1], a, b[2], b[3]);
@@ -528,125 +706,144 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
 #pragma unroll
       for (int d2 = 0; d2 < D / 16; ++d2) {
         unsigned b[4];
-        ldmatrix_x4_trans(b, vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + d2 * 16 + 8 * (lane >> 4));
+        ldmatrix_x4_trans(b, vs + Tiles::offset(key_row + 8 * ((lane >> 3) & 1), d2 * 2 + (lane >> 4)));
         mma_bf16(o[2 * d2], a, b[0], b[1]);
         mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
       }
       __syncthreads();   // everyone is done with this stage before it is loaded again
     }
-    cp_async_wait<0>();
-  }
+    if (!TMA) cp_async_wait<0>();
 
-  // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
-  float* merge_o = reinterpret_cast<float*>(stages);                 // [4][16][D]
-  float* merge_max = merge_o + 4 * SMALL_ROWS * D;                   // [4][16]
-  float* merge_sum = merge_max + 4 * SMALL_ROWS;                     // [4][16]
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    float sum = row_sum[h];
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    const int r = g + 8 * h;
-    if (tq == 0) {
-      merge_max[warp * SMALL_ROWS + r] = row_max[h];
-      merge_sum[warp * SMALL_ROWS + r] = sum;
-    }
-    float* dst = merge_o + ((size_t)warp * SMALL_ROWS + r) * D;
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
-    const int r = e / D, col = e % D;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, merge_max[w * SMALL_ROWS + r]);
-    float total = 0.f, value = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float m = merge_max[w * SMALL_ROWS + r];
-      const float weight = m == -INFINITY ? 0.f : exp2f((m - mx) * p.scale_log2);
-      total += weight * merge_sum[w * SMALL_ROWS + r];
-      value += weight * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
-    }
-    const float inv = total > 0.f ? 1.f / total : 0.f;
-    const size_t token = (size_t)q0 + r / G;
-    const int head = kv_head * G + r % G;
-    if (p.num_splits == 1) {
-      p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(value * inv);
-    } else {
-      const size_t slot = ((size_t)split * p.total_tokens + token) * p.nq + head;
-      p.partial_out[slot * D + col] = value * inv;
-      if (col == 0) p.partial_lse[slot] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;
-    }
-  }
-
-  if (p.num_splits > 1 && p.counters != nullptr) {
-    // The split that finishes last for this (row, KV head) combines all of them; the others
-    // have published their partial results (fence, then the counter).
-    __shared__ bool last_split;
-    __threadfence();
+    // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
+    float* merge_o = reinterpret_cast<float*>(stages);                 // [4][16][D]
+    float* merge_max = merge_o + 4 * SMALL_ROWS * D;                   // [4][16]
+    float* merge_sum = merge_max + 4 * SMALL_ROWS;                     // [4][16]
     __syncthreads();
-    unsigned* counter = p.counters + (size_t)row * p.nkv + kv_head;
-    if (threadIdx.x == 0) last_split = atomicAdd(counter, 1u) == (unsigned)p.num_splits - 1u;
-    __syncthreads();
-    if (!last_split) return;
-    __threadfence();
-    const size_t items = (size_t)p.total_tokens * p.nq;
-    // The splits' weights first (one trip to L2 for all of them), then the weighted sum with
-    // several partial results in flight per thread.
-    float* weights = reinterpret_cast<float*>(stages);   // [SMALL_ROWS][splits]; the stages are idle now
-    __shared__ float row_total[SMALL_ROWS];
-    const int splits = p.num_splits;
-    __syncthreads();
-    for (int e = threadIdx.x; e < packed_rows * splits; e += ATT_THREADS) {
-      const int r = e / splits, s2 = e % splits;
-      const size_t item = ((size_t)q0 + r / G) * p.nq + kv_head * G + r % G;
-      weights[r * splits + s2] = __ldcg(p.partial_lse + (size_t)s2 * items + item);
-    }
-    __syncthreads();
-    if (threadIdx.x < packed_rows) {
-      const int r = threadIdx.x;
-      float mx = -INFINITY;
-      for (int s2 = 0; s2 < splits; ++s2) mx = fmaxf(mx, weights[r * splits + s2]);
-      float total = 0.f;
-      for (int s2 = 0; s2 < splits; ++s2) {
-        const float lse = weights[r * splits + s2];
-        const float weight = lse == -INFINITY ? 0.f : exp2f(lse - mx);
-        weights[r * splits + s2] = weight;
-        total += weight;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float sum = row_sum[h];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      const int r = g + 8 * h;
+      if (tq == 0) {
+        merge_max[warp * SMALL_ROWS + r] = row_max[h];
+        merge_sum[warp * SMALL_ROWS + r] = sum;
       }
-      row_total[r] = total;
+      float* dst = merge_o + ((size_t)warp * SMALL_ROWS + r) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     __syncthreads();
+    const size_t slot = (size_t)pair + blockIdx.x;
     for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
       const int r = e / D, col = e % D;
-      const size_t item = ((size_t)q0 + r / G) * p.nq + kv_head * G + r % G;
-      const float* src = p.partial_out + item * D + col;
-      float value = 0.f;
-      int s2 = 0;
-      for (; s2 + 4 <= splits; s2 += 4) {
-        const float v0 = __ldcg(src + (size_t)(s2 + 0) * items * D), v1 = __ldcg(src + (size_t)(s2 + 1) * items * D);
-        const float v2 = __ldcg(src + (size_t)(s2 + 2) * items * D), v3 = __ldcg(src + (size_t)(s2 + 3) * items * D);
-        value += weights[r * splits + s2] * v0 + weights[r * splits + s2 + 1] * v1 + weights[r * splits + s2 + 2] * v2 + weights[r * splits + s2 + 3] * v3;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mx = fmaxf(mx, merge_max[w * SMALL_ROWS + r]);
+      float total = 0.f, value = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float m = merge_max[w * SMALL_ROWS + r];
+        const float weight = m == -INFINITY ? 0.f : exp2f((m - mx) * p.scale_log2);
+        total += weight * merge_sum[w * SMALL_ROWS + r];
+        value += weight * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
       }
-      for (; s2 < splits; ++s2) value += weights[r * splits + s2] * __ldcg(src + (size_t)s2 * items * D);
-      const float total = row_total[r];
-      p.out[item * D + col] = __float2bfloat16_rn(total > 0.f ? value / total : 0.f);
+      const float inv = total > 0.f ? 1.f / total : 0.f;
+      if (segments == 1) {
+        const size_t token = (size_t)q0 + r / G;
+        const int head = kv_head * G + r % G;
+        p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(value * inv);
+      } else {
+        p.decode_out[(slot * SMALL_ROWS + r) * D + col] = value * inv;
+        if (col == 0) p.decode_lse[slot * SMALL_ROWS + r] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;
+      }
     }
-    if (threadIdx.x == 0) *counter = 0u;   // ready for the next launch
+
+    if (segments > 1) {
+      // The block that finishes last for this (row, KV head) combines the segments; the others
+      // have published their partial results (fence, then the counter).
+      __threadfence();
+      __syncthreads();
+      unsigned* counter = p.counters + pair;
+      if (threadIdx.x == 0) last_segment = atomicAdd(counter, 1u) == (unsigned)segments - 1u;
+      __syncthreads();
+      if (last_segment) {
+        __threadfence();
+        // The segments' weights first (one trip to L2 for all of them), then the weighted sum
+        // with several partial results in flight per thread.
+        float* weights = reinterpret_cast<float*>(stages);   // [packed_rows][segments]; the stages are idle now
+        const size_t slot0 = (size_t)pair + first_block;
+        for (int e = threadIdx.x; e < packed_rows * segments; e += ATT_THREADS) {
+          const int r = e / segments, s2 = e % segments;
+          weights[e] = __ldcg(p.decode_lse + (slot0 + s2) * SMALL_ROWS + r);
+        }
+        __syncthreads();
+        if (threadIdx.x < packed_rows) {
+          const int r = threadIdx.x;
+          float mx = -INFINITY;
+          for (int s2 = 0; s2 < segments; ++s2) mx = fmaxf(mx, weights[r * segments + s2]);
+          float total = 0.f;
+          for (int s2 = 0; s2 < segments; ++s2) {
+            const float lse = weights[r * segments + s2];
+            const float weight = lse == -INFINITY ? 0.f : exp2f(lse - mx);
+            weights[r * segments + s2] = weight;
+            total += weight;
+          }
+          row_total[r] = total;
+        }
+        __syncthreads();
+        // Four values per thread and eight segments' loads in flight: the trips to L2 are what this
+        // block waits for, so they must overlap, not follow one another.
+        constexpr int SLOT_VECTORS = SMALL_ROWS * D / 4;
+        const float4* partials = reinterpret_cast<const float4*>(p.decode_out + slot0 * SMALL_ROWS * D);
+        for (int v = threadIdx.x; v < packed_rows * (D / 4); v += ATT_THREADS) {
+          const int r = v / (D / 4), col = (v % (D / 4)) * 4;
+          const float* w = weights + r * segments;
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s2 = 0; s2 < segments; s2 += 8) {
+            float4 part[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) part[j] = __ldcg(partials + (size_t)min(s2 + j, segments - 1) * SLOT_VECTORS + v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float weight = s2 + j < segments ? w[s2 + j] : 0.f;
+              sum.x += weight * part[j].x; sum.y += weight * part[j].y; sum.z += weight * part[j].z; sum.w += weight * part[j].w;
+            }
+          }
+          const float inv = row_total[r] > 0.f ? 1.f / row_total[r] : 0.f;
+          const size_t token = (size_t)q0 + r / G;
+          const int head = kv_head * G + r % G;
+          __nv_bfloat16* dst = p.out + (token * p.nq + head) * D + col;
+          *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(sum.x * inv, sum.y * inv), pack_bf16(sum.z * inv, sum.w * inv));
+        }
+        if (threadIdx.x == 0) *counter = 0u;   // ready for the next launch
+      }
+    }
+    if (TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the merge buffers were written where TMA writes next
+    __syncthreads();   // the query tile and the stages are free for the next segment
   }
 }
 
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
 // warp per (token, head).
+// skip_small: tokens of rows with at most SMALL_ROWS packed query rows are left alone (the decode
+// kernel wrote them).
 __global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
-                                      __nv_bfloat16* __restrict__ out, int num_splits, long long items) {
+                                      __nv_bfloat16* __restrict__ out, int num_splits, long long items, const int* __restrict__ q_start,
+                                      int num_rows, int nq, int group, int skip_small) {
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= items) return;
+  if (skip_small) {
+    const int token = (int)(item / nq);
+    int lo = 0, hi = num_rows - 1;   // the last row that starts at or before the token
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (q_start[mid] <= token) lo = mid; else hi = mid - 1;
+    }
+    if ((q_start[lo + 1] - q_start[lo]) * group <= SMALL_ROWS) return;
+  }
   const int lane = threadIdx.x & 31;
   float mx = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, partial_lse[(size_t)s * items + item]);
@@ -684,40 +881,123 @@ using namespace pylon;
 
 extern "C" int pylon_attention_head_dim() { return D; }
 
-// Scratch floats needed for `num_splits` splits over `total_tokens` tokens (0 for one split).
-extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_tokens, int nq) {
-  if (num_splits <= 1) return 0;
-  return (long long)num_splits * total_tokens * nq * (D + 1);
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) != cudaSuccess || result != cudaDriverEntryPointSuccess)
+      symbol = nullptr;
+    return (EncodeTiled)symbol;
+  }();
+  return fn;
+}
+
+// Tensor map of a page pool [pages, KV heads, page size, D] seen as a matrix of rows of D values, boxes of 64 rows x 64
+// values in the 128-byte swizzle.  The last few maps are kept: a model asks for the same pools at every step.
+static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
+  struct Known { const void* pages; long long rows; CUtensorMap map; };
+  static Known known[64];
+  static int count = 0, next = 0;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> guard(mutex);
+  for (int i = 0; i < count; ++i)
+    if (known[i].pages == pages && known[i].rows == rows) { *map = known[i].map; return true; }
+  EncodeTiled encode = encode_tiled();
+  if (!encode) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(__nv_bfloat16)};
+  cuuint32_t box[2] = {64, (cuuint32_t)BLOCK_N};
+  cuuint32_t element_strides[2] = {1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  known[next].pages = pages; known[next].rows = rows; known[next].map = *map;
+  next = (next + 1) % 64;
+  if (count < 64) ++count;
+  return true;
+}
+
+constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
+constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA : DEC_SMEM_GATHER;
+
+// Blocks of the decode kernel: as many as are resident at once (of the form that needs more
+// shared memory), and few enough that the weights of a pair's segments (at most blocks + 2 of
+// them, 16 rows each) fit where the combining block keeps them.
+extern "C" int pylon_attention_decode_blocks() {
+  static int blocks = 0;
+  if (blocks == 0) {
+    int device = 0, sm_count = 0, per_sm = 0, per_sm_tma = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+    if (cudaFuncSetAttribute(paged_attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_GATHER) != cudaSuccess) return -1;
+    if (cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA) != cudaSuccess) return -1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, paged_attention_decode_kernel<false>, ATT_THREADS, DEC_SMEM_GATHER) != cudaSuccess || per_sm < 1) return -1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_tma, paged_attention_decode_kernel<TMA_HEAD>, ATT_THREADS, DEC_SMEM_TMA) != cudaSuccess || per_sm_tma < 1) return -1;
+    if (per_sm_tma < per_sm) per_sm = per_sm_tma;
+    const int cap = (int)(DecodeTiles<TMA_HEAD>::STAGE_BYTES / (SMALL_ROWS * sizeof(float))) - 2;   // the smaller of the two forms' stages
+    blocks = per_sm * sm_count < cap ? per_sm * sm_count : cap;
+  }
+  return blocks;
+}
+
+// Scratch floats a call needs: `num_splits` splits of the tiled kernel over `total_tokens`
+// tokens (none for one split) and the decode kernel's segment slots (none for decode_blocks = 0).
+extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_tokens, int nq, int num_rows, int nkv, int decode_blocks) {
+  long long floats = 0;
+  if (num_splits > 1) floats += (long long)num_splits * total_tokens * nq * (D + 1);
+  if (decode_blocks > 0) floats += ((long long)num_rows * nkv + decode_blocks) * SMALL_ROWS * (D + 1);
+  return floats;
 }
 
 // q: bfloat16 [tokens, >= nq*D] with q_stride elements between tokens; pages: bfloat16
 // [num_pages, nkv, page_size, D]; out: bfloat16 [tokens, nq, D]; q_start: int32 [rows + 1];
 // kv_len: int32 [rows]; block_table: int32 [rows, table_width]; max_q: the longest row (or an
-// upper bound); scratch: float32, pylon_attention_scratch_floats() long when num_splits > 1;
-// counters: null, or num_rows * nkv unsigned integers that are zero before the call (and zero
-// again after it): with them the splits of decoded rows are combined inside the attention
-// kernel instead of by a second launch.
+// upper bound); num_splits: key/value splits of rows with more than 16 packed query rows;
+// decode_blocks: blocks of the kernel for the other rows (1 .. pylon_attention_decode_blocks());
+// scratch: float32, pylon_attention_scratch_floats() long, contents arbitrary; counters:
+// num_rows * nkv unsigned integers that are zero before the call (and zero again after it).
+// scratch and counters may be null when num_splits = 1 and no row can have 16 packed rows or fewer
+// (one row and max_q * group > 16).  error: null, or one int in device memory that a kernel sets
+// non-zero when its bounded wait for a TMA copy ran out (the output is then void).
 extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
                                          const int* block_table, int table_width, int page_size, int num_pages,
                                          int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
-                                         int max_q, int num_splits, cudaStream_t stream) {
+                                         int max_q, int num_splits, int decode_blocks, int* error, cudaStream_t stream) {
   if (num_rows <= 0 || total_tokens <= 0) return 0;
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_mma: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 1 || table_width < 1 || window < 0 || max_q < 1 || num_splits < 1)
     PYLON_REFUSE("paged_attention_mma: page size %d, table width %d, window %d, longest row %d, splits %d", page_size,
                  table_width, window, max_q, num_splits);
-  if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 4) || (q_stride % 8))
+  if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 8) || (q_stride % 8))
     PYLON_REFUSE("paged_attention_mma: q and pages must be 16-byte aligned and the token stride a multiple of 8");
   if (!(scale > 0.f)) PYLON_REFUSE("paged_attention_mma: the softmax scale must be positive");
-  if (num_splits > 1 && scratch == nullptr) PYLON_REFUSE("paged_attention_mma: splits need scratch memory");
   if (nkv > 65535 || num_rows > 65535) PYLON_REFUSE("paged_attention_mma: %d KV heads, %d rows", nkv, num_rows);
+  const int group = nq / nkv;
+  const long long packed_max = (long long)max_q * group;
+  const bool any_large = packed_max > SMALL_ROWS;
+  const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
+  if (!any_large) num_splits = 1;                        // no row for the tiled kernel
+  if (num_splits > 1 && scratch == nullptr) PYLON_REFUSE("paged_attention_mma: splits need scratch memory");
+  if (maybe_small) {
+    const int most = pylon_attention_decode_blocks();
+    if (most < 1) PYLON_REFUSE("paged_attention_mma: the decode kernel does not fit on this device");
+    if (decode_blocks < 1 || decode_blocks > most) PYLON_REFUSE("paged_attention_mma: %d decode blocks, 1 to %d are possible", decode_blocks, most);
+    if (scratch == nullptr || counters == nullptr) PYLON_REFUSE("paged_attention_mma: rows of decoded tokens need scratch memory and counters");
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_1);
     if (err == cudaSuccess && WIDE_TILES)
       err = cudaFuncSetAttribute(paged_attention_mma_kernel<WIDE_TILES ? 2 : 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_2);
-    if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_GATHER);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA);
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
   }
@@ -726,15 +1006,23 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
   p.out = (__nv_bfloat16*)out;
   const long long items = (long long)total_tokens * nq;
-  p.partial_out = scratch; p.partial_lse = scratch ? scratch + (size_t)num_splits * items * D : nullptr;
+  float* decode_scratch = scratch;
+  p.partial_out = p.partial_lse = nullptr;
+  if (num_splits > 1) {
+    p.partial_out = scratch;
+    p.partial_lse = scratch + (size_t)num_splits * items * D;
+    decode_scratch = scratch + (size_t)num_splits * items * (D + 1);
+  }
+  const size_t slots = (size_t)num_rows * nkv + (maybe_small ? decode_blocks : 0);
+  p.decode_out = decode_scratch;
+  p.decode_lse = decode_scratch ? decode_scratch + slots * SMALL_ROWS * D : nullptr;
   p.counters = counters;
+  p.error = error;
   p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
-  p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
+  p.nq = nq; p.nkv = nkv; p.group = group; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
+  p.num_rows = num_rows;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const long long packed_max = (long long)max_q * p.group;
-  const bool any_large = packed_max > SMALL_ROWS;
-  const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
   p.small_rows_elsewhere = maybe_small ? 1 : 0;
   if (any_large) {
     // 128-row blocks when the rows are long enough to fill them and the accumulators fit.
@@ -749,13 +1037,22 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
       paged_attention_mma_kernel<1><<<grid, ATT_THREADS, ATT_SMEM_1, stream>>>(p);
   }
   if (maybe_small) {
-    dim3 grid(num_splits, nkv, num_rows);
-    launch_dependent(paged_attention_decode_kernel, grid, dim3(ATT_THREADS), DEC_SMEM, stream, p);
+    CUtensorMap map_k = {}, map_v = {};
+    const long long pool_rows = (long long)num_pages * nkv * page_size;
+    const bool tma = TMA_HEAD && page_size % BLOCK_N == 0 && pool_rows < 2147483647LL - BLOCK_N;
+    if (tma) {
+      if (!page_pool_map(&map_k, k_pages, pool_rows) || !page_pool_map(&map_v, v_pages, pool_rows))
+        PYLON_REFUSE("paged_attention_mma: the tensor maps of the page pools could not be made");
+      launch_dependent(paged_attention_decode_kernel<TMA_HEAD>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_TMA, stream, p, map_k, map_v);
+    } else {
+      launch_dependent(paged_attention_decode_kernel<false>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_GATHER, stream, p, map_k, map_v);
+    }
   }
-  if (num_splits > 1 && (any_large || counters == nullptr)) {
+  if (num_splits > 1) {
     const int warps = 4;
     launch_dependent(combine_splits_kernel, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
-                     (const float*)p.partial_out, (const float*)p.partial_lse, p.out, num_splits, items);
+                     (const float*)p.partial_out, (const float*)p.partial_lse, p.out, num_splits, items, q_start, num_rows, nq, group,
+                     maybe_small ? 1 : 0);
   }
   PYLON_CHECK_LAUNCH("paged_attention_mma");
 }

@@ -9,20 +9,26 @@
 //
 // Rules of use:
 //  * The scratch is PYLON_STATIC_SCRATCH_FLOATS floats (16 MiB).  A call needs
-//    num_splits * total_tokens * nq * (head size + 1) floats when num_splits > 1 and none
-//    otherwise; a call that needs more is refused with an error text and launches nothing.
-//  * The first call on each device looks up the array's device address and raises the
+//    pylon_attention_scratch_floats() of them: room for the splits of long rows and for the
+//    segments of decoded rows.  The number of blocks for decoded rows is chosen here, as
+//    many as the device holds at once, fewer if the scratch would not hold their slots; a
+//    call that needs more than the array even then is refused with an error text and
+//    launches nothing.
+//  * The counters by which the blocks of a decoded row find out which of them is last are a
+//    second fixed array (PYLON_STATIC_COUNTERS entries; rows x KV heads beyond that are
+//    refused).  They start at zero when the library is loaded and every launch that runs to
+//    its end leaves them at zero.
+//  * The first call on each device looks up the arrays' device addresses and raises the
 //    kernels' shared-memory limit.  Make that first call outside any stream capture; later
 //    calls only launch kernels and may be captured like any other launch.
-//  * All calls on a device share the one array, and it keeps what the last call left.
+//  * All calls on a device share the arrays, and the scratch keeps what the last call left.
 //    Nothing in it has to start at zero: every slot a call reads was written earlier in
 //    the same call.  But two calls whose kernels overlap on the GPU (different streams, or
-//    graphs replayed side by side) race on it; keep calls that use splits in one stream
-//    order.
+//    graphs replayed side by side) race on them; keep calls in one stream order.
 //  * No cudaMalloc, cudaFree or allocating library routine is called, here or in the kernels.
 //
-// The array's name is a host-side handle in host code, not a device address; the address the
-// kernels get comes from cudaGetSymbolAddress, once per device, with that device current.
+// The arrays' names are host-side handles in host code, not device addresses; the addresses
+// the kernels get come from cudaGetSymbolAddress, once per device, with that device current.
 #include "attention_static.h"
 
 #include <mutex>
@@ -30,15 +36,19 @@
 #include "attention_mma.cu"
 
 static __device__ __align__(256) float pylon_static_scratch[PYLON_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned pylon_static_counters[PYLON_STATIC_COUNTERS];
+static __device__ int pylon_static_error;   // set by a kernel whose bounded wait for a TMA copy ran out
 
 namespace {
 constexpr int MAX_DEVICES = 64;
 float* scratch_of_device[MAX_DEVICES] = {nullptr};
+unsigned* counters_of_device[MAX_DEVICES] = {nullptr};
+int* error_of_device[MAX_DEVICES] = {nullptr};
 std::mutex setup_mutex;
 
-// Device address of the built-in scratch on the current device (nullptr and an error text
-// if the runtime refuses).
-float* static_scratch_address() {
+// Device addresses of the built-in scratch and counters on the current device (nullptr and an
+// error text if the runtime refuses).
+float* static_scratch_address(unsigned** counters, int** error) {
   int device = -1;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
@@ -54,13 +64,37 @@ float* static_scratch_address() {
       snprintf(pylon::last_error_buffer(), 512, "paged_attention_mma_static: cudaGetSymbolAddress failed (%s)", cudaGetErrorString(err));
       return nullptr;
     }
+    unsigned* counter_address = nullptr;
+    err = cudaGetSymbolAddress((void**)&counter_address, pylon_static_counters);
+    if (err != cudaSuccess || counter_address == nullptr) {
+      snprintf(pylon::last_error_buffer(), 512, "paged_attention_mma_static: cudaGetSymbolAddress failed (%s)", cudaGetErrorString(err));
+      return nullptr;
+    }
+    int* error_address = nullptr;
+    err = cudaGetSymbolAddress((void**)&error_address, pylon_static_error);
+    if (err != cudaSuccess || error_address == nullptr) {
+      snprintf(pylon::last_error_buffer(), 512, "paged_attention_mma_static: cudaGetSymbolAddress failed (%s)", cudaGetErrorString(err));
+      return nullptr;
+    }
+    counters_of_device[device] = counter_address;
+    error_of_device[device] = error_address;
     scratch_of_device[device] = address;
   }
+  *counters = counters_of_device[device];
+  *error = error_of_device[device];
   return scratch_of_device[device];
 }
 }  // namespace
 
 extern "C" long long pylon_static_scratch_floats() { return (long long)PYLON_STATIC_SCRATCH_FLOATS; }
+
+// 0, or non-zero after a kernel of an earlier call on the current device gave up waiting for a TMA copy (its output is
+// void); -1 if the word cannot be read.  Synchronises the device.
+extern "C" int pylon_static_error_word() {
+  int value = -1;
+  if (cudaMemcpyFromSymbol(&value, pylon_static_error, sizeof(int)) != cudaSuccess) return -1;
+  return value;
+}
 
 extern "C" int pylon_paged_attention_mma_static(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                                 void* out, const int* q_start, const int* kv_len, const int* block_table,
@@ -68,13 +102,27 @@ extern "C" int pylon_paged_attention_mma_static(const void* q, long long q_strid
                                                 float scale, int num_rows, int total_tokens, int max_q, int num_splits,
                                                 cudaStream_t stream) {
   if (num_rows <= 0 || total_tokens <= 0) return 0;
-  if (num_splits < 1 || nq < 1) PYLON_REFUSE("paged_attention_mma_static: splits %d, query heads %d", num_splits, nq);
-  const long long needed = pylon_attention_scratch_floats(num_splits, total_tokens, nq);
+  if (num_splits < 1 || nq < 1 || nkv < 1 || max_q < 1) PYLON_REFUSE("paged_attention_mma_static: splits %d, query heads %d, KV heads %d, longest row %d", num_splits, nq, nkv, max_q);
+  // Rows of decoded tokens (at most 16 packed query rows) can occur unless the call is one long row.
+  const bool maybe_small = (long long)max_q * (nq / nkv) <= pylon::SMALL_ROWS || num_rows > 1;
+  int decode_blocks = 0;
+  if (maybe_small) {
+    if ((long long)num_rows * nkv > (long long)PYLON_STATIC_COUNTERS)
+      PYLON_REFUSE("paged_attention_mma_static: %d rows x %d KV heads need more than the %u built-in counters", num_rows, nkv, PYLON_STATIC_COUNTERS);
+    decode_blocks = pylon_attention_decode_blocks();
+    if (decode_blocks < 1) PYLON_REFUSE("paged_attention_mma_static: the decode kernel does not fit on this device");
+    while (decode_blocks > 1 && pylon_attention_scratch_floats(num_splits, total_tokens, nq, num_rows, nkv, decode_blocks) > (long long)PYLON_STATIC_SCRATCH_FLOATS)
+      decode_blocks /= 2;
+  }
+  const long long needed = pylon_attention_scratch_floats(num_splits, total_tokens, nq, num_rows, nkv, decode_blocks);
   if (needed > (long long)PYLON_STATIC_SCRATCH_FLOATS)
-    PYLON_REFUSE("paged_attention_mma_static: %d splits over %d tokens and %d heads need %lld floats of scratch; the built-in scratch holds %u",
-                 num_splits, total_tokens, nq, needed, PYLON_STATIC_SCRATCH_FLOATS);
-  float* scratch = static_scratch_address();
+    PYLON_REFUSE("paged_attention_mma_static: %d splits over %d tokens and %d heads, %d rows and %d decode blocks need %lld floats of scratch; the built-in scratch holds %u",
+                 num_splits, total_tokens, nq, num_rows, decode_blocks, needed, PYLON_STATIC_SCRATCH_FLOATS);
+  unsigned* counters = nullptr;
+  int* error = nullptr;
+  float* scratch = static_scratch_address(&counters, &error);
   if (scratch == nullptr) return -2;
-  return pylon_paged_attention_mma(q, q_stride, k_pages, v_pages, out, scratch, nullptr, q_start, kv_len, block_table, table_width,
-                                   page_size, num_pages, nq, nkv, window, scale, num_rows, total_tokens, max_q, num_splits, stream);
+  return pylon_paged_attention_mma(q, q_stride, k_pages, v_pages, out, scratch, counters, q_start, kv_len, block_table, table_width,
+                                   page_size, num_pages, nq, nkv, window, scale, num_rows, total_tokens, max_q, num_splits, decode_blocks, error,
+                                   stream);
 }

@@ -7,8 +7,8 @@
 // cache pool (a later cudaMalloc there simply fails), code inside a latency-critical loop
 // where an allocator call may synchronise the device, and hosts that embed the library
 // without PyTorch's allocator at all.  Such callers own their inputs and outputs already;
-// the only memory the split-KV attention needs beyond those is its scratch for partial
-// results, and this entry point keeps that scratch inside the library.
+// the only memory the attention needs beyond those is its scratch for partial results and a
+// counter per (row, KV head), and this entry point keeps both inside the library.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -16,11 +16,14 @@
 // Floats of scratch built into the library: 4 Mi floats = 16 MiB, held on every GPU that
 // loads the library until the process exits.
 #define PYLON_STATIC_SCRATCH_FLOATS (4u * 1024u * 1024u)
+// Built-in counters, one per (row, KV head) of a call.
+#define PYLON_STATIC_COUNTERS (64u * 1024u)
 
 extern "C" {
 
-// Same arguments and result as pylon_paged_attention_mma without the scratch pointer; see
-// attention_static.cu for the rules of use.
+// Same arguments and result as pylon_paged_attention_mma without the scratch pointer, the
+// counters and the number of decode blocks (chosen here); see attention_static.cu for the
+// rules of use.
 int pylon_paged_attention_mma_static(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                      void* out, const int* q_start, const int* kv_len, const int* block_table,
                                      int table_width, int page_size, int num_pages, int nq, int nkv, int window,
@@ -29,4 +32,8 @@ int pylon_paged_attention_mma_static(const void* q, long long q_stride, const vo
 
 // Floats of built-in scratch (PYLON_STATIC_SCRATCH_FLOATS), for callers that size their batches by it.
 long long pylon_static_scratch_floats();
+
+// 0, or non-zero after a kernel of an earlier call on the current device gave up waiting for one of
+// its TMA copies (that call's output is void); -1 if the word cannot be read.  Synchronises the device.
+int pylon_static_error_word();
 }

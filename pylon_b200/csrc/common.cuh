@@ -110,18 +110,22 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-// Off unless PYLON_B200_PDL=1 is in the environment: measured on the decode step of the
-// Qwen3-4B shape it changed nothing (3.96 ms with, 3.89 ms without), so the ordinary launch
-// stays the default.
-inline bool dependent_launch_enabled() {
-  static const bool enabled = [] {
+// Off unless PYLON_B200_PDL is in the environment ("1": every launch made through
+// launch_dependent; "gemm": only the weight-streaming products, whose first weight loads do not
+// depend on the kernel before them).  Measured on the decode step of the Qwen3-4B shape, "1"
+// changed nothing or cost a few percent, so the ordinary launch stays the default.
+enum LaunchKind { LAUNCH_OTHER = 0, LAUNCH_GEMM = 1 };
+inline bool dependent_launch_enabled(LaunchKind kind) {
+  static const int mode = [] {
     const char* value = getenv("PYLON_B200_PDL");
-    return value && value[0] == '1';
+    if (!value) return 0;
+    if (value[0] == '1') return 1;
+    return value[0] == 'g' ? 2 : 0;
   }();
-  return enabled;
+  return mode == 1 || (mode == 2 && kind == LAUNCH_GEMM);
 }
 
-template <typename... KernelArgs, typename... Args>
+template <LaunchKind KIND = LAUNCH_OTHER, typename... KernelArgs, typename... Args>
 inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
@@ -132,7 +136,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, di
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  config.numAttrs = dependent_launch_enabled(KIND) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 

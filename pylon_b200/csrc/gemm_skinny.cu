@@ -200,7 +200,7 @@ static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y
     }
   }
   const int blocks = (N + NT * 16 - 1) / (NT * 16);
-  launch_dependent(kernel, dim3(blocks, k_splits), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks, k_splits), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
   PYLON_CHECK_LAUNCH("gemm_skinny");
 }
 

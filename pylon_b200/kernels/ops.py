@@ -92,8 +92,9 @@ _SIGNATURES = {
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                      c_int, c_int, c_void_p],
-        "pylon_attention_scratch_floats": [c_int, c_int, c_int],
+                                      c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_attention_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "pylon_attention_decode_blocks": [],
     },
     "sampling.cu": {
         "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -430,30 +431,33 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------
 # attention over the paged cache
 # ---------------------------------------------------------------------------------------
-def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:
-    """How many key/value splits an attention launch uses.
+_attention_error: dict[str, torch.Tensor] = {}
 
-    Steps with long rows (prefill) have enough query tiles to fill the GPU and use one.  For
-    rows of decoded tokens the blocks are (rows x KV heads x splits), two resident per SM:
-    the number of splits is the one with the least estimated time, waves x (tiles per split
-    + a fixed start-up cost), so that the last wave is not mostly empty.
+
+def attention_error_word(device: torch.device) -> torch.Tensor:
+    """The int32 word the attention kernels set when a bounded wait for one of their TMA copies
+    ran out (the output of that launch is then void).  Zero in every healthy run."""
+    key = str(device)
+    if key not in _attention_error:
+        _attention_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _attention_error[key]
+
+
+def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:
+    """How many key/value splits the tiled attention kernel uses for rows with more than 16
+    packed query rows (tokens x group).
+
+    Steps with long rows (prefill) have enough query tiles to fill the GPU and use one; a few
+    short portions over a long context are split so that two blocks per SM have work.  Rows
+    of decoded tokens do not use this: their kernel cuts all rows' tiles into equal runs.
     """
+    if max_q * group <= 16:
+        return 1
     kv_tiles = max(1, -(-max_kv // 64))
-    slots = 2 * _SM_COUNT
-    if max_q * group > 16:
-        blocks = num_rows * nkv * -(-max_q * group // 64)
-        if blocks >= _SM_COUNT or kv_tiles == 1:
-            return 1
-        return int(max(1, min(kv_tiles, 64, slots // blocks)))
-    blocks = num_rows * nkv
-    slots = 3 * _SM_COUNT      # the decode kernel fits three blocks on an SM
-    best, best_cost = 1, None
-    for splits in range(1, min(kv_tiles, 64) + 1):
-        waves = -(-blocks * splits // slots)
-        cost = waves * (-(-kv_tiles // splits) + 4)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = splits, cost
-    return best
+    blocks = num_rows * nkv * -(-max_q * group // 64)
+    if blocks >= _SM_COUNT or kv_tiles == 1:
+        return 1
+    return int(max(1, min(kv_tiles, 64, 2 * _SM_COUNT // blocks)))
 
 
 _SM_COUNT = 148
@@ -476,6 +480,7 @@ def paged_attention(
     out: Optional[torch.Tensor] = None,
     num_splits: Optional[int] = None,
     force_simple: bool = False,
+    decode_blocks: Optional[int] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
@@ -485,7 +490,8 @@ def paged_attention(
     int32 ``[rows]`` (tokens each row holds after this step, so a row's first new token is
     at position ``kv_len - (q_start[r + 1] - q_start[r])``); ``block_table`` int32
     ``[rows, width]``; ``max_q``/``max_kv``: longest row and longest context (upper bounds
-    are fine).  Returns ``[T, nq * d]``.
+    are fine).  ``num_splits`` and ``decode_blocks`` override the split of long rows' keys and
+    the number of blocks that share the decoded rows' tiles (for tests).  Returns ``[T, nq * d]``.
 
     bfloat16 with a head size that is a multiple of 16 up to 256 runs on the tensor cores
     (built per head size on first use); float32, and other head sizes up to 512, take the
@@ -511,14 +517,21 @@ def paged_attention(
     if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
         splits = attention_splits(rows, nkv, nq // nkv, max_q, max_kv) if num_splits is None else int(num_splits)
-        scratch = None
-        if splits > 1:
-            scratch = torch.empty((library.pylon_attention_scratch_floats(splits, tokens, nq),), dtype=torch.float32, device=q.device)
-        counters = _zeroed_counters(q.device, "attention", rows * nkv) if splits > 1 else None
+        # Rows of decoded tokens can occur unless the step is one long row.
+        blocks = 0
+        if max_q * (nq // nkv) <= 16 or rows > 1:
+            blocks = library.pylon_attention_decode_blocks() if decode_blocks is None else int(decode_blocks)
+            _need(blocks >= 1, "paged_attention: the decode kernel does not fit on this device")
+        scratch = counters = None
+        floats = library.pylon_attention_scratch_floats(splits, tokens, nq, rows, nkv, blocks)
+        if floats:
+            scratch = torch.empty((floats,), dtype=torch.float32, device=q.device)
+        if blocks:
+            counters = _zeroed_counters(q.device, "attention", rows * nkv)
         _check(library, library.pylon_paged_attention_mma(
             _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(counters), _ptr(q_start), _ptr(kv_len),
             _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
-            int(max_q), splits, _stream()))
+            int(max_q), splits, blocks, _ptr(attention_error_word(q.device)), _stream()))
         return out
     _need(d <= 512, f"paged_attention: head size {d} is larger than 512")
     library = _library("attention_simple.cu")

@@ -315,11 +315,13 @@ ATTENTION_CASES = [
     ([257, 90, 40], [3, 2, 1], 4, 2, 32, 16, None),
     ([400, 33, 64], [1, 1, 1], 4, 2, 64, 64, 100),
     ([1000], [1], 16, 1, 16, 256, None),                  # a group of 16 fills the tile
+    # more rows than a warp scans at once, lengths from 1 to 451, beside a prompt portion in the middle
+    ([1 + (37 * i) % 451 for i in range(20)] + [80] + [5 + (53 * i) % 300 for i in range(19)], [1] * 20 + [30] + [1] * 19, 8, 2, 64, 16, None),
 ]
 
 
 @pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: f"d{c[4]}_g{c[2] // c[3]}_p{c[5]}_w{c[6]}")
-@pytest.mark.parametrize("mode", ["float32", "bfloat16_simple", "bfloat16_mma", "bfloat16_mma_splits"])
+@pytest.mark.parametrize("mode", ["float32", "bfloat16_simple", "bfloat16_mma", "bfloat16_mma_splits", "bfloat16_mma_blocks1", "bfloat16_mma_blocks5"])
 def test_paged_attention(case, mode):
     from pylon_b200.kernels import ops
 
@@ -334,8 +336,11 @@ def test_paged_attention(case, mode):
         fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table, nq,
         max(q_lens), max(kv_lens), window=window, force_simple=mode in ("float32", "bfloat16_simple"),
         num_splits=3 if mode == "bfloat16_mma_splits" else (1 if mode == "bfloat16_mma" else None),
+        # decoded rows: all their tiles in one block's run, or in five runs that end inside rows
+        decode_blocks=int(mode[len("bfloat16_mma_blocks"):]) if mode.startswith("bfloat16_mma_blocks") else None,
     )
     torch.testing.assert_close(out.double(), expected, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)))
+    assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0   # no wait for a TMA copy ran out
 
 
 @pytest.mark.parametrize("mode", ["float32", "bfloat16_mma", "bfloat16_mma_splits"])

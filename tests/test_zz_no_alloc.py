@@ -3,8 +3,8 @@
 Some users of the kernels cannot allocate device memory when they need attention: the GPU's
 memory is all handed out already, or they sit in a loop that must not touch an allocator, or
 they use the library without PyTorch.  For them ``pylon_paged_attention_mma_static``
-(``csrc/attention_static.cu``) keeps the split-KV scratch in a fixed array inside the
-library.  This test calls that symbol with raw pointers, twice in a row on different
+(``csrc/attention_static.cu``) keeps the scratch for partial results and the counters in
+fixed arrays inside the library.  This test calls that symbol with raw pointers, twice in a row on different
 inputs (the array keeps what the last call left, so the second call shows whether stale
 contents matter), and compares with the ordinary entry point, which gets its scratch from
 the caller.  It also checks that a job too large for the built-in scratch is refused.
@@ -35,7 +35,7 @@ def load_static_library():
                          c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p]
     function.restype = c_int
     library.pylon_static_scratch_floats.restype = c_longlong
-    library.pylon_attention_scratch_floats.argtypes = [c_int, c_int, c_int]
+    library.pylon_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
     library.pylon_attention_scratch_floats.restype = c_longlong
     return library
 
@@ -86,7 +86,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     fused = torch.randn(cache.tokens, (nq + 2 * nkv) * HEAD_DIM, device="cuda").to(torch.bfloat16)
     out = torch.zeros((cache.tokens, nq * HEAD_DIM), dtype=torch.bfloat16, device="cuda")
     # claim a job of 100,000 tokens and 64 splits: far beyond 4 Mi floats; nothing may be launched
-    needed = library.pylon_attention_scratch_floats(64, 100_000, nq)
+    needed = library.pylon_attention_scratch_floats(64, 100_000, nq, 1, nkv, 0)   # one long row: no blocks for decoded rows
     assert needed > library.pylon_static_scratch_floats()
     pointer = lambda tensor: c_void_p(tensor.data_ptr())
     code = library.pylon_paged_attention_mma_static(
