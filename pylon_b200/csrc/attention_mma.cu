@@ -392,7 +392,7 @@ struct DecodeTiles {
   static constexpr size_t STAGE_BYTES = (size_t)DEC_STAGES * STAGE * sizeof(__nv_bfloat16);
   // stages (1024-byte aligned for the swizzle), query tile, two mbarriers
   static constexpr size_t SMEM = (TMA ? 1024 : 0) + STAGE_BYTES + (size_t)SMALL_ROWS * LD * sizeof(__nv_bfloat16) + (TMA ? 64 : 0);
-  static_assert(STAGE_BYTES >= 4 * SMALL_ROWS * (D + 2) * sizeof(float), "merge buffers reuse the tile stages");
+  static_assert(STAGE * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * D * sizeof(float), "the warps' outputs are merged in one idle stage");
   // Element offset of the 16-byte piece `chunk` (8 values) of key `row` within a tile.
   static __device__ __forceinline__ int offset(int row, int chunk) {
     if (TMA) return (chunk >> 3) * (BLOCK_N * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
@@ -438,7 +438,21 @@ __device__ __forceinline__ int decode_row_tiles(const AttentionParams& p, int ro
   return hi / BLOCK_N - lo / BLOCK_N + 1;
 }
 
-constexpr int DEC_MIN_TILES = 2;   // a block takes at least this many tiles: below it the merging costs more than the walk
+constexpr int DEC_PENDING = 16;    // segments a block collects before it publishes them
+constexpr int DEC_MIN_TILES = 4;   // a block takes about this many tiles at least: below it, starting and merging cost more than the walk
+
+// The runs: `used` blocks share `total` tiles, block b takes [run_begin(b), run_begin(b + 1)), so the
+// runs differ by one tile at most; run_of(x) is the block whose run holds tile x.
+// `pairs`: (row, KV head) pairs with tiles.  When the rows are equally long, a number of blocks that is a
+// multiple of the pairs makes every run end where a pair ends, and no block has to merge and publish
+// twice (30 instead of 35 us at batch 8, context 4096); it is taken if it costs under a fifth of the blocks.
+__device__ __forceinline__ int decode_blocks_used(int total, int grid, int pairs) {
+  const int used = max(1, min(grid, total / DEC_MIN_TILES));
+  const int aligned = pairs > 0 ? used / pairs * pairs : 0;
+  return aligned * 5 >= used * 4 ? aligned : used;
+}
+__device__ __forceinline__ int run_begin(int block, int total, int used) { return (int)((long long)block * total / used); }
+__device__ __forceinline__ int run_of(int tile, int total, int used) { return (int)((((long long)tile + 1) * used - 1) / total); }   // a block takes at least this many tiles: below it the merging costs more than the walk
 
 // Decoded rows.  All (row, KV head, tile) triples of the launch form one sequence, row-major,
 // and the blocks cut it into equal runs, so every block reads the same number of bytes however
@@ -451,7 +465,7 @@ constexpr int DEC_MIN_TILES = 2;   // a block takes at least this many tiles: be
 // map_k, map_v (TMA form only): the page pools as matrices [pages x KV heads x page size, D]
 // with boxes of 64 rows x 64 values.
 template <bool TMA>
-__global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v) {
   using Tiles = DecodeTiles<TMA>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -459,9 +473,11 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
   __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_base);                 // [DEC_STAGES][2][64 keys]
   __nv_bfloat16* q_tile = stages + DEC_STAGES * Tiles::STAGE;                          // [16][LD]
   uint64_t* tile_full = reinterpret_cast<uint64_t*>(q_tile + SMALL_ROWS * LD);         // [DEC_STAGES], TMA form
-  __shared__ int plan[3];   // tiles of the launch; the row this block starts in; tiles before that row
-  __shared__ bool last_segment;
-  __shared__ float row_total[SMALL_ROWS];
+  __shared__ int plan[4];   // tiles of the launch; the row this block starts in; tiles before that row; blocks with a run
+  __shared__ int pending[DEC_PENDING][6];   // segments to publish: pair, first block, segments, q0, packed rows, KV head
+  __shared__ bool pending_last[DEC_PENDING];
+  __shared__ float row_lse[SMALL_ROWS];
+  __shared__ float merge_max[4 * SMALL_ROWS], merge_sum[4 * SMALL_ROWS];   // the four warps' softmax statistics
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int G = p.group;
@@ -475,13 +491,20 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
   if (warp == 0) {
     int unused;
     const int first_chunk = lane < p.num_rows ? decode_row_tiles(p, lane, &unused) : 0;   // kept: most launches have at most 32 rows
-    int total = first_chunk;
-    for (int base = 32; base < p.num_rows; base += 32) total += base + lane < p.num_rows ? decode_row_tiles(p, base + lane, &unused) : 0;
+    int total = first_chunk, with_tiles = first_chunk > 0;
+    for (int base = 32; base < p.num_rows; base += 32) {
+      const int tiles = base + lane < p.num_rows ? decode_row_tiles(p, base + lane, &unused) : 0;
+      total += tiles;
+      with_tiles += tiles > 0;
+    }
 #pragma unroll
-    for (int offset = 16; offset; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+    for (int offset = 16; offset; offset >>= 1) {
+      total += __shfl_xor_sync(0xffffffffu, total, offset);
+      with_tiles += __shfl_xor_sync(0xffffffffu, with_tiles, offset);
+    }
     total *= p.nkv;
-    const int per_block = max(DEC_MIN_TILES, (total + (int)gridDim.x - 1) / (int)gridDim.x);
-    const int begin = blockIdx.x * per_block;
+    const int used = decode_blocks_used(total, gridDim.x, with_tiles * p.nkv);
+    const int begin = (int)blockIdx.x < used ? run_begin(blockIdx.x, total, used) : total;
     int found_row = -1, found_before = 0;
     if (begin < total) {
       int before = 0;
@@ -502,40 +525,158 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
         before += __shfl_sync(0xffffffffu, inclusive, 31);
       }
     }
-    if (lane == 0) { plan[0] = total; plan[1] = found_row; plan[2] = found_before; }
+    if (lane == 0) { plan[0] = total; plan[1] = found_row; plan[2] = found_before; plan[3] = used; }
   }
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   __syncthreads();
   const int total_tiles = plan[0];
   if (plan[1] < 0) return;
-  const int per_block = max(DEC_MIN_TILES, (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x);
-  const int run_end = min(total_tiles, ((int)blockIdx.x + 1) * per_block);
+  const int blocks_used = plan[3];
+  const int run_end = run_begin(blockIdx.x + 1, total_tiles, blocks_used);
   const bool contiguous = p.page_size % BLOCK_N == 0;
-  int position = blockIdx.x * per_block, row = plan[1], before = plan[2];
+  int position = run_begin(blockIdx.x, total_tiles, blocks_used), row = plan[1], before = plan[2];
   unsigned issued = 0, consumed = 0;   // tiles of this block so far: stage = count % DEC_STAGES
 
-  while (position < run_end && row < p.num_rows) {
-    int first_tile;
-    const int row_tiles = decode_row_tiles(p, row, &first_tile);
-    if (row_tiles == 0) { ++row; continue; }
-    const int within = position - before;
-    const int kv_head = within / row_tiles;
-    const int tile_begin = first_tile + within % row_tiles;
-    const int tile_end = tile_begin + min(run_end - position, row_tiles - within % row_tiles);
-    const int pair_start = before + kv_head * row_tiles;
-    const int first_block = pair_start / per_block;
-    const int segments = (pair_start + row_tiles - 1) / per_block - first_block + 1;   // blocks this pair lies in
-    const int pair = row * p.nkv + kv_head;
-    position += tile_end - tile_begin;
+  // The next piece of this block's run: tiles [tile_begin, tile_end) of one (row, KV head).
+  struct Segment {
+    int kv_head, tile_begin, tile_end, pair, first_block, segments, q0, packed_rows, kv_len, pos0;
+    const int* table;
+  };
+  auto next_segment = [&](Segment& s) -> bool {
+    while (position < run_end && row < p.num_rows) {
+      int first_tile;
+      const int row_tiles = decode_row_tiles(p, row, &first_tile);
+      if (row_tiles == 0) { ++row; continue; }
+      const int within = position - before;
+      s.kv_head = within / row_tiles;
+      s.tile_begin = first_tile + within % row_tiles;
+      s.tile_end = s.tile_begin + min(run_end - position, row_tiles - within % row_tiles);
+      const int pair_start = before + s.kv_head * row_tiles;
+      s.first_block = run_of(pair_start, total_tiles, blocks_used);
+      s.segments = run_of(pair_start + row_tiles - 1, total_tiles, blocks_used) - s.first_block + 1;   // blocks this pair lies in
+      s.pair = row * p.nkv + s.kv_head;
+      s.q0 = p.q_start[row];
+      const int q_len = p.q_start[row + 1] - s.q0;
+      s.packed_rows = q_len * G;
+      s.kv_len = p.kv_len[row];
+      s.pos0 = s.kv_len - q_len;
+      s.table = p.block_table + (size_t)row * p.table_width;
+      position += s.tile_end - s.tile_begin;
+      if (position - before == row_tiles * p.nkv) { before += row_tiles * p.nkv; ++row; }   // the next segment starts the next row
+      return true;
+    }
+    return false;
+  };
+  // Starts the copy of one tile into the next stage of the ring.
+  auto issue_tile = [&](const Segment& s, int tile) {
+    __nv_bfloat16* dst = stages + (issued % DEC_STAGES) * Tiles::STAGE;
+    if (TMA) {
+      if (threadIdx.x == 0) {
+        // A tile lies in one page.  Without a page for it the row coordinate points past the
+        // pool and TMA fills the boxes with zeros.
+        const int key0 = tile * BLOCK_N;
+        const int page = s.table[key0 / p.page_size];
+        const bool page_ok = page >= 0 && page < p.num_pages;
+        const int y = page_ok ? (page * p.nkv + s.kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
+        uint64_t* bar = &tile_full[issued % DEC_STAGES];
+        att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
+#pragma unroll
+        for (int box = 0; box < D / 64; ++box) {
+          att_tma_load(dst + box * (BLOCK_N * 64), &map_k, bar, box * 64, y);
+          att_tma_load(dst + Tiles::TILE + box * (BLOCK_N * 64), &map_v, bar, box * 64, y);
+        }
+      }
+    } else if (contiguous) {
+      load_kv_tile_contiguous(dst, p.k_pages, s.table, tile, s.kv_len, s.kv_head, p);
+      load_kv_tile_contiguous(dst + Tiles::TILE, p.v_pages, s.table, tile, s.kv_len, s.kv_head, p);
+    } else {
+      load_kv_tile(dst, p.k_pages, s.table, tile, s.kv_len, s.kv_head, p);
+      load_kv_tile(dst + Tiles::TILE, p.v_pages, s.table, tile, s.kv_len, s.kv_head, p);
+    }
+    ++issued;
+  };
+  // Starts the copy of a segment's packed query rows (cp.async; the caller commits the group).
+  auto load_query = [&](const Segment& s) {
+    for (int c = threadIdx.x; c < SMALL_ROWS * CHUNKS; c += ATT_THREADS) {
+      const int r = c / CHUNKS, col = c % CHUNKS;
+      const bool valid = r < s.packed_rows;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + (size_t)(s.q0 + r / G) * p.q_stride + (size_t)(s.kv_head * G + r % G) * D + col * 8;
+      cp_async_16(q_tile + r * LD + col * 8, src, valid);
+    }
+  };
 
-    const int q0 = p.q_start[row];
-    const int q_len = p.q_start[row + 1] - q0;
-    const int packed_rows = q_len * G;
-    const int kv_len = p.kv_len[row];
-    const int pos0 = kv_len - q_len;
-    const int* table = p.block_table + (size_t)row * p.table_width;
-    if (position - before == row_tiles * p.nkv) { before += row_tiles * p.nkv; ++row; }   // the next segment starts the next row
+  // Segments of pairs that other blocks share leave partial results; the block publishes them
+  // together (one fence and one round of counter updates for all of them, at the end of its run
+  // or when the list is full), and combines those pairs for which it turns out to be last.
+  int pending_count = 0;
+  auto publish_and_combine = [&]() {
+    if (pending_count == 0) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x < pending_count)
+      pending_last[threadIdx.x] = atomicAdd(p.counters + pending[threadIdx.x][0], 1u) == (unsigned)pending[threadIdx.x][2] - 1u;
+    __syncthreads();
+    for (int entry = 0; entry < pending_count; ++entry) {
+      if (!pending_last[entry]) continue;
+      const int pair = pending[entry][0], first_block = pending[entry][1], segments = pending[entry][2];
+      const int q0 = pending[entry][3], packed_rows = pending[entry][4], kv_head = pending[entry][5];
+      __threadfence();
+      // One trip to L2: every thread asks for its four values of up to eight segments and for
+      // those segments' log-sum-exps at once, then weighs and adds them.  More segments go round
+      // again, the sum so far rescaled as in the attention loop itself.
+      constexpr int SLOT_VECTORS = SMALL_ROWS * D / 4;
+      const size_t slot0 = (size_t)pair + first_block;
+      const float4* partials = reinterpret_cast<const float4*>(p.decode_out + slot0 * SMALL_ROWS * D);
+      const float* lses = p.decode_lse + slot0 * SMALL_ROWS;
+      for (int v = threadIdx.x; v < packed_rows * (D / 4); v += ATT_THREADS) {
+        const int r = v / (D / 4), col = (v % (D / 4)) * 4;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        float run_max = -INFINITY, run_total = 0.f;
+        for (int s2 = 0; s2 < segments; s2 += 8) {
+          float4 part[8];
+          float lse[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int segment = min(s2 + j, segments - 1);
+            part[j] = __ldcg(partials + (size_t)segment * SLOT_VECTORS + v);
+            lse[j] = s2 + j < segments ? __ldcg(lses + (size_t)segment * SMALL_ROWS + r) : -INFINITY;
+          }
+          float new_max = run_max;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) new_max = fmaxf(new_max, lse[j]);
+          if (new_max == -INFINITY) continue;   // nothing visible in these segments
+          const float alpha = fast_exp2(run_max - new_max);   // 0 for the first round
+          sum.x *= alpha; sum.y *= alpha; sum.z *= alpha; sum.w *= alpha;
+          run_total *= alpha;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float weight = fast_exp2(lse[j] - new_max);   // 0 for -infinity
+            sum.x += weight * part[j].x; sum.y += weight * part[j].y; sum.z += weight * part[j].z; sum.w += weight * part[j].w;
+            run_total += weight;
+          }
+          run_max = new_max;
+        }
+        const float inv = run_total > 0.f ? 1.f / run_total : 0.f;
+        const size_t token = (size_t)q0 + r / G;
+        const int head = kv_head * G + r % G;
+        __nv_bfloat16* dst = p.out + (token * p.nq + head) * D + col;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(sum.x * inv, sum.y * inv), pack_bf16(sum.z * inv, sum.w * inv));
+      }
+      if (threadIdx.x == 0) p.counters[pair] = 0u;   // ready for the next launch
+    }
+    pending_count = 0;
+  };
+
+  Segment current, following;
+  bool have = next_segment(current);
+  bool prefetched = false;   // the segment's query and first tile were asked for while the one before it was merged
+  while (have) {
+    const bool have_following = next_segment(following);
+    const int kv_head = current.kv_head, tile_begin = current.tile_begin, tile_end = current.tile_end, pair = current.pair;
+    const int first_block = current.first_block, segments = current.segments, q0 = current.q0, packed_rows = current.packed_rows;
+    const int kv_len = current.kv_len, pos0 = current.pos0;
 
     int row_pos[2];
     bool row_valid[2];
@@ -552,46 +693,15 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
 
     auto issue = [&](int tile) {
-      if (tile < tile_end) {
-        __nv_bfloat16* dst = stages + (issued % DEC_STAGES) * Tiles::STAGE;
-        if (TMA) {
-          if (threadIdx.x == 0) {
-            // A tile lies in one page.  Without a page for it the row coordinate points past the
-            // pool and TMA fills the boxes with zeros.
-            const int key0 = tile * BLOCK_N;
-            const int page = table[key0 / p.page_size];
-            const bool page_ok = page >= 0 && page < p.num_pages;
-            const int y = page_ok ? (page * p.nkv + kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
-            uint64_t* bar = &tile_full[issued % DEC_STAGES];
-            att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
-#pragma unroll
-            for (int box = 0; box < D / 64; ++box) {
-              att_tma_load(dst + box * (BLOCK_N * 64), &map_k, bar, box * 64, y);
-              att_tma_load(dst + Tiles::TILE + box * (BLOCK_N * 64), &map_v, bar, box * 64, y);
-            }
-          }
-        } else if (contiguous) {
-          load_kv_tile_contiguous(dst, p.k_pages, table, tile, kv_len, kv_head, p);
-          load_kv_tile_contiguous(dst + Tiles::TILE, p.v_pages, table, tile, kv_len, kv_head, p);
-        } else {
-          load_kv_tile(dst, p.k_pages, table, tile, kv_len, kv_head, p);
-          load_kv_tile(dst + Tiles::TILE, p.v_pages, table, tile, kv_len, kv_head, p);
-        }
-        ++issued;
-      }
+      if (tile < tile_end) issue_tile(current, tile);
       if (!TMA) cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
     };
-
-    for (int c = threadIdx.x; c < SMALL_ROWS * CHUNKS; c += ATT_THREADS) {
-      const int r = c / CHUNKS, col = c % CHUNKS;
-      const bool valid = r < packed_rows;
-      const __nv_bfloat16* src = p.q;
-      if (valid) src = p.q + (size_t)(q0 + r / G) * p.q_stride + (size_t)(kv_head * G + r % G) * D + col * 8;
-      cp_async_16(q_tile + r * LD + col * 8, src, valid);
-    }
-    if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
+    if (!prefetched) {
+      load_query(current);
+      if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
 #pragma unroll
-    for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
+      for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
+    }
 
     const bool upper_rows_unused = packed_rows <= 8;
     // The query fragments stay in registers when the head is small enough to leave room.
@@ -599,8 +709,16 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
     unsigned q_frag[Q_IN_REGISTERS ? D / 16 : 1][4];
     bool q_loaded = false;
 
+    bool tile_prefetched = false;   // the following segment's first tile is on its way
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-      issue(tile + DEC_STAGES - 1);
+      if (TMA && DEC_STAGES == 2 && tile + 1 == tile_end && have_following) {
+        // The ring has a free stage and this segment no tile for it: the following segment's
+        // first tile comes in while this one's last tile is multiplied and the warps are merged.
+        issue_tile(following, following.tile_begin);
+        tile_prefetched = true;
+      } else {
+        issue(tile + DEC_STAGES - 1);
+      }
       const __nv_bfloat16* ks = stages + (consumed % DEC_STAGES) * Tiles::STAGE;
       const __nv_bfloat16* vs = ks + Tiles::TILE;
       if (TMA) {
@@ -714,13 +832,24 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
     }
     if (!TMA) cp_async_wait<0>();
 
+    // While this segment is merged and written out, the next one's query is on its way into the
+    // query tile, which every warp has read; its first tile went into the stage that is not the
+    // one read last (where the merge happens).
+    prefetched = false;
+    if (TMA && DEC_STAGES == 2 && have_following) {
+      load_query(following);
+      cp_async_commit();
+      if (!tile_prefetched) issue_tile(following, following.tile_begin);
+      prefetched = true;
+    }
+
     // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
-    float* merge_o = reinterpret_cast<float*>(stages);                 // [4][16][D]
-    float* merge_max = merge_o + 4 * SMALL_ROWS * D;                   // [4][16]
-    float* merge_sum = merge_max + 4 * SMALL_ROWS;                     // [4][16]
+    __nv_bfloat16* idle_stage = stages + ((consumed + DEC_STAGES - 1) % DEC_STAGES) * Tiles::STAGE;   // the stage read last
+    float* merge_o = reinterpret_cast<float*>(idle_stage);             // [4][16][D]: exactly one stage of the TMA form
     __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
+      if (h == 1 && upper_rows_unused) continue;   // nothing reads rows 8..15 of the merge buffers then
       float sum = row_sum[h];
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -734,94 +863,54 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_decode_kernel(con
       for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     __syncthreads();
-    const size_t slot = (size_t)pair + blockIdx.x;
-    for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
-      const int r = e / D, col = e % D;
+    // Per row, once: the warps' weights 2^(max_w - max) over the total, and the log-sum-exp.
+    if (threadIdx.x < packed_rows) {
+      const int r = threadIdx.x;
       float mx = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) mx = fmaxf(mx, merge_max[w * SMALL_ROWS + r]);
-      float total = 0.f, value = 0.f;
+      float weight[4], total = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const float m = merge_max[w * SMALL_ROWS + r];
-        const float weight = m == -INFINITY ? 0.f : exp2f((m - mx) * p.scale_log2);
-        total += weight * merge_sum[w * SMALL_ROWS + r];
-        value += weight * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
+        weight[w] = m == -INFINITY ? 0.f : fast_exp2((m - mx) * p.scale_log2);
+        total += weight[w] * merge_sum[w * SMALL_ROWS + r];
       }
       const float inv = total > 0.f ? 1.f / total : 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) merge_max[w * SMALL_ROWS + r] = weight[w] * inv;   // from here on: the warp's share
+      row_lse[r] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;     // the segment's log-sum-exp (log2)
+    }
+    __syncthreads();
+    const size_t slot = (size_t)pair + blockIdx.x;
+    for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
+      const int r = e / D, col = e % D;
+      float value = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) value += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
       if (segments == 1) {
         const size_t token = (size_t)q0 + r / G;
         const int head = kv_head * G + r % G;
-        p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(value * inv);
+        p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(value);
       } else {
-        p.decode_out[(slot * SMALL_ROWS + r) * D + col] = value * inv;
-        if (col == 0) p.decode_lse[slot * SMALL_ROWS + r] = total > 0.f ? mx * p.scale_log2 + log2f(total) : -INFINITY;
+        p.decode_out[(slot * SMALL_ROWS + r) * D + col] = value;
+        if (col == 0) p.decode_lse[slot * SMALL_ROWS + r] = row_lse[r];
       }
     }
 
     if (segments > 1) {
-      // The block that finishes last for this (row, KV head) combines the segments; the others
-      // have published their partial results (fence, then the counter).
-      __threadfence();
-      __syncthreads();
-      unsigned* counter = p.counters + pair;
-      if (threadIdx.x == 0) last_segment = atomicAdd(counter, 1u) == (unsigned)segments - 1u;
-      __syncthreads();
-      if (last_segment) {
-        __threadfence();
-        // The segments' weights first (one trip to L2 for all of them), then the weighted sum
-        // with several partial results in flight per thread.
-        float* weights = reinterpret_cast<float*>(stages);   // [packed_rows][segments]; the stages are idle now
-        const size_t slot0 = (size_t)pair + first_block;
-        for (int e = threadIdx.x; e < packed_rows * segments; e += ATT_THREADS) {
-          const int r = e / segments, s2 = e % segments;
-          weights[e] = __ldcg(p.decode_lse + (slot0 + s2) * SMALL_ROWS + r);
-        }
-        __syncthreads();
-        if (threadIdx.x < packed_rows) {
-          const int r = threadIdx.x;
-          float mx = -INFINITY;
-          for (int s2 = 0; s2 < segments; ++s2) mx = fmaxf(mx, weights[r * segments + s2]);
-          float total = 0.f;
-          for (int s2 = 0; s2 < segments; ++s2) {
-            const float lse = weights[r * segments + s2];
-            const float weight = lse == -INFINITY ? 0.f : exp2f(lse - mx);
-            weights[r * segments + s2] = weight;
-            total += weight;
-          }
-          row_total[r] = total;
-        }
-        __syncthreads();
-        // Four values per thread and eight segments' loads in flight: the trips to L2 are what this
-        // block waits for, so they must overlap, not follow one another.
-        constexpr int SLOT_VECTORS = SMALL_ROWS * D / 4;
-        const float4* partials = reinterpret_cast<const float4*>(p.decode_out + slot0 * SMALL_ROWS * D);
-        for (int v = threadIdx.x; v < packed_rows * (D / 4); v += ATT_THREADS) {
-          const int r = v / (D / 4), col = (v % (D / 4)) * 4;
-          const float* w = weights + r * segments;
-          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s2 = 0; s2 < segments; s2 += 8) {
-            float4 part[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) part[j] = __ldcg(partials + (size_t)min(s2 + j, segments - 1) * SLOT_VECTORS + v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float weight = s2 + j < segments ? w[s2 + j] : 0.f;
-              sum.x += weight * part[j].x; sum.y += weight * part[j].y; sum.z += weight * part[j].z; sum.w += weight * part[j].w;
-            }
-          }
-          const float inv = row_total[r] > 0.f ? 1.f / row_total[r] : 0.f;
-          const size_t token = (size_t)q0 + r / G;
-          const int head = kv_head * G + r % G;
-          __nv_bfloat16* dst = p.out + (token * p.nq + head) * D + col;
-          *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(sum.x * inv, sum.y * inv), pack_bf16(sum.z * inv, sum.w * inv));
-        }
-        if (threadIdx.x == 0) *counter = 0u;   // ready for the next launch
+      if (threadIdx.x == 0) {
+        int* entry = pending[pending_count];
+        entry[0] = pair; entry[1] = first_block; entry[2] = segments; entry[3] = q0; entry[4] = packed_rows; entry[5] = kv_head;
       }
+      if (++pending_count == DEC_PENDING) publish_and_combine();
     }
     if (TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the merge buffers were written where TMA writes next
     __syncthreads();   // the query tile and the stages are free for the next segment
+    current = following;
+    have = have_following;
   }
+  publish_and_combine();
 }
 
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
@@ -927,23 +1016,20 @@ static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
 constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
 constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA : DEC_SMEM_GATHER;
 
-// Blocks of the decode kernel: as many as are resident at once (of the form that needs more
-// shared memory), and few enough that the weights of a pair's segments (at most blocks + 2 of
-// them, 16 rows each) fit where the combining block keeps them.
+// Blocks of the decode kernel: as many as are resident at once, of the form that needs more
+// shared memory.
 extern "C" int pylon_attention_decode_blocks() {
-  static int blocks = 0;
-  if (blocks == 0) {
+  static int resident = 0;
+  if (resident == 0) {
     int device = 0, sm_count = 0, per_sm = 0, per_sm_tma = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
     if (cudaFuncSetAttribute(paged_attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_GATHER) != cudaSuccess) return -1;
     if (cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA) != cudaSuccess) return -1;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, paged_attention_decode_kernel<false>, ATT_THREADS, DEC_SMEM_GATHER) != cudaSuccess || per_sm < 1) return -1;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_tma, paged_attention_decode_kernel<TMA_HEAD>, ATT_THREADS, DEC_SMEM_TMA) != cudaSuccess || per_sm_tma < 1) return -1;
-    if (per_sm_tma < per_sm) per_sm = per_sm_tma;
-    const int cap = (int)(DecodeTiles<TMA_HEAD>::STAGE_BYTES / (SMALL_ROWS * sizeof(float))) - 2;   // the smaller of the two forms' stages
-    blocks = per_sm * sm_count < cap ? per_sm * sm_count : cap;
+    resident = (per_sm_tma < per_sm ? per_sm_tma : per_sm) * sm_count;
   }
-  return blocks;
+  return resident;
 }
 
 // Scratch floats a call needs: `num_splits` splits of the tiled kernel over `total_tokens`

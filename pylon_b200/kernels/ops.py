@@ -79,6 +79,9 @@ _SIGNATURES = {
         "pylon_gemm_skinny_partial": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p],
         "pylon_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
+    "gemm_stream.cu": {
+        "pylon_gemm_stream_partial": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p],
+    },
     "gemm_tcgen05.cu": {
         "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                                     c_void_p, c_int, c_void_p],
@@ -309,26 +312,57 @@ def _tcgen05_fills_the_sms(m: int, n: int) -> bool:
     return tiles >= 0.8 * rounds * _SM_COUNT
 
 
-PARTIAL_MAX_BLOCKS = 2 * 148   # products with fewer 16-row blocks than this are split over k as well
+STREAM_MAX_ROWS = 8   # up to this many rows the products for the residual stream run on the TMA-fed kernel
+STREAM_MAX_PARTS = 4
 
 
 def linear_for_residual(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` for a result that goes straight into the residual stream: either the
-    product ``[M, N]`` in the activation dtype, or - for few rows and a matrix with too few
-    rows of its own to keep the GPU busy - float32 partial sums ``[parts, M, N]`` over slices
-    of k, which the stream's next norm adds up (no extra kernel, no atomics)."""
+    product ``[M, N]`` in the activation dtype, or - for the few rows of a decode step -
+    float32 partial sums ``[parts, M, N]`` over slices of k, which the stream's next norm adds
+    up (no extra kernel, no atomics).  The slices make enough blocks to fill the GPU however
+    few rows the matrix has."""
     m, k = x.shape
     n = w.shape[0]
-    blocks = -(-n // 16)
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and m <= SKINNY_MAX_ROWS and blocks < PARTIAL_MAX_BLOCKS
-            and k >= 2048 and k % 8 == 0 and n % 4 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
-            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
-        parts = int(min(4, max(2, (3 * 148) // blocks)))
-        y = torch.empty((parts, m, n), dtype=torch.float32, device=x.device)
-        library = _library("gemm_skinny.cu")
-        _check(library, library.pylon_gemm_skinny_partial(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), parts, _stream()))
-        return y
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and m <= STREAM_MAX_ROWS and k >= 1024 and k % 8 == 0
+            and n % 4 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return linear_stream_partial(x, w)
     return linear(x, w)
+
+
+_stream_error: dict[str, torch.Tensor] = {}
+
+
+def stream_error_word(device: torch.device) -> torch.Tensor:
+    """The int32 word the TMA-fed decode product sets when one of its bounded waits ran out
+    (its result is then void).  Zero in every healthy run."""
+    key = str(device)
+    if key not in _stream_error:
+        _stream_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _stream_error[key]
+
+
+def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int] = None) -> torch.Tensor:
+    """bfloat16 ``x [M <= 8, K] @ w [N, K].T`` as float32 partial sums ``[parts, M, N]`` over
+    slices of k, the weights streamed by TMA through a shared-memory ring.  ``parts`` defaults
+    to what gives every SM up to three blocks (64 weight rows x one slice each), at most
+    ``STREAM_MAX_PARTS``: more parts cost the reader more than they save here (the norm that adds
+    them up took 3.0 us with 4 parts and 5.1 us with 11)."""
+    _need_cuda(x, w)
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
+          "linear_stream_partial: bfloat16 x [M, K] and w [N, K]")
+    _need(x.stride(1) == 1 and w.stride(1) == 1, "linear_stream_partial: the reduced dimension must be contiguous")
+    m, k = x.shape
+    n = w.shape[0]
+    slabs, k_boxes = -(-n // 64), -(-k // 64)
+    if parts is None:
+        parts = max(1, min(STREAM_MAX_PARTS, k_boxes, (3 * _SM_COUNT) // slabs))
+    y = torch.empty((parts, m, n), dtype=torch.float32, device=x.device)
+    library = _library("gemm_stream.cu")
+    _check(library, library.pylon_gemm_stream_partial(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), parts,
+                                                      _ptr(stream_error_word(x.device)), _stream()))
+    return y
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

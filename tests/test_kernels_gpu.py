@@ -233,6 +233,27 @@ def test_partial_sums_for_the_residual(m, n, k):
     assert ops.linear_for_residual(torch.zeros(9, k, device=DEVICE, dtype=torch.bfloat16), w).dim() == 2
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 2560, 4096), (5, 100, 72), (3, 2564, 4104), (8, 130, 1032), (7, 6144, 2560)])
+def test_stream_gemm_partial_sums(m, n, k):
+    """The TMA-fed decode product: row, column and k counts that do not fill its 64 x 64 boxes,
+    every sensible number of parts, and a strided activation view."""
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(m, k + 16, device=DEVICE).to(torch.bfloat16)[:, 8 : 8 + k]
+    w = (torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    k_boxes = -(-k // 64)
+    for parts in sorted({None, 1, min(2, k_boxes), min(3, k_boxes), min(k_boxes, 16)}, key=lambda v: -1 if v is None else v):
+        y = ops.linear_stream_partial(x, w, parts)
+        assert y.dtype == torch.float32 and y.shape[1:] == (m, n) and (parts is None or y.shape[0] == parts)
+        torch.testing.assert_close(y.double().sum(0), want, rtol=1e-3, atol=1e-3)
+    assert int(ops.stream_error_word(torch.device(DEVICE)).item()) == 0
+    with pytest.raises(ops.KernelError, match="more than 8 rows"):
+        ops.linear_stream_partial(torch.zeros(9, k, device=DEVICE, dtype=torch.bfloat16), w)
+    with pytest.raises(ops.KernelError, match="parts"):
+        ops.linear_stream_partial(x, w, k_boxes + 1)
+
+
 def test_skinny_gemm_refuses():
     from pylon_b200.kernels import ops
 
