@@ -1050,12 +1050,13 @@ extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_to
 // num_rows * nkv unsigned integers that are zero before the call (and zero again after it).
 // scratch and counters may be null when num_splits = 1 and no row can have 16 packed rows or fewer
 // (one row and max_q * group > 16).  error: null, or one int in device memory that a kernel sets
-// non-zero when its bounded wait for a TMA copy ran out (the output is then void).
+// non-zero when its bounded wait for a TMA copy ran out (the output is then void).  skip_large != 0: rows with
+// more than 16 packed query rows are left alone (another kernel writes them).
 extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
                                          const int* block_table, int table_width, int page_size, int num_pages,
                                          int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
-                                         int max_q, int num_splits, int decode_blocks, int* error, cudaStream_t stream) {
+                                         int max_q, int num_splits, int decode_blocks, int skip_large, int* error, cudaStream_t stream) {
   if (num_rows <= 0 || total_tokens <= 0) return 0;
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_mma: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 1 || table_width < 1 || window < 0 || max_q < 1 || num_splits < 1)
@@ -1069,7 +1070,8 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   const long long packed_max = (long long)max_q * group;
   const bool any_large = packed_max > SMALL_ROWS;
   const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
-  if (!any_large) num_splits = 1;                        // no row for the tiled kernel
+  const bool run_tiled = any_large && !skip_large;
+  if (!run_tiled) num_splits = 1;                        // no row for the tiled kernel
   if (num_splits > 1 && scratch == nullptr) PYLON_REFUSE("paged_attention_mma: splits need scratch memory");
   if (maybe_small) {
     const int most = pylon_attention_decode_blocks();
@@ -1110,7 +1112,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.num_rows = num_rows;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.small_rows_elsewhere = maybe_small ? 1 : 0;
-  if (any_large) {
+  if (run_tiled) {
     // 128-row blocks when the rows are long enough to fill them and the accumulators fit.
     const bool wide = WIDE_TILES && packed_max >= 256;
     const int block_rows = wide ? 128 : 64;

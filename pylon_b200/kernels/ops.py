@@ -95,9 +95,13 @@ _SIGNATURES = {
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                      c_int, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "pylon_attention_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
         "pylon_attention_decode_blocks": [],
+    },
+    "attention_tcgen05.cu": {
+        "pylon_paged_attention_tcgen05": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "sampling.cu": {
         "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -120,7 +124,7 @@ def build_all() -> list[str]:
     """Every library with its default sizes (the tensor-core attention for head size 128)."""
     names = []
     for source in _SIGNATURES:
-        defines = {"PYLON_HEAD_DIM": 128} if source == "attention_mma.cu" else None
+        defines = {"PYLON_HEAD_DIM": 128} if source in ("attention_mma.cu", "attention_tcgen05.cu") else None
         _library(source, defines)
         names.append(build.library_name(source, defines))
     return names
@@ -515,6 +519,7 @@ def paged_attention(
     num_splits: Optional[int] = None,
     force_simple: bool = False,
     decode_blocks: Optional[int] = None,
+    prefill_kernel: Optional[str] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
@@ -525,11 +530,15 @@ def paged_attention(
     at position ``kv_len - (q_start[r + 1] - q_start[r])``); ``block_table`` int32
     ``[rows, width]``; ``max_q``/``max_kv``: longest row and longest context (upper bounds
     are fine).  ``num_splits`` and ``decode_blocks`` override the split of long rows' keys and
-    the number of blocks that share the decoded rows' tiles (for tests).  Returns ``[T, nq * d]``.
+    the number of blocks that share the decoded rows' tiles, ``prefill_kernel`` (``"tcgen05"`` or
+    ``"mma"``) the kernel for rows of more than 16 packed query rows (for tests).  Returns
+    ``[T, nq * d]``.
 
     bfloat16 with a head size that is a multiple of 16 up to 256 runs on the tensor cores
-    (built per head size on first use); float32, and other head sizes up to 512, take the
-    plain kernel.
+    (built per head size on first use): prompt portions on ``tcgen05.mma`` with the accumulators
+    in tensor memory where the head size is 64 or 128 and a page holds a multiple of 64 keys,
+    else on ``mma.sync``; decoded tokens on their own kernel.  float32, and other head sizes up
+    to 512, take the plain kernel.
     """
     _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out)
     _need(k_pages.dim() == 4 and k_pages.shape == v_pages.shape and k_pages.is_contiguous() and v_pages.is_contiguous(), "paged_attention: pages must be contiguous [P, nkv, page_size, d]")
@@ -550,10 +559,27 @@ def paged_attention(
     _need(scale > 0, "paged_attention: the softmax scale must be positive")
     if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
-        splits = attention_splits(rows, nkv, nq // nkv, max_q, max_kv) if num_splits is None else int(num_splits)
+        group = nq // nkv
+        any_large = max_q * group > 16
         # Rows of decoded tokens can occur unless the step is one long row.
+        maybe_small = not any_large or rows > 1
+        # Prompt portions go to the tcgen05 kernel where it exists: head size 64 or 128, pages of a multiple of 64 keys.
+        if prefill_kernel is None:
+            prefill_kernel = "tcgen05" if d in (64, 128) and page_size % 64 == 0 and num_splits in (None, 1) else "mma"
+        _need(prefill_kernel in ("tcgen05", "mma"), f"paged_attention: unknown prefill kernel {prefill_kernel!r}")
+        use_tcgen05 = any_large and prefill_kernel == "tcgen05"
+        if use_tcgen05:
+            _need(d in (64, 128) and page_size % 64 == 0, "paged_attention: the tcgen05 kernel needs head size 64 or 128 and pages of a multiple of 64 keys")
+            fast = _library("attention_tcgen05.cu", {"PYLON_HEAD_DIM": d})
+            _check(fast, fast.pylon_paged_attention_tcgen05(
+                _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
+                block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, int(max_q), int(maybe_small),
+                _ptr(attention_error_word(q.device)), _stream()))
+            if not maybe_small:
+                return out
+        splits = 1 if use_tcgen05 else (attention_splits(rows, nkv, group, max_q, max_kv) if num_splits is None else int(num_splits))
         blocks = 0
-        if max_q * (nq // nkv) <= 16 or rows > 1:
+        if maybe_small:
             blocks = library.pylon_attention_decode_blocks() if decode_blocks is None else int(decode_blocks)
             _need(blocks >= 1, "paged_attention: the decode kernel does not fit on this device")
         scratch = counters = None
@@ -565,7 +591,7 @@ def paged_attention(
         _check(library, library.pylon_paged_attention_mma(
             _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(counters), _ptr(q_start), _ptr(kv_len),
             _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
-            int(max_q), splits, blocks, _ptr(attention_error_word(q.device)), _stream()))
+            int(max_q), splits, blocks, int(use_tcgen05), _ptr(attention_error_word(q.device)), _stream()))
         return out
     _need(d <= 512, f"paged_attention: head size {d} is larger than 512")
     library = _library("attention_simple.cu")

@@ -336,17 +336,24 @@ ATTENTION_CASES = [
     ([257, 90, 40], [3, 2, 1], 4, 2, 32, 16, None),
     ([400, 33, 64], [1, 1, 1], 4, 2, 64, 64, 100),
     ([1000], [1], 16, 1, 16, 256, None),                  # a group of 16 fills the tile
+    # prompt portions for the tcgen05 kernel: several query tiles, tiles that end inside a page, a group of 5, windows
+    ([700, 129, 64], [700, 65, 3], 8, 2, 128, 64, None),
+    ([1000, 300], [333, 300], 10, 2, 128, 128, None),
+    ([520, 77], [200, 77], 4, 4, 64, 64, 150),
+    ([900], [900], 6, 1, 64, 192, 70),
     # more rows than a warp scans at once, lengths from 1 to 451, beside a prompt portion in the middle
     ([1 + (37 * i) % 451 for i in range(20)] + [80] + [5 + (53 * i) % 300 for i in range(19)], [1] * 20 + [30] + [1] * 19, 8, 2, 64, 16, None),
 ]
 
 
 @pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: f"d{c[4]}_g{c[2] // c[3]}_p{c[5]}_w{c[6]}")
-@pytest.mark.parametrize("mode", ["float32", "bfloat16_simple", "bfloat16_mma", "bfloat16_mma_splits", "bfloat16_mma_blocks1", "bfloat16_mma_blocks5"])
+@pytest.mark.parametrize("mode", ["float32", "bfloat16_simple", "bfloat16_mma", "bfloat16_mma_splits", "bfloat16_mma_blocks1", "bfloat16_mma_blocks5", "bfloat16_tcgen05"])
 def test_paged_attention(case, mode):
     from pylon_b200.kernels import ops
 
     kv_lens, q_lens, nq, nkv, d, page, window = case
+    if mode == "bfloat16_tcgen05" and not (d in (64, 128) and page % 64 == 0):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages of a multiple of 64 keys")
     dtype = torch.float32 if mode == "float32" else torch.bfloat16
     cache = Paged(kv_lens, q_lens, nkv, d, page, dtype)
     # q sits inside a wider fused buffer, as in the engine
@@ -359,6 +366,7 @@ def test_paged_attention(case, mode):
         num_splits=3 if mode == "bfloat16_mma_splits" else (1 if mode == "bfloat16_mma" else None),
         # decoded rows: all their tiles in one block's run, or in five runs that end inside rows
         decode_blocks=int(mode[len("bfloat16_mma_blocks"):]) if mode.startswith("bfloat16_mma_blocks") else None,
+        prefill_kernel="tcgen05" if mode == "bfloat16_tcgen05" else ("mma" if mode.startswith("bfloat16_mma") else None),
     )
     torch.testing.assert_close(out.double(), expected, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)))
     assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0   # no wait for a TMA copy ran out
