@@ -49,7 +49,7 @@ constexpr int FA_Q_BYTES = FA_BM * D * 2;          // D / 64 panels of [128 rows
 constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;      // [128 rows][64 keys]
 constexpr int FA_TILE_BYTES = FA_BN * D * 2;       // keys or values of one tile: D / 64 boxes of [64 keys][64 values]
 constexpr int FA_STAGE_BYTES = 2 * FA_TILE_BYTES;
-constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_P_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers */;
+constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_P_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers: 13 x 8 bytes and the tensor-memory address */;
 // At least 80 KB: never more than two blocks on an SM, so that their 2 x 256 columns of tensor memory always fit and no
 // block waits in tcgen05.alloc for another to finish.
 constexpr size_t FA_SMEM = FA_SMEM_USED > 80 * 1024 ? FA_SMEM_USED : 80 * 1024;
@@ -88,6 +88,13 @@ __device__ __forceinline__ bool fa_mbar_wait(uint64_t* bar, unsigned parity) {
     if (done) return true;
   }
   return false;
+}
+// One look at the barrier, without waiting.
+__device__ __forceinline__ bool fa_mbar_test(uint64_t* bar, unsigned parity) {
+  unsigned done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(done) : "r"(fa_smem(bar)), "r"(parity) : "memory");
+  return done != 0;
 }
 __device__ __forceinline__ void fa_tma_load(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -158,31 +165,34 @@ __host__ __device__ constexpr unsigned fa_instr_desc(int m, int n, bool b_mn_maj
   return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
-// Grid (query tiles, KV heads, rows).  error: 1 producer, 2 MMA issuer, 3 softmax gave up waiting; 4 shared memory misaligned.
+// Grid (KV heads, rows, query tiles).  error: 1 producer, 2 MMA issuer, 3 softmax gave up waiting; 4 shared memory misaligned.
 __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const FaParams p, const __grid_constant__ CUtensorMap map_k,
                                                                            const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_tile = smem;
   unsigned char* p_tile = q_tile + FA_Q_BYTES;
   unsigned char* stages = p_tile + FA_P_BYTES;
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(stages + FA_STAGES * FA_STAGE_BYTES);   // [2]
-  uint64_t* kv_empty = kv_full + 2;    // [2]
-  uint64_t* s_full = kv_empty + 2;     // [2] scores of a tile are in tensor memory
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(stages + FA_STAGES * FA_STAGE_BYTES);   // [2] the keys of a tile have landed
+  uint64_t* k_empty = k_full + 2;      // [2] ... and are read (their scores are computed)
+  uint64_t* v_full = k_empty + 2;      // [2] the same for the values
+  uint64_t* v_empty = v_full + 2;      // [2]
+  uint64_t* s_full = v_empty + 2;      // [2] scores of a tile are in tensor memory
   uint64_t* p_full = s_full + 2;       // weights of a tile are in shared memory (and the scores read)
-  uint64_t* pv_done = p_full + 1;      // the weighted sum of a tile is added: the weights' buffer and the stage are free
+  uint64_t* pv_done = p_full + 1;      // the weighted sum of a tile is added: the weights' buffer is free
   uint64_t* q_full = pv_done + 1;      // the query tile is in shared memory
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_full + 1);
 
-  const int row = blockIdx.z, kv_head = blockIdx.y;
+  const int row = blockIdx.y, kv_head = blockIdx.x;
   const int q0 = p.q_start[row];
   const int q_len = p.q_start[row + 1] - q0;
   const int G = p.group;
   const int packed_rows = q_len * G;
   if (packed_rows <= 0 || (p.skip_small && packed_rows <= FA_SMALL_ROWS)) return;
-  // Later query tiles see more keys: hand them out first so the longest blocks start first.
+  // Later query tiles see more keys: hand them out first (the query tile runs slowest in the grid, so the longest
+  // blocks of all heads and rows start first).
   const int q_tiles = (packed_rows + FA_BM - 1) / FA_BM;
-  if ((int)blockIdx.x >= q_tiles) return;
-  const int m0 = (q_tiles - 1 - (int)blockIdx.x) * FA_BM;
+  if ((int)blockIdx.z >= q_tiles) return;
+  const int m0 = (q_tiles - 1 - (int)blockIdx.z) * FA_BM;
   const int kv_len = p.kv_len[row];
   const int pos0 = kv_len - q_len;   // position of the row's first new token
   const int* table = p.block_table + (size_t)row * p.table_width;
@@ -197,7 +207,10 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     return;
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) { fa_mbar_init(&kv_full[s], 1); fa_mbar_init(&kv_empty[s], 1); fa_mbar_init(&s_full[s], 1); }
+    for (int s = 0; s < 2; ++s) {
+      fa_mbar_init(&k_full[s], 1); fa_mbar_init(&k_empty[s], 1); fa_mbar_init(&v_full[s], 1); fa_mbar_init(&v_empty[s], 1);
+      fa_mbar_init(&s_full[s], 1);
+    }
     fa_mbar_init(p_full, 128);
     fa_mbar_init(pv_done, 1);
     fa_mbar_init(q_full, 128);
@@ -217,7 +230,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     if (lane == 0) {
       for (int t = 0; t < num_tiles; ++t) {
         const int stage = t & 1;
-        if (!fa_mbar_wait(&kv_empty[stage], ((t >> 1) & 1) ^ 1)) { atomicExch(p.error, 1); break; }
+        const unsigned parity = ((t >> 1) & 1) ^ 1;
         // A tile lies in one page.  Without a page for it the row coordinate points past the pool and TMA fills the boxes
         // with zeros.
         const int key0 = (first_tile + t) * FA_BN;
@@ -225,12 +238,15 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         const bool page_ok = page >= 0 && page < p.num_pages;
         const int y = page_ok ? (page * p.nkv + kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
         unsigned char* dst = stages + stage * FA_STAGE_BYTES;
-        fa_mbar_expect_tx(&kv_full[stage], FA_STAGE_BYTES);
+        // The keys' half of a stage is free as soon as its scores are computed, a whole tile before the values' half.
+        if (!fa_mbar_wait(&k_empty[stage], parity)) { atomicExch(p.error, 1); break; }
+        fa_mbar_expect_tx(&k_full[stage], FA_TILE_BYTES);
 #pragma unroll
-        for (int box = 0; box < D / 64; ++box) {
-          fa_tma_load(dst + box * (FA_BN * 128), &map_k, &kv_full[stage], box * 64, y);
-          fa_tma_load(dst + FA_TILE_BYTES + box * (FA_BN * 128), &map_v, &kv_full[stage], box * 64, y);
-        }
+        for (int box = 0; box < D / 64; ++box) fa_tma_load(dst + box * (FA_BN * 128), &map_k, &k_full[stage], box * 64, y);
+        if (!fa_mbar_wait(&v_empty[stage], parity)) { atomicExch(p.error, 1); break; }
+        fa_mbar_expect_tx(&v_full[stage], FA_TILE_BYTES);
+#pragma unroll
+        for (int box = 0; box < D / 64; ++box) fa_tma_load(dst + FA_TILE_BYTES + box * (FA_BN * 128), &map_v, &v_full[stage], box * 64, y);
       }
     }
   } else if (warp == 5) {
@@ -240,25 +256,19 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       constexpr unsigned idesc_o = fa_instr_desc(FA_BM, D, true);
       bool alive = fa_mbar_wait(q_full, 0);
       if (!alive) atomicExch(p.error, 2);
-      auto scores = [&](int t) -> bool {   // S[t % 2] = Q K(t)^T
-        const int stage = t & 1;
-        if (!fa_mbar_wait(&kv_full[stage], (t >> 1) & 1)) { atomicExch(p.error, 2); return false; }
+      auto scores = [&](int t) {   // S[t % 2] = Q K(t)^T; the keys have landed
         fa_fence_after();
-        const unsigned char* k_tile = stages + stage * FA_STAGE_BYTES;
+        const unsigned char* k_tile = stages + (t & 1) * FA_STAGE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {   // 16 values = 32 bytes along the swizzled row: +2 in 16-byte units; 64 values to a panel
           const uint64_t a = fa_desc(q_tile + (kk / 4) * (FA_BM * 128), 16, 1024) + 2 * (kk % 4);
           const uint64_t b = fa_desc(k_tile + (kk / 4) * (FA_BN * 128), 16, 1024) + 2 * (kk % 4);
           fa_mma(tmem_base + (t & 1) * FA_S_COLUMNS, a, b, idesc_s, kk != 0 ? 1u : 0u);
         }
+        fa_commit(&k_empty[t & 1]);
         fa_commit(&s_full[t & 1]);
-        return true;
       };
-      if (alive) alive = scores(0);
-      for (int t = 0; t < num_tiles && alive; ++t) {
-        if (t + 1 < num_tiles) alive = scores(t + 1);   // runs while tile t goes through the softmax
-        if (!alive) break;
-        if (!fa_mbar_wait(p_full, t & 1)) { atomicExch(p.error, 2); break; }
+      auto weighted_sum = [&](int t) {   // O += P(t) V(t); the weights are written
         fa_fence_after();
         const unsigned char* v_tile = stages + (t & 1) * FA_STAGE_BYTES + FA_TILE_BYTES;
 #pragma unroll
@@ -267,8 +277,23 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
           const uint64_t b = fa_desc(v_tile + kk * 2048, FA_BN * 128, 1024);
           fa_mma(tmem_base + FA_O_COLUMN, a, b, idesc_o, (t | kk) != 0 ? 1u : 0u);
         }
-        fa_commit(&kv_empty[t & 1]);
+        fa_commit(&v_empty[t & 1]);
         fa_commit(pv_done);
+      };
+      if (alive) {
+        alive = fa_mbar_wait(&k_full[0], 0);
+        if (alive) scores(0); else atomicExch(p.error, 2);
+      }
+      // Per tile two things are to be issued, whichever can go first: the scores of the next tile (its keys must have
+      // landed) and the weighted sum of this one (its weights must be written and its values landed).
+      for (int t = 0; t < num_tiles && alive; ++t) {
+        bool scores_due = t + 1 < num_tiles, sum_due = true;
+        const unsigned next_parity = ((t + 1) >> 1) & 1, parity = (t >> 1) & 1;
+        for (unsigned tries = 0; (scores_due || sum_due) && alive; ++tries) {
+          if (scores_due && fa_mbar_test(&k_full[(t + 1) & 1], next_parity)) { scores(t + 1); scores_due = false; }
+          if (sum_due && fa_mbar_test(p_full, t & 1) && fa_mbar_test(&v_full[t & 1], parity)) { weighted_sum(t); sum_due = false; }
+          if (tries == FA_WAIT_LIMIT) { atomicExch(p.error, 2); alive = false; }
+        }
       }
     }
   } else {
@@ -304,7 +329,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         for (int half = 0; half < 2; ++half) {
           fa_tmem_load_32(lane_base + (t & 1) * FA_S_COLUMNS + half * 32, raw);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) s[half * 32 + j] = __uint_as_float(raw[j]) * p.scale_log2;
+          for (int j = 0; j < 32; ++j) s[half * 32 + j] = __uint_as_float(raw[j]);
         }
       }
       const int key0 = (first_tile + t) * FA_BN;
@@ -321,11 +346,23 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       float tile_max = s[0];
 #pragma unroll
       for (int j = 1; j < FA_BN; ++j) tile_max = fmaxf(tile_max, s[j]);
+      tile_max *= p.scale_log2;   // the scale is positive: the largest score stays the largest
       // The reference moves only when the maximum has grown by more than the step (or was not set yet).
       const bool move = tile_max > reference + FA_RESCALE_STEP || (reference == -INFINITY && tile_max > -INFINITY);
       const float alpha = move ? (reference == -INFINITY ? 0.f : fa_exp2(reference - tile_max)) : 1.f;
       if (move) reference = tile_max;
       const float use = reference == -INFINITY ? 0.f : reference;
+      // The weights first, in registers: the product of the tile before this one may still be running.
+      sum *= alpha;
+      float tile_sum = 0.f;
+      unsigned packed[FA_BN / 2];
+#pragma unroll
+      for (int j = 0; j < FA_BN; j += 2) {
+        const float w0 = fa_exp2(fmaf(s[j], p.scale_log2, -use)), w1 = fa_exp2(fmaf(s[j + 1], p.scale_log2, -use));   // 0 for masked keys
+        tile_sum += w0 + w1;
+        packed[j / 2] = fa_pack(w0, w1);
+      }
+      sum += tile_sum;
       // The weights' buffer and the output are free once the tile before this one is added up.
       if (t > 0) {
         if (!fa_mbar_wait(pv_done, (t - 1) & 1)) { atomicExch(p.error, 3); alive = false; break; }
@@ -341,23 +378,14 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
           }
         }
       }
-      sum *= alpha;
-      float tile_sum = 0.f;
-      unsigned packed[FA_BN / 2];
-#pragma unroll
-      for (int j = 0; j < FA_BN; j += 2) {
-        const float w0 = fa_exp2(s[j] - use), w1 = fa_exp2(s[j + 1] - use);   // 0 for masked keys
-        tile_sum += w0 + w1;
-        packed[j / 2] = fa_pack(w0, w1);
-      }
-      sum += tile_sum;
 #pragma unroll
       for (int c = 0; c < FA_BN / 8; ++c)
         *reinterpret_cast<uint4*>(p_tile + r * 128 + ((c ^ (r & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       if (key0 + FA_BN > kv_len) {
         // Keys past the row's length are masked, but their values (whatever the page held) still meet a weight of zero in
-        // the product: make them zero.  The tile has landed: its scores came from it.
+        // the product: make them zero, once they have landed.
+        if (!fa_mbar_wait(&v_full[t & 1], (t >> 1) & 1)) { atomicExch(p.error, 3); alive = false; break; }
         unsigned char* v_tile = stages + (t & 1) * FA_STAGE_BYTES + FA_TILE_BYTES;
         const int first_unused = kv_len - key0;
         for (int c = r; c < FA_BN * (D / 8); c += 128) {
@@ -485,7 +513,7 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.error = error;
   const long long q_tiles = ((long long)max_q * p.group + FA_BM - 1) / FA_BM;
-  if (q_tiles > 2147483647LL) PYLON_REFUSE("paged_attention_tcgen05: too many query tiles");
-  attention_tcgen05_kernel<<<dim3((unsigned)q_tiles, nkv, num_rows), FA_THREADS, FA_SMEM, stream>>>(p, map_k, map_v);
+  if (q_tiles > 65535) PYLON_REFUSE("paged_attention_tcgen05: too many query tiles");
+  attention_tcgen05_kernel<<<dim3(nkv, num_rows, (unsigned)q_tiles), FA_THREADS, FA_SMEM, stream>>>(p, map_k, map_v);
   PYLON_CHECK_LAUNCH("paged_attention_tcgen05");
 }
