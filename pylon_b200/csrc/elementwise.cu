@@ -298,7 +298,10 @@ struct HeadChunk<float, CHUNK> {
   }
 };
 
-template <typename T, int CHUNK>
+// HPW heads of one token per warp: their loads are issued together, so a warp has HPW times the
+// bytes in flight per trip to memory (with one head per warp a 2048-token step ran at a third of
+// the memory bandwidth); the token's position, page and angles are looked up once.
+template <typename T, int CHUNK, int HPW>
 __global__ void qk_norm_rope_kv_write_vec_kernel(
     T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
@@ -311,49 +314,65 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
+  const int groups = (heads + HPW - 1) / HPW;
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
-  if (item >= (long long)num_tokens * heads) return;
-  const int t = (int)(item / heads), head = (int)(item % heads);
-  T* src = qkv + ((size_t)t * heads + head) * d + lane * CHUNK;
+  if (item >= (long long)num_tokens * groups) return;
+  const int t = (int)(item / groups), head_begin = (int)(item % groups) * HPW;
+  T* token_src = qkv + (size_t)t * heads * d + lane * CHUNK;
+  float x[HPW][CHUNK];
+#pragma unroll
+  for (int h = 0; h < HPW; ++h)
+    if (head_begin + h < heads) HeadChunk<T, CHUNK>::load(token_src + (size_t)(head_begin + h) * d, x[h]);
   const int pos = positions[t];
-  T* page_dst = nullptr;
-  if (head >= nq) {
+  size_t page_offset = 0;
+  bool page_ok = true;
+  if (head_begin + HPW > nq) {   // a key or value head among them
     const int row = token_row[t];
     const int page = block_table[(size_t)row * table_width + pos / page_size];
-    if (page < 0 || page >= num_pages) return;   // never for a prepared step; keeps memory safe
-    const int kv_head = (head - nq) % nkv;
-    T* pages = head < nq + nkv ? k_pages : v_pages;
-    page_dst = pages + (((size_t)page * nkv + kv_head) * page_size + pos % page_size) * d + lane * CHUNK;
+    page_ok = page >= 0 && page < num_pages;   // always for a prepared step; keeps memory safe
+    page_offset = ((size_t)(page_ok ? page : 0) * nkv * page_size + pos % page_size) * d + lane * CHUNK;
   }
-  float x[CHUNK];
-  HeadChunk<T, CHUNK>::load(src, x);
-  if (head >= nq + nkv) {   // value: plain copy
-    HeadChunk<T, CHUNK>::store(page_dst, x);
-    return;
-  }
-  const float* weight = head < nq ? q_weight : k_weight;
-  if (weight) {
-    float sumsq = 0.f;
-#pragma unroll
-    for (int i = 0; i < CHUNK; ++i) sumsq += x[i] * x[i];
-    sumsq = warp_sum(sumsq);
-    const float inv = rsqrtf(sumsq / (float)d + eps);
-#pragma unroll
-    for (int i = 0; i < CHUNK; ++i) x[i] = x[i] * inv * weight[lane * CHUNK + i];
-  }
-  if (cos_table) {
+  float c[CHUNK], s[CHUNK];
+  if (cos_table && head_begin < nq + nkv) {
     const int p = pos < table_positions ? pos : table_positions - 1;   // the host checks the range
     const int column = (lane & 15) * CHUNK;                            // both halves share their angles
-    const float* c = cos_table + (size_t)p * half + column;
-    const float* s = sin_table + (size_t)p * half + column;
-    const bool upper = lane >= 16;
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) {
-      const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
-      x[i] = upper ? x[i] * c[i] + partner * s[i] : x[i] * c[i] - partner * s[i];
-    }
+    for (int i = 0; i < CHUNK; ++i) { c[i] = cos_table[(size_t)p * half + column + i]; s[i] = sin_table[(size_t)p * half + column + i]; }
   }
-  HeadChunk<T, CHUNK>::store(head < nq ? src : page_dst, x);
+  const bool upper = lane >= 16;
+#pragma unroll
+  for (int h = 0; h < HPW; ++h) {
+    const int head = head_begin + h;
+    if (head >= heads) break;
+    T* page_dst = nullptr;
+    if (head >= nq) {
+      if (!page_ok) continue;
+      const int kv_head = (head - nq) % nkv;
+      page_dst = (head < nq + nkv ? k_pages : v_pages) + page_offset + (size_t)kv_head * page_size * d;
+    }
+    if (head >= nq + nkv) {   // value: plain copy
+      HeadChunk<T, CHUNK>::store(page_dst, x[h]);
+      continue;
+    }
+    const float* weight = head < nq ? q_weight : k_weight;
+    if (weight) {
+      float sumsq = 0.f;
+#pragma unroll
+      for (int i = 0; i < CHUNK; ++i) sumsq += x[h][i] * x[h][i];
+      sumsq = warp_sum(sumsq);
+      const float inv = rsqrtf(sumsq / (float)d + eps);
+#pragma unroll
+      for (int i = 0; i < CHUNK; ++i) x[h][i] = x[h][i] * inv * weight[lane * CHUNK + i];
+    }
+    if (cos_table) {
+#pragma unroll
+      for (int i = 0; i < CHUNK; ++i) {
+        const float partner = __shfl_xor_sync(0xffffffffu, x[h][i], 16);
+        x[h][i] = upper ? x[h][i] * c[i] + partner * s[i] : x[h][i] * c[i] - partner * s[i];
+      }
+    }
+    HeadChunk<T, CHUNK>::store(head < nq ? token_src + (size_t)head * d : page_dst, x[h]);
+  }
 }
 
 // -----------------------------------------------------------------------------------------
@@ -481,10 +500,21 @@ static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float e
   const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0);
   if (whole && aligned && (d == 64 || d == 128 || d == 256)) {
     const float* cos_used = rotary_dim == d ? cos_t : nullptr;
-#define PYLON_LAUNCH_QK_VEC(C)                                                                              \
-    launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C>, dim3(blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps, cos_used, \
-                     sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, v_pages,  \
-                     num_pages, nq, nkv, num_tokens)
+    // Many tokens: four heads per warp (more bytes in flight); few: one, for as many warps as possible.
+    const bool many = num_tokens >= 64;
+    const long long vec_items = (long long)num_tokens * (many ? (nq + 2 * nkv + 3) / 4 : nq + 2 * nkv);
+    const unsigned vec_blocks = (unsigned)((vec_items + warps - 1) / warps);
+#define PYLON_LAUNCH_QK_VEC(C)                                                                                            \
+    do {                                                                                                                  \
+      if (many)                                                                                                           \
+        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 4>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps,  \
+                         cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
+                         v_pages, num_pages, nq, nkv, num_tokens);                                                         \
+      else                                                                                                                \
+        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 1>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps,  \
+                         cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
+                         v_pages, num_pages, nq, nkv, num_tokens);                                                         \
+    } while (0)
     if (d == 64) PYLON_LAUNCH_QK_VEC(2);
     else if (d == 128) PYLON_LAUNCH_QK_VEC(4);
     else PYLON_LAUNCH_QK_VEC(8);
