@@ -27,9 +27,10 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-# Two tiny configurations that differ in every size and option Qwen3 dense has: head counts
+# Tiny configurations that differ in every size and option Qwen3 dense has: head counts
 # and group size, head size, widths that are no power of two, layers, vocabulary, rope
-# base, norm eps, tied or untied head.
+# base, norm eps, tied or untied head.  tinyC has the head size (64) and page size (64) at
+# which the TMA-fed decode attention and the tcgen05 prefill attention run, with a group of 3.
 TINY_CONFIGS = {
     "tinyA": dict(vocab_size=256, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                   head_dim=16, intermediate_size=128, max_position_embeddings=512, rope_theta=10_000.0,
@@ -37,9 +38,12 @@ TINY_CONFIGS = {
     "tinyB": dict(vocab_size=320, hidden_size=96, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=3,
                   head_dim=32, intermediate_size=224, max_position_embeddings=512, rope_theta=1_000_000.0,
                   rms_norm_eps=1e-5, tie_word_embeddings=False),
+    "tinyC": dict(vocab_size=288, hidden_size=80, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+                  head_dim=64, intermediate_size=176, max_position_embeddings=512, rope_theta=50_000.0,
+                  rms_norm_eps=1e-6, tie_word_embeddings=False),
 }
-TINY_SEEDS = {"tinyA": 0, "tinyB": 1}
-TINY_PAGE_SIZES = {"tinyA": 16, "tinyB": 8}
+TINY_SEEDS = {"tinyA": 0, "tinyB": 1, "tinyC": 2}
+TINY_PAGE_SIZES = {"tinyA": 16, "tinyB": 8, "tinyC": 64}
 
 
 @pytest.fixture(scope="session")

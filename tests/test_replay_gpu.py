@@ -11,7 +11,7 @@ from conftest import TINY_CONFIGS, TINY_PAGE_SIZES
 
 pytestmark = pytest.mark.gpu
 
-REQUEST_LENGTHS = {"tinyA": (70, 45, 133, 8, 96, 33), "tinyB": (40, 131, 64, 9, 77, 24, 1)}
+REQUEST_LENGTHS = {"tinyA": (70, 45, 133, 8, 96, 33), "tinyB": (40, 131, 64, 9, 77, 24, 1), "tinyC": (150, 70, 201, 9, 64, 130)}
 TOLERANCE = {"float32": dict(rtol=1e-4, atol=1e-5), "bfloat16": dict(rtol=2e-2, atol=2e-2)}
 
 
@@ -59,7 +59,7 @@ CUTTINGS = {
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
-@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB", "tinyC"])
 def test_cuttings_match_plain(name, cutting, dtype, tiny_folders, expected):
     requests = make_requests(name)
     steps = CUTTINGS[cutting](requests)
@@ -73,7 +73,7 @@ def test_cuttings_match_plain(name, cutting, dtype, tiny_folders, expected):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cutting", ["tail_one_by_one", "mixed"])
-@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB", "tinyC"])
 def test_decode_steps_replayed_from_cuda_graphs(name, cutting, dtype, tiny_folders, expected):
     """With graphs on, steps of single tokens come from captured graphs (one per batch size);
     the logits must be the same as without."""
