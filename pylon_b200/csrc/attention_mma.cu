@@ -527,8 +527,6 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     }
     if (lane == 0) { plan[0] = total; plan[1] = found_row; plan[2] = found_before; plan[3] = used; }
   }
-  grid_dependency_wait();
-  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   __syncthreads();
   const int total_tiles = plan[0];
   if (plan[1] < 0) return;
@@ -671,6 +669,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
 
   Segment current, following;
   bool have = next_segment(current);
+  bool waited = false;       // for the kernel before this one (programmatic dependent launch)
   bool prefetched = false;   // the segment's query and first tile were asked for while the one before it was merged
   while (have) {
     const bool have_following = next_segment(following);
@@ -697,10 +696,24 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       if (!TMA) cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
     };
     if (!prefetched) {
+      bool first_issued = false;
+      if (!waited) {
+        // A tile that ends before the row's first new token holds nothing the kernel before this one writes: it is
+        // asked for before this kernel waits for that one.  The queries and the newest keys are its work.
+        if (TMA && DEC_STAGES == 2 && (tile_begin + 1) * BLOCK_N <= pos0) {
+          issue_tile(current, tile_begin);
+          first_issued = true;
+        }
+        grid_dependency_wait();
+        allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
+        waited = true;
+      }
       load_query(current);
       if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
+      if (!first_issued) {
 #pragma unroll
-      for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
+        for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
+      }
     }
 
     const bool upper_rows_unused = packed_rows <= 8;

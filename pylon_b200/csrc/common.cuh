@@ -110,16 +110,17 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-// Off unless PYLON_B200_PDL is in the environment ("1": every launch made through
-// launch_dependent; "gemm": only the weight-streaming products, whose first weight loads do not
-// depend on the kernel before them).  Measured on the decode step of the Qwen3-4B shape, "1"
-// changed nothing or cost a few percent, so the ordinary launch stays the default.
+// On for every launch made through launch_dependent unless PYLON_B200_PDL says otherwise ("0": off; "gemm": only
+// the weight-streaming products).  Each of these kernels does what does not depend on its predecessor before it
+// waits (the products ask for their first weights, the decode attention makes its plan from the rows' lengths and
+// asks for its first old tile, the rotation looks up position, page and angles, the norm loads its weights) and lets
+// its own dependents start only after its wait, so at most two kernels share the GPU.  Measured on the decode step of
+// the Qwen3-4B shape, batch 8: 3.06 ms with, 3.26 ms without (batch 1: 2.50 against 2.79 ms).
 enum LaunchKind { LAUNCH_OTHER = 0, LAUNCH_GEMM = 1 };
 inline bool dependent_launch_enabled(LaunchKind kind) {
   static const int mode = [] {
     const char* value = getenv("PYLON_B200_PDL");
-    if (!value) return 0;
-    if (value[0] == '1') return 1;
+    if (!value || value[0] == '1') return 1;
     return value[0] == 'g' ? 2 : 0;
   }();
   return mode == 1 || (mode == 2 && kind == LAUNCH_GEMM);

@@ -93,14 +93,21 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __
                                                                        T* __restrict__ out, int width, float eps, int write_residual,
                                                                        int delta_parts, long long part_stride) {
   __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int groups = width >> 2;
+  // The norm's weights do not depend on the kernel before this one: they are on their way while it finishes.
+  float4 w[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const int i = threadIdx.x + k * NORM_THREADS;
+    w[k] = i < groups ? Vec4<float>::load(weight + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
-  const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* res = residual + (size_t)row * width;
   const DT* del = delta ? delta + (size_t)row * width : nullptr;
   T* dst = out + (size_t)r * width;
-  const int groups = width >> 2;
   float4 x[ITEMS];
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {
@@ -128,8 +135,7 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(float* __
     const int i = threadIdx.x + k * NORM_THREADS;
     if (i < groups) {
       if (del && write_residual) Vec4<float>::store(res + 4 * i, x[k]);
-      const float4 w = Vec4<float>::load(weight + 4 * i);
-      Vec4<T>::store(dst + 4 * i, make_float4(x[k].x * inv * w.x, x[k].y * inv * w.y, x[k].z * inv * w.z, x[k].w * inv * w.w));
+      Vec4<T>::store(dst + 4 * i, make_float4(x[k].x * inv * w[k].x, x[k].y * inv * w[k].y, x[k].z * inv * w[k].z, x[k].w * inv * w[k].w));
     }
   }
 }
@@ -309,8 +315,6 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
     int table_width, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
     int num_tokens) {
   constexpr int d = CHUNK * 32, half = d / 2;
-  grid_dependency_wait();
-  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -318,11 +322,8 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
   if (item >= (long long)num_tokens * groups) return;
   const int t = (int)(item / groups), head_begin = (int)(item % groups) * HPW;
-  T* token_src = qkv + (size_t)t * heads * d + lane * CHUNK;
-  float x[HPW][CHUNK];
-#pragma unroll
-  for (int h = 0; h < HPW; ++h)
-    if (head_begin + h < heads) HeadChunk<T, CHUNK>::load(token_src + (size_t)(head_begin + h) * d, x[h]);
+  // Position, page and angles are the step's own data, not the work of the kernel before this one: they are looked up
+  // while that kernel finishes.
   const int pos = positions[t];
   size_t page_offset = 0;
   bool page_ok = true;
@@ -339,6 +340,13 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i) { c[i] = cos_table[(size_t)p * half + column + i]; s[i] = sin_table[(size_t)p * half + column + i]; }
   }
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
+  T* token_src = qkv + (size_t)t * heads * d + lane * CHUNK;
+  float x[HPW][CHUNK];
+#pragma unroll
+  for (int h = 0; h < HPW; ++h)
+    if (head_begin + h < heads) HeadChunk<T, CHUNK>::load(token_src + (size_t)(head_begin + h) * d, x[h]);
   const bool upper = lane >= 16;
 #pragma unroll
   for (int h = 0; h < HPW; ++h) {

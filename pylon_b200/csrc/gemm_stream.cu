@@ -80,16 +80,26 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
-  grid_dependency_wait();
-  allow_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
-      unsigned stage = 0, phase = 0;
-      for (int box = box_begin; box < box_end; ++box) {
+      // The weights do not depend on the kernel before this one: the boxes that fit in the ring are asked for before
+      // this kernel waits for it (a dependent launch may start while that kernel is still running); the activations'
+      // boxes follow after the wait, on the same barriers.
+      const int ahead = min(ST_STAGES, box_end - box_begin);
+      for (int i = 0; i < ahead; ++i) {
+        st_mbar_expect_tx(&full[i], ST_STAGE_BYTES);   // rows past N, M or K arrive as zeros and count all the same
+        st_tma_load(stages + (size_t)i * ST_STAGE_BYTES, &map_w, &full[i], (box_begin + i) * ST_BK, n0);
+      }
+      grid_dependency_wait();
+      allow_dependents();
+      for (int i = 0; i < ahead; ++i)
+        st_tma_load(stages + (size_t)i * ST_STAGE_BYTES + ST_W_BYTES, &map_x, &full[i], (box_begin + i) * ST_BK, 0);
+      unsigned stage = 0, phase = 1;   // the ring has gone round once
+      for (int box = box_begin + ahead; box < box_end; ++box) {
         if (!st_mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); break; }
         unsigned char* dst = stages + (size_t)stage * ST_STAGE_BYTES;
-        st_mbar_expect_tx(&full[stage], ST_STAGE_BYTES);   // rows past N, M or K arrive as zeros and count all the same
+        st_mbar_expect_tx(&full[stage], ST_STAGE_BYTES);
         st_tma_load(dst, &map_w, &full[stage], box * ST_BK, n0);
         st_tma_load(dst + ST_W_BYTES, &map_x, &full[stage], box * ST_BK, 0);
         if (++stage == ST_STAGES) { stage = 0; phase ^= 1; }
@@ -97,6 +107,7 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
     }
     return;
   }
+  grid_dependency_wait();   // before the result is written: its memory may be what that kernel still reads
 
   // Consumers.  In the 128-byte swizzle the 16-byte unit u of row r sits at unit u ^ (r % 8).
   const int slab_row = (warp - 1) * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);   // this lane's row of w for ldmatrix
