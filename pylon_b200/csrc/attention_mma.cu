@@ -676,6 +676,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     const int kv_head = current.kv_head, tile_begin = current.tile_begin, tile_end = current.tile_end, pair = current.pair;
     const int first_block = current.first_block, segments = current.segments, q0 = current.q0, packed_rows = current.packed_rows;
     const int kv_len = current.kv_len, pos0 = current.pos0;
+    int issued_ahead = 0;   // tiles of this segment asked for before the wait for the kernel ahead (first segment only)
 
     int row_pos[2];
     bool row_valid[2];
@@ -696,13 +697,15 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       if (!TMA) cp_async_commit();   // an empty group keeps the count of groups in step with the tiles
     };
     if (!prefetched) {
-      bool first_issued = false;
       if (!waited) {
-        // A tile that ends before the row's first new token holds nothing the kernel before this one writes: it is
-        // asked for before this kernel waits for that one.  The queries and the newest keys are its work.
-        if (TMA && DEC_STAGES == 2 && (tile_begin + 1) * BLOCK_N <= pos0) {
-          issue_tile(current, tile_begin);
-          first_issued = true;
+        // Tiles that end before the row's first new token hold nothing the kernel before this one writes: as many
+        // of them as the ring has stages are asked for before this kernel waits for that one.  The queries and the
+        // newest keys are its work.
+        if (TMA) {
+          while (issued_ahead < DEC_STAGES && tile_begin + issued_ahead < tile_end && (tile_begin + issued_ahead + 1) * BLOCK_N <= pos0) {
+            issue_tile(current, tile_begin + issued_ahead);
+            ++issued_ahead;
+          }
         }
         grid_dependency_wait();
         allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
@@ -710,7 +713,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       }
       load_query(current);
       if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
-      if (!first_issued) {
+      if (issued_ahead == 0) {
 #pragma unroll
         for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
       }
@@ -724,7 +727,9 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
 
     bool tile_prefetched = false;   // the following segment's first tile is on its way
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-      if (TMA && DEC_STAGES == 2 && tile + 1 == tile_end && have_following) {
+      if (tile + DEC_STAGES - 1 < tile_begin + issued_ahead) {
+        // asked for before the wait
+      } else if (TMA && DEC_STAGES == 2 && tile + 1 == tile_end && have_following) {
         // The ring has a free stage and this segment no tile for it: the following segment's
         // first tile comes in while this one's last tile is multiplied and the warps are merged.
         issue_tile(following, following.tile_begin);

@@ -224,6 +224,10 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   __syncthreads();
   fa_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  // Barriers and tensor memory are set up while the kernel before this one finishes (dependent launch); the queries and
+  // the newest keys are its work: they are read, and anything written, only from here on.
+  grid_dependency_wait();
+  allow_dependents();
 
   if (warp == 4) {
     // ---- TMA producer ----
@@ -514,6 +518,6 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   p.error = error;
   const long long q_tiles = ((long long)max_q * p.group + FA_BM - 1) / FA_BM;
   if (q_tiles > 65535) PYLON_REFUSE("paged_attention_tcgen05: too many query tiles");
-  attention_tcgen05_kernel<<<dim3(nkv, num_rows, (unsigned)q_tiles), FA_THREADS, FA_SMEM, stream>>>(p, map_k, map_v);
+  launch_dependent(attention_tcgen05_kernel, dim3(nkv, num_rows, (unsigned)q_tiles), dim3(FA_THREADS), FA_SMEM, stream, p, map_k, map_v);
   PYLON_CHECK_LAUNCH("paged_attention_tcgen05");
 }

@@ -172,6 +172,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Barriers and tensor memory are set up while the kernel before this one finishes (dependent launch); its output is
+  // read, and anything written, only from here on.
+  grid_dependency_wait();
+  allow_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -325,7 +329,7 @@ static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __
   if (!make_map(&map_c, c, M, SWIGLU ? N / 2 : N, ldc, 32, TcStore<BN, SWIGLU>::COLUMNS)) PYLON_REFUSE("gemm_tcgen05: the output's tensor map could not be made");
   const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   const int blocks = tiles < sm_count ? tiles : sm_count;
-  kernel<<<blocks, TC_THREADS, TcShared<BN>::BYTES, stream>>>(map_a, map_b, map_c, M, N, K, error);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error);
   PYLON_CHECK_LAUNCH("gemm_tcgen05");
 }
 
