@@ -128,18 +128,24 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
     }
   };
 
-  // The weights do not depend on the kernel before this one: the first fragments are on
-  // their way before this kernel waits for its activations.  (Asking L2 for the block's whole
+  // The weights do not depend on the kernel before this one: the fragments of both register
+  // buffers are on their way before this kernel waits for its activations.  (Asking L2 for the block's whole
   // weight slab up front with cp.async.bulk.prefetch.L2 was measured slower: 22 against 18
   // microseconds on the 19456 x 2560 product.)
   int ks0 = step_begin + warp;
   load_weights(wa, ks0);
+  bool second_loaded = ks0 + STRIDE < k_steps;   // both register buffers are filled before the wait
+  if (second_loaded) load_weights(wb, ks0 + STRIDE);
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   load_activations(xa, ks0);
   for (; ks0 < k_steps; ks0 += 2 * STRIDE) {
     const bool more = ks0 + STRIDE < k_steps;
-    if (more) { load_weights(wb, ks0 + STRIDE); load_activations(xb, ks0 + STRIDE); }
+    if (more) {
+      if (!second_loaded) load_weights(wb, ks0 + STRIDE);
+      second_loaded = false;
+      load_activations(xb, ks0 + STRIDE);
+    }
     multiply(wa, xa);
     if (more) {
       if (ks0 + 2 * STRIDE < k_steps) { load_weights(wa, ks0 + 2 * STRIDE); load_activations(xa, ks0 + 2 * STRIDE); }
