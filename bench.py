@@ -287,6 +287,9 @@ def run_serving_workload(name: str, torch) -> dict:
     engine = Engine(None, config, device="cuda:0", model_config=Qwen3Config(**fields), random_seed=0)
     prompts = [rng.integers(0, fields["vocab_size"], size=n).tolist() for n in lengths]
     engine.generate(prompts[:2], [SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True)] * 2)   # warm up: libraries, allocator
+    # The decode graph of every batch size is captured before the first request, as raun6k/Pylon does when it starts
+    # (src/pylon/engine.py:823-836); otherwise each size's first step pays for its capture (about 20 ms).
+    captured = engine.capture_decode_graphs()
     torch.cuda.synchronize()
     started = time.perf_counter()
     for prompt, sampling in zip(prompts, params):
@@ -313,7 +316,7 @@ def run_serving_workload(name: str, torch) -> dict:
                    "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
                    "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
                    "requests": requests, "new_tokens": new_tokens, "page_size": PAGE_SIZE, "prefill_chunk": PREFILL_TOKENS,
-                   "temperature": params[0].temperature, "cuda_graphs": True},
+                   "temperature": params[0].temperature, "cuda_graphs": True, "graphs_captured_at_start": len(captured)},
     }
 
 
