@@ -347,9 +347,14 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
           if (!visible) s[j] = -INFINITY;
         }
       }
-      float tile_max = s[0];
+      // Eight chains side by side: one chain of 63 dependent comparisons would cost more than the exponentials.
+      float lane_max[8];
 #pragma unroll
-      for (int j = 1; j < FA_BN; ++j) tile_max = fmaxf(tile_max, s[j]);
+      for (int j = 0; j < 8; ++j) lane_max[j] = s[j];
+#pragma unroll
+      for (int j = 8; j < FA_BN; ++j) lane_max[j & 7] = fmaxf(lane_max[j & 7], s[j]);
+      float tile_max = fmaxf(fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])),
+                             fmaxf(fmaxf(lane_max[4], lane_max[5]), fmaxf(lane_max[6], lane_max[7])));
       tile_max *= p.scale_log2;   // the scale is positive: the largest score stays the largest
       // The reference moves only when the maximum has grown by more than the step (or was not set yet).
       const bool move = tile_max > reference + FA_RESCALE_STEP || (reference == -INFINITY && tile_max > -INFINITY);
@@ -358,15 +363,15 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       const float use = reference == -INFINITY ? 0.f : reference;
       // The weights first, in registers: the product of the tile before this one may still be running.
       sum *= alpha;
-      float tile_sum = 0.f;
+      float part_sum[4] = {0.f, 0.f, 0.f, 0.f};   // four chains, for the same reason
       unsigned packed[FA_BN / 2];
 #pragma unroll
       for (int j = 0; j < FA_BN; j += 2) {
         const float w0 = fa_exp2(fmaf(s[j], p.scale_log2, -use)), w1 = fa_exp2(fmaf(s[j + 1], p.scale_log2, -use));   // 0 for masked keys
-        tile_sum += w0 + w1;
+        part_sum[(j >> 1) & 3] += w0 + w1;
         packed[j / 2] = fa_pack(w0, w1);
       }
-      sum += tile_sum;
+      sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
       // The weights' buffer and the output are free once the tile before this one is added up.
       if (t > 0) {
         if (!fa_mbar_wait(pv_done, (t - 1) & 1)) { atomicExch(p.error, 3); alive = false; break; }
