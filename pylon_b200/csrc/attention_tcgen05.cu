@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + token) * p.q_stride + (size_t)head * D);
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
-        const uint4 v = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+        const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);   // an ordinary load: the kernel that wrote the queries overlaps this one's start
         *reinterpret_cast<uint4*>(q_tile + (c / 8) * (FA_BM * 128) + r * 128 + (((c % 8) ^ (r & 7)) << 4)) = v;
       }
       fa_fence_async_shared();

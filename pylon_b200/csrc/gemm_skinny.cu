@@ -23,9 +23,11 @@ __device__ __forceinline__ uint4 load_stream_16(const void* p) {   // weights: r
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
-__device__ __forceinline__ uint4 load_cached_16(const void* p) {   // activations: shared by every block
+// Activations: shared by every block, so they may stay in L1; an ordinary (coherent) load, because under a dependent
+// launch the kernel that writes them may still be running when this one starts.
+__device__ __forceinline__ uint4 load_cached_16(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
@@ -54,13 +56,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
   extern __shared__ float reduce[];   // [WARPS][NT * 16][MT * 8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (NT * 16);
-  // blockIdx.y splits k (gridDim.y parts): each part writes its own float32 partial result
-  // [M, N] at y + part * M * ldy, and whoever consumes them adds them up.
-  const int all_steps = (K + 31) / 32;
-  const int share = (all_steps + gridDim.y - 1) / gridDim.y;
-  const int step_begin = blockIdx.y * share;
-  const int k_steps = min(all_steps, step_begin + share);
-  y += (size_t)blockIdx.y * M * ldy;
+  const int step_begin = 0, k_steps = (K + 31) / 32;
 
   const __nv_bfloat16* w_rows[NT][2];
 #pragma unroll
@@ -194,7 +190,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
 
 template <int MT, int NT, int WARPS, int UNROLL, bool SWIGLU, typename OutT>
 static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y, int M, int N, int K, long long ldx,
-                         long long ldw, long long ldy, cudaStream_t stream, int k_splits = 1) {
+                         long long ldw, long long ldy, cudaStream_t stream) {
   constexpr size_t smem = (size_t)WARPS * NT * 16 * MT * 8 * sizeof(float);
   auto kernel = gemm_skinny_kernel<MT, NT, WARPS, UNROLL, SWIGLU, OutT>;
   if (smem > 48 * 1024) {
@@ -206,7 +202,7 @@ static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y
     }
   }
   const int blocks = (N + NT * 16 - 1) / (NT * 16);
-  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks, k_splits), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(WARPS * 32), smem, stream, x, w, y, M, N, K, ldx, ldw, ldy);
   PYLON_CHECK_LAUNCH("gemm_skinny");
 }
 
@@ -236,19 +232,6 @@ extern "C" int pylon_gemm_skinny_bf16(const void* x, const void* w, void* y, int
   if (out_dtype == PYLON_DTYPE_F32)
     return pylon::dispatch_skinny<float>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)y, M, N, K, ldx, ldw, ldy, stream);
   PYLON_REFUSE("gemm_skinny: unknown result dtype %d", out_dtype);
-}
-
-// The product as k_splits float32 partial sums: y [k_splits, M, N] contiguous, whose sum over the first dimension is
-// x @ w.T.  For products with few weight rows (M <= 8): more blocks, more loads in flight; the reader adds the parts.
-extern "C" int pylon_gemm_skinny_partial(const void* x, const void* w, float* y, int M, int N, int K, long long ldx, long long ldw,
-                                         int k_splits, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 8) PYLON_REFUSE("gemm_skinny_partial: M = %d is more than 8 rows", M);
-  if (k_splits < 1 || k_splits > 16) PYLON_REFUSE("gemm_skinny_partial: %d parts", k_splits);
-  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("gemm_skinny_partial: K = %d and the row strides must be multiples of 8", K);
-  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16)) PYLON_REFUSE("gemm_skinny_partial: x and w must be 16-byte aligned");
-  if (ldx < K || ldw < K) PYLON_REFUSE("gemm_skinny_partial: a row stride is shorter than its row");
-  return pylon::launch_skinny<1, 1, 8, 2, false, float>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, y, M, N, K, ldx, ldw, N, stream, k_splits);
 }
 
 // silu(x gate^T) * (x up^T) in one kernel (M <= 16, bfloat16): w's rows are interleaved in groups of 8 (rows 16b..16b+7

@@ -5,8 +5,8 @@ every time; only the small integer arrays of the step (tokens, positions, length
 tables) change.  Such a step is captured once per batch size into a ``torch.cuda.CUDAGraph``
 over a static copy of those arrays; afterwards a step is one pinned-to-device copy and one
 graph launch.  Kernels read every length from the device, so a graph captured at one
-context length serves all of them; the number of key/value splits of the attention launch is
-fixed at capture for the longest context the engine holds.
+context length serves all of them: the decode attention divides the key tiles among its
+blocks inside the kernel, from the lengths of the step at hand.
 
 As in raun6k/Pylon (src/pylon/decode/graph.py:157-242): one graph per exact batch size, no
 padding to a larger one; a size whose capture failed is not tried again and runs eagerly;
