@@ -9,8 +9,7 @@
 // those 8 consecutive elements serve as the lane's k-slots of two MMAs, and no shared-memory
 // staging or ldmatrix is needed.  The warps of a block take interleaved 32-wide k-steps of
 // the same weight rows (so a block reads contiguous 512-byte runs) and their partial sums
-// are added in shared memory in a fixed order.  Loads are double-buffered in registers.  The
-// gate/up product can apply SwiGLU in its epilogue.
+// are added in shared memory in a fixed order.  Loads are double-buffered in registers.
 //
 // Stands in for the library products raun6k/Pylon's nn.Linear layers call at decode
 // (src/pylon/model/layers.py:26-27,126,138; src/pylon/model/model.py:144).
@@ -42,15 +41,9 @@ __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// SWIGLU fusion: the weight rows are interleaved in groups of 8 - rows 16b..16b+7 are gate rows
-// 8b..8b+7, rows 16b+8..16b+15 the matching up rows - so every block holds both halves of 8
-// outputs and stores silu(gate) * up, [M, N / 2], instead of the product itself.  (Taking
-// the residual add and the next RMSNorm into the product as well - the block that finishes
-// last normalising the rows - was tried and measured slower than the separate norm kernel.)
-
 // MT: 8-row tiles of x (M <= 8 * MT).  NT: 16-row tiles of W per block.  WARPS: k-split
-// inside a block.  SWIGLU: the fused epilogue described above (needs NT == 1).
-template <int MT, int NT, int WARPS, int UNROLL, bool SWIGLU, typename OutT>
+// inside a block.
+template <int MT, int NT, int WARPS, int UNROLL, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                                  OutT* __restrict__ y, int M, int N, int K, long long ldx, long long ldw, long long ldy) {
   extern __shared__ float reduce[];   // [WARPS][NT * 16][MT * 8]
@@ -160,39 +153,22 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const __nv_bflo
 #pragma unroll
       for (int i = 0; i < 4; ++i) mine[(mt * 8 + 2 * t + (i & 1)) * ROWS + nt * 16 + g + 8 * (i >> 1)] = acc[nt][mt][i];
   __syncthreads();
-  if (SWIGLU) {
-    // Rows 0..7 of the block are gate rows, rows 8..15 the matching up rows.
-    for (int e = threadIdx.x; e < 8 * COLS; e += WARPS * 32) {
-      const int m = e / 8, j = e % 8;
-      const int n = n0 + j;              // the gate row; its up row is n + 8
-      if (m < M && n + 8 < N) {
-        float gate = 0.f, up = 0.f;
+  for (int e = threadIdx.x; e < ROWS * COLS; e += WARPS * 32) {
+    const int m = e / ROWS, n = n0 + e % ROWS;
+    if (m < M && n < N) {
+      float sum = 0.f;
 #pragma unroll
-        for (int wv = 0; wv < WARPS; ++wv) {
-          gate += reduce[(size_t)wv * ROWS * COLS + m * ROWS + j];
-          up += reduce[(size_t)wv * ROWS * COLS + m * ROWS + j + 8];
-        }
-        store_out<OutT>(y + (size_t)m * ldy + (n0 >> 1) + j, gate / (1.f + __expf(-gate)) * up);
-      }
-    }
-  } else {
-    for (int e = threadIdx.x; e < ROWS * COLS; e += WARPS * 32) {
-      const int m = e / ROWS, n = n0 + e % ROWS;
-      if (m < M && n < N) {
-        float sum = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < WARPS; ++wv) sum += reduce[(size_t)wv * ROWS * COLS + e];
-        store_out<OutT>(y + (size_t)m * ldy + n, sum);
-      }
+      for (int wv = 0; wv < WARPS; ++wv) sum += reduce[(size_t)wv * ROWS * COLS + e];
+      store_out<OutT>(y + (size_t)m * ldy + n, sum);
     }
   }
 }
 
-template <int MT, int NT, int WARPS, int UNROLL, bool SWIGLU, typename OutT>
+template <int MT, int NT, int WARPS, int UNROLL, typename OutT>
 static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y, int M, int N, int K, long long ldx,
                          long long ldw, long long ldy, cudaStream_t stream) {
   constexpr size_t smem = (size_t)WARPS * NT * 16 * MT * 8 * sizeof(float);
-  auto kernel = gemm_skinny_kernel<MT, NT, WARPS, UNROLL, SWIGLU, OutT>;
+  auto kernel = gemm_skinny_kernel<MT, NT, WARPS, UNROLL, OutT>;
   if (smem > 48 * 1024) {
     static bool configured = false;
     if (!configured) {
@@ -209,10 +185,10 @@ static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y
 template <typename OutT>
 static int dispatch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y, int M, int N, int K, long long ldx,
                            long long ldw, long long ldy, cudaStream_t stream) {
-  if (M <= 8) return launch_skinny<1, 1, 8, 2, false, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-  if (M <= 16) return launch_skinny<2, 1, 8, 2, false, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-  if (M <= 32) return launch_skinny<4, 1, 8, 1, false, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
-  return launch_skinny<8, 2, 4, 1, false, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+  if (M <= 8) return launch_skinny<1, 1, 8, 2, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+  if (M <= 16) return launch_skinny<2, 1, 8, 2, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+  if (M <= 32) return launch_skinny<4, 1, 8, 1, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+  return launch_skinny<8, 2, 4, 1, OutT>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
 }
 
 }  // namespace pylon
@@ -232,20 +208,4 @@ extern "C" int pylon_gemm_skinny_bf16(const void* x, const void* w, void* y, int
   if (out_dtype == PYLON_DTYPE_F32)
     return pylon::dispatch_skinny<float>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)y, M, N, K, ldx, ldw, ldy, stream);
   PYLON_REFUSE("gemm_skinny: unknown result dtype %d", out_dtype);
-}
-
-// silu(x gate^T) * (x up^T) in one kernel (M <= 16, bfloat16): w's rows are interleaved in groups of 8 (rows 16b..16b+7
-// gate rows 8b..8b+7, rows 16b+8..16b+15 the matching up rows; N a multiple of 16); y [M, N / 2] (row stride ldy).
-extern "C" int pylon_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
-                                        long long ldy, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 16) PYLON_REFUSE("gemm_skinny_swiglu: M = %d is more than 16 rows", M);
-  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("gemm_skinny_swiglu: K = %d and the row strides must be multiples of 8", K);
-  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16)) PYLON_REFUSE("gemm_skinny_swiglu: x and w must be 16-byte aligned");
-  if (ldx < K || ldw < K) PYLON_REFUSE("gemm_skinny_swiglu: a row stride is shorter than its row");
-  if (N % 16 || !y || ldy < N / 2) PYLON_REFUSE("gemm_skinny_swiglu: N = %d must be a multiple of 16 and the result N / 2 columns wide", N);
-  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
-  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-  if (M <= 8) return pylon::launch_skinny<1, 1, 8, 2, true, __nv_bfloat16>(xp, wp, (__nv_bfloat16*)y, M, N, K, ldx, ldw, ldy, stream);
-  return pylon::launch_skinny<2, 1, 8, 2, true, __nv_bfloat16>(xp, wp, (__nv_bfloat16*)y, M, N, K, ldx, ldw, ldy, stream);
 }

@@ -1,14 +1,15 @@
-// y[part] = x[:, k-slice(part)] * w[:, k-slice(part)]^T for at most 8 activation rows, as float32
-// partial sums over `parts` slices of k: the product of a decode step whose result goes into
-// the residual stream (attention output and feed-forward down projections).  Whoever reads y
-// adds the parts up.
+// x * w^T for at most 64 activation rows - the products of a decode step - in three forms:
+//   partial sums   y[part] = x[:, k-slice(part)] * w[:, k-slice(part)]^T as float32, for results that go into
+//                  the residual stream (attention output and down projections); whoever reads y adds the parts up
+//   product        y = x * w^T in bfloat16 (one slice of k)
+//   SwiGLU         w's rows alternate in groups of 8 between gate and up rows; y = silu(gate) * up in bfloat16
 //
 // These products are small (20 to 50 MB of weights) and bound by how soon their bytes are in
 // flight, not by arithmetic.  One block takes a 64-row slab of w and one slice of k.  A producer
 // thread asks TMA for the slab box by box (64 rows x 64 k, 128-byte swizzle; the 8 x 64 box of x
 // rides on the same mbarrier) into a ring that holds a block's whole share, so all of it is on
 // its way after one round trip; four consumer warps (16 weight rows each) multiply with
-// mma.sync, w as the 16-row A operand, x as the 8-column B operand.  Streaming a matrix this
+// mma.sync, w as the 16-row A operand, x as 8-column B operands (MT of them for up to 8 * MT rows).  Streaming a matrix this
 // way took 6.4 us for the 2560 x 4096 output projection where per-thread 16-byte loads took 10.
 //
 // All waits on mbarriers are bounded: a wait that runs out sets an error word for the host and
@@ -25,9 +26,16 @@
 
 namespace pylon {
 
-constexpr int ST_ROWS = 64, ST_BK = 64, ST_STAGES = 7, ST_CONSUMERS = 4, ST_THREADS = 32 * (1 + ST_CONSUMERS);
-constexpr int ST_W_BYTES = ST_ROWS * ST_BK * 2, ST_X_BYTES = 8 * ST_BK * 2, ST_STAGE_BYTES = ST_W_BYTES + ST_X_BYTES;
-constexpr size_t ST_SMEM = (size_t)ST_STAGES * ST_STAGE_BYTES + 1024 /* alignment slack */ + 128 /* barriers */;
+constexpr int ST_ROWS = 64, ST_BK = 64, ST_CONSUMERS = 4, ST_THREADS = 32 * (1 + ST_CONSUMERS);
+constexpr int ST_W_BYTES = ST_ROWS * ST_BK * 2;
+enum StreamForm { ST_PARTIAL = 0, ST_PRODUCT = 1, ST_SWIGLU = 2 };
+// MT: 8-row tiles of x.  A stage holds the box of w and the box of x; as many stages as fit in 64 KB (three blocks to an SM).
+template <int MT>
+struct StreamRing {
+  static constexpr int X_BYTES = 8 * MT * ST_BK * 2, STAGE_BYTES = ST_W_BYTES + X_BYTES;
+  static constexpr int STAGES = (64 * 1024) / STAGE_BYTES;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 128 /* barriers */;
+};
 constexpr unsigned ST_WAIT_LIMIT = 1u << 22;   // try_wait calls before a wait gives up
 
 __device__ __forceinline__ unsigned st_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -62,13 +70,17 @@ __device__ __forceinline__ void st_mma(float (&c)[4], const unsigned (&a)[4], un
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Grid (parts, slabs of 64 weight rows).  error: 1 the producer, 2 a consumer gave up waiting.
+// Grid (parts, slabs of 64 weight rows).  y: float32 [parts, M, N] (ST_PARTIAL), bfloat16 [M, N] (ST_PRODUCT) or
+// bfloat16 [M, N / 2] (ST_SWIGLU), row stride ldy for the last two.  error: 1 the producer, 2 a consumer gave up waiting.
+template <int MT, int FORM>
 __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                                                                  float* __restrict__ y, int M, int N, int K, int* __restrict__ error) {
+                                                                     void* __restrict__ y, int M, int N, int K, long long ldy, int* __restrict__ error) {
+  using Ring = StreamRing<MT>;
+  constexpr int STAGES = Ring::STAGES, STAGE_BYTES = Ring::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(stages + (size_t)ST_STAGES * ST_STAGE_BYTES);
-  uint64_t* empty = full + ST_STAGES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages + (size_t)STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int part = blockIdx.x, parts = gridDim.x, n0 = blockIdx.y * ST_ROWS;
   const int k_boxes = (K + ST_BK - 1) / ST_BK;
@@ -76,7 +88,7 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
 
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < ST_STAGES; ++s) { st_mbar_init(&full[s], 1); st_mbar_init(&empty[s], ST_CONSUMERS); }
+    for (int s = 0; s < STAGES; ++s) { st_mbar_init(&full[s], 1); st_mbar_init(&empty[s], ST_CONSUMERS); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -86,23 +98,23 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
       // The weights do not depend on the kernel before this one: the boxes that fit in the ring are asked for before
       // this kernel waits for it (a dependent launch may start while that kernel is still running); the activations'
       // boxes follow after the wait, on the same barriers.
-      const int ahead = min(ST_STAGES, box_end - box_begin);
+      const int ahead = min(STAGES, box_end - box_begin);
       for (int i = 0; i < ahead; ++i) {
-        st_mbar_expect_tx(&full[i], ST_STAGE_BYTES);   // rows past N, M or K arrive as zeros and count all the same
-        st_tma_load(stages + (size_t)i * ST_STAGE_BYTES, &map_w, &full[i], (box_begin + i) * ST_BK, n0);
+        st_mbar_expect_tx(&full[i], STAGE_BYTES);   // rows past N, M or K arrive as zeros and count all the same
+        st_tma_load(stages + (size_t)i * STAGE_BYTES, &map_w, &full[i], (box_begin + i) * ST_BK, n0);
       }
       grid_dependency_wait();
       allow_dependents();
       for (int i = 0; i < ahead; ++i)
-        st_tma_load(stages + (size_t)i * ST_STAGE_BYTES + ST_W_BYTES, &map_x, &full[i], (box_begin + i) * ST_BK, 0);
+        st_tma_load(stages + (size_t)i * STAGE_BYTES + ST_W_BYTES, &map_x, &full[i], (box_begin + i) * ST_BK, 0);
       unsigned stage = 0, phase = 1;   // the ring has gone round once
       for (int box = box_begin + ahead; box < box_end; ++box) {
         if (!st_mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); break; }
-        unsigned char* dst = stages + (size_t)stage * ST_STAGE_BYTES;
-        st_mbar_expect_tx(&full[stage], ST_STAGE_BYTES);
+        unsigned char* dst = stages + (size_t)stage * STAGE_BYTES;
+        st_mbar_expect_tx(&full[stage], STAGE_BYTES);
         st_tma_load(dst, &map_w, &full[stage], box * ST_BK, n0);
         st_tma_load(dst + ST_W_BYTES, &map_x, &full[stage], box * ST_BK, 0);
-        if (++stage == ST_STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
     return;
@@ -113,36 +125,63 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
   const int slab_row = (warp - 1) * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);   // this lane's row of w for ldmatrix
   const unsigned w_row_offset = (unsigned)slab_row * 128, w_xor = (unsigned)(slab_row & 7);
   const unsigned x_row_offset = (unsigned)(lane & 7) * 128, x_xor = (unsigned)(lane & 7);
-  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // even and odd k-steps: two MMA chains
+  float acc[MT][2][4];   // per tile of x: even and odd k-steps, two MMA chains
+#pragma unroll
+  for (int j = 0; j < MT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][0][i] = acc[j][1][i] = 0.f;
   unsigned stage = 0, phase = 0;
   bool alive = true;
   for (int box = box_begin; box < box_end; ++box) {
     if (!st_mbar_wait(&full[stage], phase)) { atomicExch(error, 2); alive = false; break; }
-    const unsigned w_box = st_smem(stages + (size_t)stage * ST_STAGE_BYTES), x_box = w_box + ST_W_BYTES;
+    const unsigned w_box = st_smem(stages + (size_t)stage * STAGE_BYTES), x_box = w_box + ST_W_BYTES;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {   // 32 k each
-      unsigned b[4];                          // x: units 4 * half .. + 3 of rows 0..7
-      st_ldmatrix_x4(b, x_box + x_row_offset + ((((unsigned)(4 * half) + (lane >> 3)) ^ x_xor) << 4));
+      unsigned a[2][4];
 #pragma unroll
-      for (int step = 0; step < 2; ++step) {  // 16 k each
-        unsigned a[4];
-        st_ldmatrix_x4(a, w_box + w_row_offset + ((((unsigned)(4 * half + 2 * step) + (lane >> 4)) ^ w_xor) << 4));
-        st_mma(acc[step], a, b[2 * step], b[2 * step + 1]);
+      for (int step = 0; step < 2; ++step)    // 16 k each
+        st_ldmatrix_x4(a[step], w_box + w_row_offset + ((((unsigned)(4 * half + 2 * step) + (lane >> 4)) ^ w_xor) << 4));
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        unsigned b[4];                         // x: units 4 * half .. + 3 of rows 8j .. 8j + 7
+        st_ldmatrix_x4(b, x_box + (unsigned)(j * 8 * 128) + x_row_offset + ((((unsigned)(4 * half) + (lane >> 3)) ^ x_xor) << 4));
+        st_mma(acc[j][0], a[0], b[0], b[1]);
+        st_mma(acc[j][1], a[1], b[2], b[3]);
       }
     }
     __syncwarp();
     if (lane == 0) st_mbar_arrive(&empty[stage]);
-    if (++stage == ST_STAGES) { stage = 0; phase ^= 1; }
+    if (++stage == STAGES) { stage = 0; phase ^= 1; }
   }
   if (!alive) return;
 
-  // Accumulator element i of lane (g, t): weight row g + 8 * (i / 2), activation row 2 * t + (i % 2).
+  // Accumulator element i of lane (g, t): weight row g + 8 * (i / 2), activation row 2 * t + (i % 2) of its tile.
   const int g = lane >> 2, t = lane & 3;
-  float* out = y + (size_t)part * M * N;
+  const int row0 = n0 + (warp - 1) * 16 + g;   // the weight row of elements 0 and 1; elements 2 and 3: row0 + 8
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int n = n0 + (warp - 1) * 16 + g + 8 * (i >> 1), m = 2 * t + (i & 1);
-    if (n < N && m < M) out[(size_t)m * N + n] = acc[0][i] + acc[1][i];
+  for (int j = 0; j < MT; ++j) {
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = acc[j][0][i] + acc[j][1][i];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int m = j * 8 + 2 * t + e;
+      if (m >= M) continue;
+      if (FORM == ST_PARTIAL) {
+        float* out = reinterpret_cast<float*>(y) + ((size_t)part * M + m) * N;
+        if (row0 < N) out[row0] = v[e];
+        if (row0 + 8 < N) out[row0 + 8] = v[2 + e];
+      } else if (FORM == ST_PRODUCT) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)m * ldy;
+        if (row0 < N) out[row0] = __float2bfloat16_rn(v[e]);
+        if (row0 + 8 < N) out[row0 + 8] = __float2bfloat16_rn(v[2 + e]);
+      } else {   // rows row0 (gate) and row0 + 8 (its up row) are both this lane's
+        if (row0 + 8 < N) {
+          const float gate = v[e], up = v[2 + e];
+          reinterpret_cast<__nv_bfloat16*>(y)[(size_t)m * ldy + (n0 + (warp - 1) * 16) / 2 + g] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
+        }
+      }
+    }
   }
 }
 
@@ -194,31 +233,62 @@ static bool matrix_map(CUtensorMap* map, const void* base, long long rows, long 
   return true;
 }
 
+template <int MT, int FORM>
+static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, void* y, int M, int N, int K, long long ldy, int parts, int slabs,
+                         int* error, cudaStream_t stream) {
+  auto kernel = gemm_stream_kernel<MT, FORM>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamRing<MT>::SMEM);
+    if (err != cudaSuccess) PYLON_REFUSE("gemm_stream: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(parts, slabs), dim3(ST_THREADS), StreamRing<MT>::SMEM, stream, map_w, map_x, y, M, N, K, ldy, error);
+  PYLON_CHECK_LAUNCH("gemm_stream");
+}
+
+template <int FORM>
+static int dispatch_stream(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy, int parts,
+                           int* error, cudaStream_t stream, const char* name) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) PYLON_REFUSE("%s: M = %d is more than 64 rows", name, M);
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("%s: K = %d and the row strides must be multiples of 8", name, K);
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 4)) PYLON_REFUSE("%s: x and w must be 16-byte aligned", name);
+  if (ldx < K || ldw < K) PYLON_REFUSE("%s: a row stride is shorter than its row", name);
+  const int k_boxes = (K + ST_BK - 1) / ST_BK, slabs = (N + ST_ROWS - 1) / ST_ROWS;
+  if (parts < 1 || parts > k_boxes || parts > 65535 || slabs > 65535) PYLON_REFUSE("%s: %d parts over %d slices of k, %d slabs", name, parts, k_boxes, slabs);
+  if (!error) PYLON_REFUSE("%s: an error word is needed", name);
+  const int tiles = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  CUtensorMap map_w, map_x;
+  if (!matrix_map(&map_w, w, N, K, ldw, ST_ROWS) || !matrix_map(&map_x, x, M, K, ldx, 8 * tiles)) PYLON_REFUSE("%s: the tensor maps could not be made", name);
+  if (tiles == 1) return launch_stream<1, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
+  if (tiles == 2) return launch_stream<2, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
+  if (tiles == 4) return launch_stream<4, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
+  return launch_stream<8, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
+}
+
 }  // namespace pylon
 
-// x: bfloat16 [M, K] (row stride ldx), M <= 8; w: bfloat16 [N, K] (row stride ldw); y: float32 [parts, M, N] contiguous,
+// x: bfloat16 [M, K] (row stride ldx), M <= 64; w: bfloat16 [N, K] (row stride ldw); y: float32 [parts, M, N] contiguous,
 // whose sum over the first dimension is x @ w.T.  K and the row strides multiples of 8, x and w 16-byte aligned,
 // 1 <= parts <= number of 64-wide slices of k.  error: one int in device memory that the kernel sets non-zero if one of its
 // waits ran out (the result is then void).
 extern "C" int pylon_gemm_stream_partial(const void* x, const void* w, float* y, int M, int N, int K, long long ldx, long long ldw,
                                          int parts, int* error, cudaStream_t stream) {
-  using namespace pylon;
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 8) PYLON_REFUSE("gemm_stream: M = %d is more than 8 rows", M);
-  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("gemm_stream: K = %d and the row strides must be multiples of 8", K);
-  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 4)) PYLON_REFUSE("gemm_stream: x and w must be 16-byte aligned");
-  if (ldx < K || ldw < K) PYLON_REFUSE("gemm_stream: a row stride is shorter than its row");
-  const int k_boxes = (K + ST_BK - 1) / ST_BK, slabs = (N + ST_ROWS - 1) / ST_ROWS;
-  if (parts < 1 || parts > k_boxes || parts > 65535 || slabs > 65535) PYLON_REFUSE("gemm_stream: %d parts over %d slices of k, %d slabs", parts, k_boxes, slabs);
-  if (!error) PYLON_REFUSE("gemm_stream: an error word is needed");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ST_SMEM);
-    if (err != cudaSuccess) PYLON_REFUSE("gemm_stream: %s", cudaGetErrorString(err));
-    configured = true;
-  }
-  CUtensorMap map_w, map_x;
-  if (!matrix_map(&map_w, w, N, K, ldw, ST_ROWS) || !matrix_map(&map_x, x, M, K, ldx, 8)) PYLON_REFUSE("gemm_stream: the tensor maps could not be made");
-  launch_dependent<LAUNCH_GEMM>(gemm_stream_kernel, dim3(parts, slabs), dim3(ST_THREADS), ST_SMEM, stream, map_w, map_x, y, M, N, K, error);
-  PYLON_CHECK_LAUNCH("gemm_stream");
+  return pylon::dispatch_stream<pylon::ST_PARTIAL>(x, w, y, M, N, K, ldx, ldw, N, parts, error, stream, "gemm_stream_partial");
+}
+
+// The product itself: y bfloat16 [M, N], row stride ldy.
+extern "C" int pylon_gemm_stream_bf16(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                      long long ldy, int* error, cudaStream_t stream) {
+  if (ldy < N) PYLON_REFUSE("gemm_stream_bf16: a row stride is shorter than its row");
+  return pylon::dispatch_stream<pylon::ST_PRODUCT>(x, w, y, M, N, K, ldx, ldw, ldy, 1, error, stream, "gemm_stream_bf16");
+}
+
+// silu(x gate^T) * (x up^T): w's rows are interleaved in groups of 8 (rows 16b..16b+7 gate rows 8b..8b+7, rows 16b+8..16b+15
+// the matching up rows; N a multiple of 16); y bfloat16 [M, N / 2], row stride ldy.
+extern "C" int pylon_gemm_stream_swiglu(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                        long long ldy, int* error, cudaStream_t stream) {
+  if (N % 16 || ldy < N / 2) PYLON_REFUSE("gemm_stream_swiglu: N = %d must be a multiple of 16 and the result N / 2 columns wide", N);
+  return pylon::dispatch_stream<pylon::ST_SWIGLU>(x, w, y, M, N, K, ldx, ldw, ldy, 1, error, stream, "gemm_stream_swiglu");
 }

@@ -76,10 +76,11 @@ _SIGNATURES = {
     },
     "gemm_skinny.cu": {
         "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
-        "pylon_gemm_skinny_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     },
     "gemm_stream.cu": {
         "pylon_gemm_stream_partial": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p],
+        "pylon_gemm_stream_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
+        "pylon_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
     },
     "gemm_tcgen05.cu": {
         "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
@@ -315,7 +316,7 @@ def _tcgen05_fills_the_sms(m: int, n: int) -> bool:
     return tiles >= 0.8 * rounds * _SM_COUNT
 
 
-STREAM_MAX_ROWS = 8   # up to this many rows the products for the residual stream run on the TMA-fed kernel
+STREAM_MAX_ROWS = 32   # up to this many rows the TMA-fed kernel beats the library (it takes up to 64)
 STREAM_MAX_PARTS = 4
 
 
@@ -347,7 +348,7 @@ def stream_error_word(device: torch.device) -> torch.Tensor:
 
 
 def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int] = None) -> torch.Tensor:
-    """bfloat16 ``x [M <= 8, K] @ w [N, K].T`` as float32 partial sums ``[parts, M, N]`` over
+    """bfloat16 ``x [M <= 64, K] @ w [N, K].T`` as float32 partial sums ``[parts, M, N]`` over
     slices of k, the weights streamed by TMA through a shared-memory ring.  ``parts`` defaults
     to what gives every SM up to three blocks (64 weight rows x one slice each), at most
     ``STREAM_MAX_PARTS``: more parts cost the reader more than they save here (the norm that adds
@@ -368,6 +369,23 @@ def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int]
     return y
 
 
+def linear_stream(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """bfloat16 ``x [M <= 64, K] @ w [N, K].T`` on the TMA-fed kernel, one block per 64 weight rows
+    over the whole of k; with ``swiglu`` the rows of ``w`` are interleaved gate/up groups (see
+    :func:`interleave_gate_up`) and the result is ``silu(gate) * up``, ``[M, N / 2]``."""
+    _need_cuda(x, w)
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
+          "linear_stream: bfloat16 x [M, K] and w [N, K]")
+    _need(x.stride(1) == 1 and w.stride(1) == 1, "linear_stream: the reduced dimension must be contiguous")
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
+    library = _library("gemm_stream.cu")
+    entry = library.pylon_gemm_stream_swiglu if swiglu else library.pylon_gemm_stream_bf16
+    _check(library, entry(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), _ptr(stream_error_word(x.device)), _stream()))
+    return y
+
+
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """The weight-streaming kernel itself: bfloat16 ``x [M <= 64, K] @ w [N, K].T`` with ``K``
     and the row strides multiples of 8 and 16-byte aligned operands; anything else is refused."""
@@ -383,7 +401,6 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = tor
     return y
 
 
-FUSED_MAX_ROWS = 8   # up to this many rows the gate/up product applies SwiGLU itself
 TCGEN05_MIN_ROWS = 128   # from this many rows the gate/up product runs on our tcgen05 kernel, SwiGLU in its epilogue
 
 _tcgen05_error: dict[str, torch.Tensor] = {}
@@ -446,18 +463,15 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for weights stacked by :func:`interleave_gate_up`:
-    one kernel for few rows, the product and the SwiGLU kernel otherwise."""
+    one kernel for few rows (the TMA-fed decode kernel) and for many (the tcgen05 kernel), the
+    library product and the SwiGLU kernel in between."""
     _need_cuda(x, w_interleaved)
     n, k = w_interleaved.shape
     m = x.shape[0]
-    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and x.dim() == 2 and m <= FUSED_MAX_ROWS and x.shape[1] == k
+    if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and x.dim() == 2 and m <= STREAM_MAX_ROWS and x.shape[1] == k
             and k % 8 == 0 and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0
             and w_interleaved.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):
-        y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-        library = _library("gemm_skinny.cu")
-        _check(library, library.pylon_gemm_skinny_swiglu(_ptr(x), _ptr(w_interleaved), _ptr(y), m, n, k, x.stride(0), w_interleaved.stride(0),
-                                                         n // 2, _stream()))
-        return y
+        return linear_stream(x, w_interleaved, swiglu=True)
     if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and k % 8 == 0
             and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0 and w_interleaved.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):

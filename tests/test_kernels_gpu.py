@@ -122,11 +122,12 @@ def test_skinny_gemm_every_row_count(m, n, k):
     torch.testing.assert_close(ops.linear_skinny(view, w, torch.float32).double(), view.double() @ w.double().T, rtol=1e-3, atol=1e-3)
 
 
-@pytest.mark.parametrize("m", [1, 7, 8, 20])
+@pytest.mark.parametrize("m", [1, 7, 8, 9, 20, 32, 33, 64, 70])
 @pytest.mark.parametrize("inter, k", [(9728, 2560), (224, 96), (24, 64)])
 def test_linear_swiglu_with_interleaved_weights(m, inter, k):
     """silu(x gate^T) * (x up^T) from weights stacked in alternating groups of 8 rows: fused in
-    the product's kernel for few rows, product plus SwiGLU kernel for more."""
+    the product's kernel for few rows (every tile count of the TMA-fed kernel), product plus
+    SwiGLU kernel for more."""
     from pylon_b200.kernels import ops
 
     gate = (torch.randn(inter, k, device=DEVICE) * 0.05).to(torch.bfloat16)
@@ -137,6 +138,9 @@ def test_linear_swiglu_with_interleaved_weights(m, inter, k):
     g, u = x.double() @ gate.double().T, x.double() @ up.double().T
     want = g * torch.sigmoid(g) * u
     torch.testing.assert_close(ops.linear_swiglu(x, stacked).double(), want, rtol=2e-2, atol=2e-2)
+    if m <= 64:   # the TMA-fed kernel itself, also where the dispatch prefers the library
+        torch.testing.assert_close(ops.linear_stream(x, stacked, swiglu=True).double(), want, rtol=2e-2, atol=2e-2)
+        assert int(ops.stream_error_word(torch.device(DEVICE)).item()) == 0
     # the SwiGLU kernel alone on interleaved columns, both dtypes
     for dtype in (torch.bfloat16, torch.float32):
         columns = torch.randn(m, 2 * inter, device=DEVICE).to(dtype)
@@ -200,7 +204,7 @@ def test_tcgen05_gemm_with_swiglu_epilogue(m, inter, k):
         ops.linear_tcgen05(torch.zeros(128, 20, device=DEVICE, dtype=torch.bfloat16), torch.zeros(64, 20, device=DEVICE, dtype=torch.bfloat16))
 
 
-@pytest.mark.parametrize("m", [1, 8])
+@pytest.mark.parametrize("m", [1, 8, 19, 32])
 @pytest.mark.parametrize("n, k", [(2560, 4096), (2560, 9728), (96, 2048)])
 def test_partial_sums_for_the_residual(m, n, k):
     """Products with few weight rows come back as float32 partial sums over slices of k; the
@@ -230,13 +234,15 @@ def test_partial_sums_for_the_residual(m, n, k):
     picked = ops.add_rmsnorm(residual.clone(), parts, weight, eps, torch.bfloat16, rows=rows)
     torch.testing.assert_close(picked.double(), want[m - 1 :], rtol=3e-2, atol=3e-2)
     # many rows, or a matrix with many rows of its own: the plain product
-    assert ops.linear_for_residual(torch.zeros(9, k, device=DEVICE, dtype=torch.bfloat16), w).dim() == 2
+    assert ops.linear_for_residual(torch.zeros(33, k, device=DEVICE, dtype=torch.bfloat16), w).dim() == 2
 
 
-@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 2560, 4096), (5, 100, 72), (3, 2564, 4104), (8, 130, 1032), (7, 6144, 2560)])
+@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 2560, 4096), (5, 100, 72), (3, 2564, 4104), (8, 130, 1032), (7, 6144, 2560),
+                                     (9, 130, 1032), (16, 2560, 4096), (23, 100, 72), (32, 328, 264), (47, 2564, 520), (64, 2560, 1024)])
 def test_stream_gemm_partial_sums(m, n, k):
     """The TMA-fed decode product: row, column and k counts that do not fill its 64 x 64 boxes,
-    every sensible number of parts, and a strided activation view."""
+    every tile count of the activations, every sensible number of parts, a strided activation
+    view; and the same product in its bfloat16 form."""
     from pylon_b200.kernels import ops
 
     x = torch.randn(m, k + 16, device=DEVICE).to(torch.bfloat16)[:, 8 : 8 + k]
@@ -247,9 +253,10 @@ def test_stream_gemm_partial_sums(m, n, k):
         y = ops.linear_stream_partial(x, w, parts)
         assert y.dtype == torch.float32 and y.shape[1:] == (m, n) and (parts is None or y.shape[0] == parts)
         torch.testing.assert_close(y.double().sum(0), want, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(ops.linear_stream(x, w).double(), want, rtol=2e-2, atol=2e-2)
     assert int(ops.stream_error_word(torch.device(DEVICE)).item()) == 0
-    with pytest.raises(ops.KernelError, match="more than 8 rows"):
-        ops.linear_stream_partial(torch.zeros(9, k, device=DEVICE, dtype=torch.bfloat16), w)
+    with pytest.raises(ops.KernelError, match="more than 64 rows"):
+        ops.linear_stream_partial(torch.zeros(65, k, device=DEVICE, dtype=torch.bfloat16), w)
     with pytest.raises(ops.KernelError, match="parts"):
         ops.linear_stream_partial(x, w, k_boxes + 1)
 
