@@ -468,14 +468,16 @@ extern "C" int pylon_add_rmsnorm(float* residual, const void* delta, const float
   PYLON_CHECK_LAUNCH("add_rmsnorm");
 }
 
-// The same with the delta given as `parts` float32 partial sums [parts, all rows, width] (contiguous): bfloat16 output,
-// width a multiple of 4 and at most 8192, no row selection.
-extern "C" int pylon_add_parts_rmsnorm(float* residual, const float* delta_parts, int parts, const float* weight, void* out,
-                                       int n_rows, int width, float eps, cudaStream_t stream) {
+// The same with the delta given as `parts` float32 partial sums [parts, all_rows, width] (contiguous): bfloat16 output,
+// width a multiple of 4 and at most 8192.  rows: null (every row: the sum is added to the residual in place, n_rows =
+// all_rows) or n_rows int32 row numbers (those rows only, normalised from residual + sum; the residual stays as it is).
+extern "C" int pylon_add_parts_rmsnorm(float* residual, const float* delta_parts, int parts, const float* weight, const int* rows,
+                                       void* out, int n_rows, int all_rows, int width, float eps, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (parts < 1 || !delta_parts) PYLON_REFUSE("add_parts_rmsnorm: %d parts", parts);
-  if (!launch_add_rmsnorm_vec<__nv_bfloat16, float>(residual, delta_parts, weight, nullptr, (__nv_bfloat16*)out, n_rows, width, eps, 1, parts,
-                                                     (long long)n_rows * width, stream))
+  if (!rows && n_rows != all_rows) PYLON_REFUSE("add_parts_rmsnorm: %d of %d rows without a row selection", n_rows, all_rows);
+  if (!launch_add_rmsnorm_vec<__nv_bfloat16, float>(residual, delta_parts, weight, rows, (__nv_bfloat16*)out, n_rows, width, eps, rows ? 0 : 1,
+                                                     parts, (long long)all_rows * width, stream))
     PYLON_REFUSE("add_parts_rmsnorm: width %d must be a multiple of 4, at most 8192, with 16-byte aligned buffers", width);
   PYLON_CHECK_LAUNCH("add_parts_rmsnorm");
 }

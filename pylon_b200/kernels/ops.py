@@ -65,7 +65,7 @@ _SIGNATURES = {
         "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "pylon_residual_add": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
-        "pylon_add_parts_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+        "pylon_add_parts_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -162,12 +162,14 @@ def add_rmsnorm(
     :func:`linear_for_residual`): their sum is the delta."""
     _need_cuda(residual, delta, weight, rows, out)
     if delta is not None and delta.dim() == 3:
-        if rows is None and out is None and out_dtype == torch.bfloat16 and delta.dtype == torch.float32 and delta.is_contiguous() \
-                and delta.shape[1:] == residual.shape and residual.is_contiguous() and residual.shape[1] % 4 == 0 and residual.shape[1] <= 8192:
-            normed = torch.empty(residual.shape, dtype=torch.bfloat16, device=residual.device)
+        if out is None and out_dtype == torch.bfloat16 and delta.dtype == torch.float32 and delta.is_contiguous() \
+                and delta.shape[1:] == residual.shape and residual.is_contiguous() and residual.shape[1] % 4 == 0 and residual.shape[1] <= 8192 \
+                and (rows is None or (rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous())):
+            n_rows = residual.shape[0] if rows is None else rows.shape[0]
+            normed = torch.empty((n_rows, residual.shape[1]), dtype=torch.bfloat16, device=residual.device)
             library = _library("elementwise.cu")
-            _check(library, library.pylon_add_parts_rmsnorm(_ptr(residual), _ptr(delta), delta.shape[0], _ptr(weight), _ptr(normed),
-                                                            residual.shape[0], residual.shape[1], float(eps), _stream()))
+            _check(library, library.pylon_add_parts_rmsnorm(_ptr(residual), _ptr(delta), delta.shape[0], _ptr(weight), _ptr(rows), _ptr(normed),
+                                                            n_rows, residual.shape[0], residual.shape[1], float(eps), _stream()))
             return normed
         delta = delta.sum(dim=0).to(out_dtype)
     _need(residual.dtype == torch.float32 and residual.dim() == 2 and residual.is_contiguous(), "add_rmsnorm: residual must be contiguous float32 [T, width]")
