@@ -195,9 +195,9 @@ def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
     assert not finished and produced == batch * steps, (len(finished), produced)
     while scheduler.has_work():
         engine.tick()
-    # per step: the packed int32 metadata buffer goes up, one int32 token per request comes back
+    # per step: the packed int32 metadata buffer goes up; one int32 token per request and the kernels' four error words come back
     layout = StepLayout(tokens=batch, rows=batch, logits=batch, table_widths=(CONTEXT // PAGE_SIZE,))
-    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4, "d2h_bytes_per_step": batch * 4}
+    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4, "d2h_bytes_per_step": batch * 4 + 16}
 
 
 def time_prefill(engine, torch, repeats: int, rng) -> dict:

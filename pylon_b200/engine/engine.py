@@ -22,6 +22,7 @@ from pylon_b200.config.engine_config import EngineConfig
 from pylon_b200.config.registry import ARCHITECTURES, read_config
 from pylon_b200.engine.scheduler import GenerationResult, Scheduler
 from pylon_b200.engine.step import StepEntry, StepFunction
+from pylon_b200.kernels import ops
 from pylon_b200.models.decoder import DecoderModel
 from pylon_b200.sampling.params import SamplingParams
 from pylon_b200.sampling.sampler import Sampler
@@ -165,7 +166,13 @@ class Engine:
     def tick(self) -> list[GenerationResult]:
         """One scheduler tick: admit, run one step, accept its tokens."""
         with torch.cuda.device(self.device):
-            return self.scheduler.tick()
+            return self._tick()
+
+    def _tick(self) -> list[GenerationResult]:
+        results = self.scheduler.tick()
+        # the tick has read its tokens back, so the device is idle: a 16-byte look at the kernels' error words
+        ops.raise_on_kernel_errors(self.device)
+        return results
 
     def default_stop_ids(self) -> tuple[int, ...]:
         return tuple(self.spec.eos_token_ids)
@@ -196,7 +203,7 @@ class Engine:
                     stop = params.stop_ids if params.stop_ids is not None else self.default_stop_ids()
                     self.scheduler.add(request_id, prompt, params, stop)
                     ids.append(request_id)
-                for result in self.scheduler.tick():
+                for result in self._tick():
                     results[result.request_id] = result
         ordered = [results[request_id] for request_id in ids]
         for result in ordered:

@@ -60,6 +60,34 @@ def _check(library: ctypes.CDLL, code: int) -> None:
         raise KernelError(library.pylon_last_error().decode(errors="replace") or f"kernel call failed ({code})")
 
 
+# Kernels that wait on mbarriers (TMA copies, tensor-core completion) bound every wait; one that
+# runs out sets its word here instead of hanging, and the result of that launch is void.  One
+# tensor per device: [tcgen05 product, attention, TMA-fed decode product, unused].
+_error_word_storage: dict[str, torch.Tensor] = {}
+_ERROR_WORD_NAMES = ("tcgen05 product", "attention", "TMA-fed decode product")
+
+
+def _error_words(device: torch.device) -> torch.Tensor:
+    key = str(device)
+    if key not in _error_word_storage:
+        _error_word_storage[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _error_word_storage[key]
+
+
+def raise_on_kernel_errors(device: torch.device) -> None:
+    """Reads the error words of ``device`` (a 16-byte copy that waits for the work queued so
+    far) and raises if a kernel gave up one of its bounded waits since the last call; the
+    words are cleared, so the next call reports only what happens from now on."""
+    key = str(device)
+    if key not in _error_word_storage:
+        return   # no kernel that can set them has run
+    words = _error_word_storage[key].cpu().tolist()
+    if any(words):
+        _error_word_storage[key].zero_()
+        what = ", ".join(f"{name} (code {code})" for name, code in zip(_ERROR_WORD_NAMES, words) if code)
+        raise KernelError(f"a bounded wait ran out in: {what}; the results of that step are void")
+
+
 _SIGNATURES = {
     "elementwise.cu": {
         "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -337,16 +365,10 @@ def linear_for_residual(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return linear(x, w)
 
 
-_stream_error: dict[str, torch.Tensor] = {}
-
-
 def stream_error_word(device: torch.device) -> torch.Tensor:
     """The int32 word the TMA-fed decode product sets when one of its bounded waits ran out
     (its result is then void).  Zero in every healthy run."""
-    key = str(device)
-    if key not in _stream_error:
-        _stream_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _stream_error[key]
+    return _error_words(device)[2:3]
 
 
 def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int] = None) -> torch.Tensor:
@@ -405,16 +427,10 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = tor
 
 TCGEN05_MIN_ROWS = 128   # from this many rows the gate/up product runs on our tcgen05 kernel, SwiGLU in its epilogue
 
-_tcgen05_error: dict[str, torch.Tensor] = {}
-
-
 def tcgen05_error_word(device: torch.device) -> torch.Tensor:
     """The int32 word the tcgen05 kernels set when one of their bounded waits ran out
-    (0 = never).  Reading it synchronises; tests and the benchmark look at it."""
-    key = str(device)
-    if key not in _tcgen05_error:
-        _tcgen05_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tcgen05_error[key]
+    (the result of that launch is then void).  Zero in every healthy run."""
+    return _error_words(device)[0:1]
 
 
 def tcgen05_force_tile(columns: int = 0) -> None:
@@ -484,16 +500,10 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------
 # attention over the paged cache
 # ---------------------------------------------------------------------------------------
-_attention_error: dict[str, torch.Tensor] = {}
-
-
 def attention_error_word(device: torch.device) -> torch.Tensor:
     """The int32 word the attention kernels set when a bounded wait for one of their TMA copies
     ran out (the output of that launch is then void).  Zero in every healthy run."""
-    key = str(device)
-    if key not in _attention_error:
-        _attention_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _attention_error[key]
+    return _error_words(device)[1:2]
 
 
 def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:

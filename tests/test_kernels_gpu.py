@@ -261,6 +261,21 @@ def test_stream_gemm_partial_sums(m, n, k):
         ops.linear_stream_partial(x, w, k_boxes + 1)
 
 
+def test_kernel_error_words_are_reported_once():
+    """A kernel whose bounded wait ran out sets a word on the device; the engine's check turns
+    it into an exception and clears it.  (The word is set from the host here: no kernel is made
+    to give up.)"""
+    from pylon_b200.kernels import ops
+
+    device = torch.device(DEVICE)
+    ops.raise_on_kernel_errors(device)            # nothing pending after the tests before this one
+    ops.attention_error_word(device).fill_(3)
+    with pytest.raises(ops.KernelError, match="attention \\(code 3\\)"):
+        ops.raise_on_kernel_errors(device)
+    ops.raise_on_kernel_errors(device)            # cleared
+    assert int(ops.tcgen05_error_word(device).item()) == 0 and int(ops.stream_error_word(device).item()) == 0
+
+
 def test_skinny_gemm_refuses():
     from pylon_b200.kernels import ops
 
