@@ -65,7 +65,7 @@ struct FaParams {
   const int* q_start;
   const int* kv_len;
   const int* block_table;
-  int table_width, page_size, num_pages, nq, nkv, group, window, skip_small;
+  int table_width, page_size, num_pages, nq, nkv, group, window, skip_small, first_row;
   float scale_log2;
   int* error;
 };
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   uint64_t* q_full = pv_done + 1;      // the query tile is in shared memory
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_full + 1);
 
-  const int row = blockIdx.y, kv_head = blockIdx.x;
+  const int row = p.first_row + blockIdx.y, kv_head = blockIdx.x;
   const int q0 = p.q_start[row];
   const int q_len = p.q_start[row + 1] - q0;
   const int G = p.group;
@@ -487,13 +487,14 @@ extern "C" int pylon_attention_tcgen05_head_dim() { return D; }
 
 // q: bfloat16 [tokens, >= nq*D] with q_stride elements between tokens; pages: bfloat16 [num_pages, nkv, page_size, D] with
 // page_size a multiple of 64; out: bfloat16 [tokens, nq, D]; q_start: int32 [rows + 1]; kv_len: int32 [rows]; block_table:
-// int32 [rows, table_width]; max_q: the longest row (or an upper bound).  skip_small != 0: rows with at most 16 packed query
-// rows (tokens x group) are left alone (another kernel writes them).  error: one int in device memory that the kernel sets
+// int32 [rows, table_width]; rows [first_row, first_row + num_rows) of those arrays are attended to (a caller that knows
+// which rows bring prompt portions names just those); max_q: the longest row (or an upper bound).  skip_small != 0: rows
+// with at most 16 packed query rows (tokens x group) are left alone (another kernel writes them).  error: one int in device memory that the kernel sets
 // non-zero when one of its bounded waits ran out (the output is then void).
 extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, const void* k_pages, const void* v_pages, void* out,
                                              const int* q_start, const int* kv_len, const int* block_table, int table_width,
-                                             int page_size, int num_pages, int nq, int nkv, int window, float scale, int num_rows,
-                                             int max_q, int skip_small, int* error, cudaStream_t stream) {
+                                             int page_size, int num_pages, int nq, int nkv, int window, float scale, int first_row,
+                                             int num_rows, int max_q, int skip_small, int* error, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_tcgen05: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 64 || page_size % 64) PYLON_REFUSE("paged_attention_tcgen05: pages of %d keys; a multiple of 64 is needed", page_size);
@@ -501,7 +502,7 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 16) || (q_stride % 8))
     PYLON_REFUSE("paged_attention_tcgen05: q, pages and out must be 16-byte aligned and the token stride a multiple of 8");
   if (!(scale > 0.f)) PYLON_REFUSE("paged_attention_tcgen05: the softmax scale must be positive");
-  if (nkv > 65535 || num_rows > 65535) PYLON_REFUSE("paged_attention_tcgen05: %d KV heads, %d rows", nkv, num_rows);
+  if (nkv > 65535 || num_rows > 65535 || first_row < 0) PYLON_REFUSE("paged_attention_tcgen05: %d KV heads, %d rows from row %d", nkv, num_rows, first_row);
   if (!error) PYLON_REFUSE("paged_attention_tcgen05: an error word is needed");
   const long long pool_rows = (long long)num_pages * nkv * page_size;
   if (pool_rows >= 2147483647LL - FA_BN) PYLON_REFUSE("paged_attention_tcgen05: the page pool has too many rows for a tensor map coordinate");
@@ -518,7 +519,7 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out;
   p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
-  p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.skip_small = skip_small;
+  p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.skip_small = skip_small; p.first_row = first_row;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.error = error;
   const long long q_tiles = ((long long)max_q * p.group + FA_BM - 1) / FA_BM;

@@ -186,4 +186,5 @@ class StepFunction:
         max_q, max_kv = self.fill(entries, layout, host.numpy())
         device_buffer = host.to(self.device, non_blocking=True)
         step, tables = self.view(device_buffer, layout, max_q, max_kv)
+        step.row_tokens = tuple(len(entry.tokens) for entry in entries)
         return self.model.forward(step, self.cache.layer_caches(tables))

@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -129,7 +129,7 @@ _SIGNATURES = {
     },
     "attention_tcgen05.cu": {
         "pylon_paged_attention_tcgen05": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+                                          c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "sampling.cu": {
         "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -545,6 +545,7 @@ def paged_attention(
     force_simple: bool = False,
     decode_blocks: Optional[int] = None,
     prefill_kernel: Optional[str] = None,
+    row_tokens: Optional[Sequence[int]] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
@@ -556,8 +557,11 @@ def paged_attention(
     ``[rows, width]``; ``max_q``/``max_kv``: longest row and longest context (upper bounds
     are fine).  ``num_splits`` and ``decode_blocks`` override the split of long rows' keys and
     the number of blocks that share the decoded rows' tiles, ``prefill_kernel`` (``"tcgen05"`` or
-    ``"mma"``) the kernel for rows of more than 16 packed query rows (for tests).  Returns
-    ``[T, nq * d]``.
+    ``"mma"``) the kernel for rows of more than 16 packed query rows (for tests).
+    ``row_tokens``: the rows' token counts on the host, if the caller has them: the kernel
+    for prompt portions then launches blocks only for the rows that are its own (a step that
+    mixes one portion with 63 decoded rows would otherwise start 63 rows of blocks that find
+    nothing to do).  Returns ``[T, nq * d]``.
 
     bfloat16 with a head size that is a multiple of 16 up to 256 runs on the tensor cores
     (built per head size on first use): prompt portions on ``tcgen05.mma`` with the accumulators
@@ -596,9 +600,14 @@ def paged_attention(
         if use_tcgen05:
             _need(d in (64, 128) and page_size % 64 == 0, "paged_attention: the tcgen05 kernel needs head size 64 or 128 and pages of a multiple of 64 keys")
             fast = _library("attention_tcgen05.cu", {"PYLON_HEAD_DIM": d})
+            first_row, row_count = 0, rows
+            if row_tokens is not None and len(row_tokens) == rows:
+                large = [index for index, count in enumerate(row_tokens) if count * group > 16]
+                if large and large[-1] - large[0] + 1 == len(large):   # one run of rows: the scheduler puts decoded rows first
+                    first_row, row_count = large[0], len(large)
             _check(fast, fast.pylon_paged_attention_tcgen05(
                 _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
-                block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, int(max_q), int(maybe_small),
+                block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, first_row, row_count, int(max_q), int(maybe_small),
                 _ptr(attention_error_word(q.device)), _stream()))
             if not maybe_small:
                 return out

@@ -91,6 +91,6 @@ class GroupedQueryAttention(Mixer):
         )
         context = ops.paged_attention(
             qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
-            self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale,
+            self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
         )
         return ops.linear_for_residual(context, self.w_o)

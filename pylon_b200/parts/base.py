@@ -105,7 +105,8 @@ class StepView:
     logit_rows  int32 [L]     tokens whose logits are wanted
     num_tokens, num_rows, num_logits, max_q, max_kv: host integers (upper bounds when the
     step is replayed from a CUDA graph).
-    ``host``: the same arrays as numpy, for parts that plan on the host (absent in replay).
+    row_tokens: the number of tokens each row brings, as host integers, for parts that plan
+    their launches on the host; ``None`` when the step is replayed from a CUDA graph.
     """
 
     token_ids: torch.Tensor
@@ -122,6 +123,7 @@ class StepView:
     max_kv: int
     dtype: torch.dtype
     device: torch.device
+    row_tokens: Optional[tuple] = None
 
 
 # ---------------------------------------------------------------------------------------

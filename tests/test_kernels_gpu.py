@@ -363,6 +363,7 @@ ATTENTION_CASES = [
     ([1000, 300], [333, 300], 10, 2, 128, 128, None),
     ([520, 77], [200, 77], 4, 4, 64, 64, 150),
     ([900], [900], 6, 1, 64, 192, 70),
+    ([100, 257, 64, 31, 90, 400, 300], [1, 1, 1, 2, 1, 200, 300], 8, 2, 128, 64, None),   # decoded rows first, then two prompt portions
     # more rows than a warp scans at once, lengths from 1 to 451, beside a prompt portion in the middle
     ([1 + (37 * i) % 451 for i in range(20)] + [80] + [5 + (53 * i) % 300 for i in range(19)], [1] * 20 + [30] + [1] * 19, 8, 2, 64, 16, None),
 ]
@@ -389,6 +390,7 @@ def test_paged_attention(case, mode):
         # decoded rows: all their tiles in one block's run, or in five runs that end inside rows
         decode_blocks=int(mode[len("bfloat16_mma_blocks"):]) if mode.startswith("bfloat16_mma_blocks") else None,
         prefill_kernel="tcgen05" if mode == "bfloat16_tcgen05" else ("mma" if mode.startswith("bfloat16_mma") else None),
+        row_tokens=q_lens if mode == "bfloat16_tcgen05" else None,   # the hint by which the tcgen05 kernel launches only its rows
     )
     torch.testing.assert_close(out.double(), expected, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)))
     assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0   # no wait for a TMA copy ran out
