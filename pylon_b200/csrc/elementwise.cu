@@ -425,7 +425,8 @@ __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* _
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]);
       const float2 u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+      // approximate division: no slow path (the exact one takes a subroutine for zero numerators), ample for a bfloat16 result
+      o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
     }
     out[i] = o4;
   }

@@ -108,6 +108,9 @@ __host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// silu for a bfloat16 result.  The approximate division has no slow path: the exact one takes a subroutine for a zero
+// numerator, and the rows of a last, partly filled tile are all zeros (a 1,984-row product took 167 us instead of 146).
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -248,7 +251,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
               for (int j = 0; j < 8; j += 2) {
                 const float g0 = __uint_as_float(raw[group * 16 + j]), g1 = __uint_as_float(raw[group * 16 + j + 1]);
                 const float u0 = __uint_as_float(raw[group * 16 + 8 + j]), u1 = __uint_as_float(raw[group * 16 + 8 + j + 1]);
-                packed[group * 4 + j / 2] = pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                packed[group * 4 + j / 2] = pack2(silu_fast(g0) * u0, silu_fast(g1) * u1);
               }
           } else {
 #pragma unroll
