@@ -307,9 +307,14 @@ struct HeadChunk<float, CHUNK> {
 // HPW heads of one token per warp: their loads are issued together, so a warp has HPW times the
 // bytes in flight per trip to memory (with one head per warp a 2048-token step ran at a third of
 // the memory bandwidth); the token's position, page and angles are looked up once.
+//
+// The projections come either as qkv [T, heads * d] in the activation type (q is then written back in place) or as
+// `parts` float32 partial sums [parts, T, heads * d], `part_stride` elements apart, which are added up here (q then goes
+// to q_out [T, nq * d]).
 template <typename T, int CHUNK, int HPW>
 __global__ void qk_norm_rope_kv_write_vec_kernel(
-    T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+    T* __restrict__ qkv, const float* __restrict__ qkv_parts, int parts, long long part_stride, T* __restrict__ q_out,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     const int* __restrict__ positions, const int* __restrict__ token_row, const int* __restrict__ block_table,
     int table_width, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
@@ -342,11 +347,23 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   }
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
-  T* token_src = qkv + (size_t)t * heads * d + lane * CHUNK;
+  const size_t token_offset = (size_t)t * heads * d + lane * CHUNK;
   float x[HPW][CHUNK];
 #pragma unroll
-  for (int h = 0; h < HPW; ++h)
-    if (head_begin + h < heads) HeadChunk<T, CHUNK>::load(token_src + (size_t)(head_begin + h) * d, x[h]);
+  for (int h = 0; h < HPW; ++h) {
+    if (head_begin + h >= heads) continue;
+    if (qkv_parts) {
+      HeadChunk<float, CHUNK>::load(qkv_parts + token_offset + (size_t)(head_begin + h) * d, x[h]);
+      for (int part = 1; part < parts; ++part) {   // in order: the sum does not depend on who wrote which part first
+        float more[CHUNK];
+        HeadChunk<float, CHUNK>::load(qkv_parts + (size_t)part * part_stride + token_offset + (size_t)(head_begin + h) * d, more);
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) x[h][i] += more[i];
+      }
+    } else {
+      HeadChunk<T, CHUNK>::load(qkv + token_offset + (size_t)(head_begin + h) * d, x[h]);
+    }
+  }
   const bool upper = lane >= 16;
 #pragma unroll
   for (int h = 0; h < HPW; ++h) {
@@ -379,7 +396,8 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
         x[h][i] = upper ? x[h][i] * c[i] + partner * s[i] : x[h][i] * c[i] - partner * s[i];
       }
     }
-    HeadChunk<T, CHUNK>::store(head < nq ? token_src + (size_t)head * d : page_dst, x[h]);
+    T* q_dst = qkv_parts ? q_out + ((size_t)t * nq + head) * d + lane * CHUNK : qkv + token_offset + (size_t)head * d;
+    HeadChunk<T, CHUNK>::store(head < nq ? q_dst : page_dst, x[h]);
   }
 }
 
@@ -497,7 +515,7 @@ extern "C" int pylon_residual_add(float* residual, const void* delta, long long 
 }
 
 template <typename T>
-static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float eps, const float* cos_t,
+static int launch_qk_norm_rope(T* qkv, const float* qkv_parts, int parts, long long part_stride, T* q_out, const float* qw, const float* kw, float eps, const float* cos_t,
                                const float* sin_t, int rotary_dim, int table_positions, const int* positions,
                                const int* token_row, const int* block_table, int table_width, int page_size,
                                T* k_pages, T* v_pages, int num_pages, int nq, int nkv, int d, int num_tokens,
@@ -508,7 +526,10 @@ static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float e
   const size_t smem = (size_t)warps * d * sizeof(float);
   // Head sizes 64, 128, 256 rotated over the whole head (or not at all), aligned: the vector form.
   const bool whole = (rotary_dim == d && cos_t) || (rotary_dim == 0 || !cos_t);
-  const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0);
+  const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0) &&
+                       ((uintptr_t)qkv_parts % 16 == 0) && ((uintptr_t)q_out % 16 == 0) && (part_stride % 4 == 0);
+  if (qkv_parts && !(whole && aligned && (d == 64 || d == 128 || d == 256)))
+    PYLON_REFUSE("qk_norm_rope_kv_write: partial sums need head size 64, 128 or 256, rotation over the whole head and 16-byte aligned buffers");
   if (whole && aligned && (d == 64 || d == 128 || d == 256)) {
     const float* cos_used = rotary_dim == d ? cos_t : nullptr;
     // Many tokens: four heads per warp (more bytes in flight); few: one, for as many warps as possible.
@@ -518,11 +539,11 @@ static int launch_qk_norm_rope(T* qkv, const float* qw, const float* kw, float e
 #define PYLON_LAUNCH_QK_VEC(C)                                                                                            \
     do {                                                                                                                  \
       if (many)                                                                                                           \
-        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 4>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps,  \
+        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 4>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qkv_parts, parts, part_stride, q_out, qw, kw, eps,  \
                          cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
                          v_pages, num_pages, nq, nkv, num_tokens);                                                         \
       else                                                                                                                \
-        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 1>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps,  \
+        launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 1>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qkv_parts, parts, part_stride, q_out, qw, kw, eps,  \
                          cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
                          v_pages, num_pages, nq, nkv, num_tokens);                                                         \
     } while (0)
@@ -558,15 +579,35 @@ extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, con
   if (nq < 0 || nkv < 1 || page_size < 1 || table_width < 1)
     PYLON_REFUSE("qk_norm_rope_kv_write: heads %d/%d, page size %d, table width %d", nq, nkv, page_size, table_width);
   if (dtype == PYLON_DTYPE_F32)
-    return launch_qk_norm_rope<float>((float*)qkv, q_weight, k_weight, eps, cos_table, sin_table, rotary_dim,
+    return launch_qk_norm_rope<float>((float*)qkv, nullptr, 0, 0, nullptr, q_weight, k_weight, eps, cos_table, sin_table, rotary_dim,
                                       table_positions, positions, token_row, block_table, table_width, page_size,
                                       (float*)k_pages, (float*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
   if (dtype == PYLON_DTYPE_BF16)
-    return launch_qk_norm_rope<__nv_bfloat16>((__nv_bfloat16*)qkv, q_weight, k_weight, eps, cos_table, sin_table,
+    return launch_qk_norm_rope<__nv_bfloat16>((__nv_bfloat16*)qkv, nullptr, 0, 0, nullptr, q_weight, k_weight, eps, cos_table, sin_table,
                                               rotary_dim, table_positions, positions, token_row, block_table,
                                               table_width, page_size, (__nv_bfloat16*)k_pages,
                                               (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
   PYLON_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
+}
+
+// The same for bfloat16 with the projections given as `parts` float32 partial sums [parts, num_tokens, (nq + 2 nkv) * d]
+// (contiguous): they are added up, q goes to q_out [num_tokens, nq * d], k and v into the pages.  Head size 64, 128 or
+// 256, rotary_dim 0 or d.
+extern "C" int pylon_qk_norm_rope_kv_write_parts(const float* qkv_parts, int parts, void* q_out, const float* q_weight, const float* k_weight,
+                                                 float eps, const float* cos_table, const float* sin_table, int rotary_dim,
+                                                 int table_positions, const int* positions, const int* token_row,
+                                                 const int* block_table, int table_width, int page_size, void* k_pages,
+                                                 void* v_pages, int num_pages, int nq, int nkv, int d, int num_tokens,
+                                                 cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (!qkv_parts || parts < 1 || !q_out) PYLON_REFUSE("qk_norm_rope_kv_write_parts: %d parts", parts);
+  if (nq < 0 || nkv < 1 || page_size < 1 || table_width < 1)
+    PYLON_REFUSE("qk_norm_rope_kv_write_parts: heads %d/%d, page size %d, table width %d", nq, nkv, page_size, table_width);
+  if (rotary_dim != 0 && rotary_dim != d) PYLON_REFUSE("qk_norm_rope_kv_write_parts: rotary size %d must be 0 or the head size %d", rotary_dim, d);
+  return launch_qk_norm_rope<__nv_bfloat16>(nullptr, qkv_parts, parts, (long long)num_tokens * (nq + 2 * nkv) * d, (__nv_bfloat16*)q_out, q_weight,
+                                            k_weight, eps, cos_table, sin_table, rotary_dim, table_positions, positions, token_row, block_table,
+                                            table_width, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d,
+                                            num_tokens, stream);
 }
 
 extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int interleaved, int dtype,

@@ -97,6 +97,9 @@ _SIGNATURES = {
         "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_qk_norm_rope_kv_write_parts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                              c_int, c_void_p],
         "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
@@ -246,13 +249,19 @@ def qk_norm_rope_kv_write(
     nq: int,
     nkv: int,
     head_dim: int,
-) -> None:
+) -> torch.Tensor:
     """On ``qkv [T, (nq + 2 nkv) * d]``: RMSNorm each q and k head (when weights are given),
     rotate them by the float32 ``cos``/``sin [positions, rotary_dim / 2]`` tables, write q
-    back in place and k, v into ``[pages, nkv, page_size, d]`` pages at each token's slot."""
+    back in place and k, v into ``[pages, nkv, page_size, d]`` pages at each token's slot.
+    Returns the tensor whose first ``nq * d`` columns now hold q: ``qkv`` itself.
+
+    ``qkv`` may also be float32 partial sums ``[parts, T, (nq + 2 nkv) * d]`` (see
+    :func:`linear_for_rotation`): they are added up on the way, and q is returned in a tensor
+    of its own, ``[T, nq * d]`` in the pages' dtype."""
     _need_cuda(qkv, q_weight, k_weight, cos, sin, positions, token_row, block_table, k_pages, v_pages)
-    tokens = qkv.shape[0]
-    _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + 2 * nkv) * head_dim, "qk_norm_rope_kv_write: qkv must be contiguous [T, (nq + 2 nkv) * d]")
+    partial = qkv.dim() == 3
+    tokens = qkv.shape[-2]
+    _need(qkv.dim() in (2, 3) and qkv.is_contiguous() and qkv.shape[-1] == (nq + 2 * nkv) * head_dim, "qk_norm_rope_kv_write: qkv must be contiguous [T, (nq + 2 nkv) * d]")
     for weight in (q_weight, k_weight):
         if weight is not None:
             _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "qk_norm_rope_kv_write: norm weights must be float32 [d]")
@@ -267,14 +276,25 @@ def qk_norm_rope_kv_write(
     for meta in (positions, token_row):
         _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "qk_norm_rope_kv_write: positions/token_row must be int32 [T]")
     _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "qk_norm_rope_kv_write: block_table must be contiguous int32 [rows, width]")
+    activation = k_pages.dtype if partial else qkv.dtype
     for pages in (k_pages, v_pages):
-        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, head_dim),
+        _need(pages.dtype == activation and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, head_dim),
               "qk_norm_rope_kv_write: pages must be contiguous [pages, nkv, page_size, d] in the activation dtype")
     library = _library("elementwise.cu")
+    if partial:
+        _need(qkv.dtype == torch.float32 and activation == torch.bfloat16 and head_dim in (64, 128, 256) and rotary_dim in (0, head_dim),
+              "qk_norm_rope_kv_write: partial sums are float32, for bfloat16 pages, head size 64, 128 or 256 and rotation over the whole head")
+        q = torch.empty((tokens, nq * head_dim), dtype=torch.bfloat16, device=qkv.device)
+        _check(library, library.pylon_qk_norm_rope_kv_write_parts(
+            _ptr(qkv), qkv.shape[0], _ptr(q), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
+            _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
+            k_pages.shape[0], nq, nkv, head_dim, tokens, _stream()))
+        return q
     _check(library, library.pylon_qk_norm_rope_kv_write(
         _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
         _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
         k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _stream()))
+    return qkv
 
 
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
@@ -361,6 +381,20 @@ def linear_for_residual(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and m <= STREAM_MAX_ROWS and k >= 1024 and k % 8 == 0
             and n % 4 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        return linear_stream_partial(x, w)
+    return linear(x, w)
+
+
+def linear_for_rotation(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """The fused QKV product for :func:`qk_norm_rope_kv_write`: the product ``[M, N]`` in the
+    activation dtype, or - for the few rows of a decode step, where the TMA-fed kernel with
+    its slices of k is the fastest way to read the weights - float32 partial sums
+    ``[parts, M, N]``, which the rotation kernel adds up as it reads them."""
+    m, k = x.shape
+    n = w.shape[0]
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and m <= STREAM_MAX_ROWS and k >= 1024 and k % 8 == 0
+            and head_dim in (64, 128, 256) and rotary_dim in (0, head_dim) and n % 4 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         return linear_stream_partial(x, w)
     return linear(x, w)
 

@@ -78,19 +78,19 @@ class GroupedQueryAttention(Mixer):
 
     # -- run -----------------------------------------------------------------------------
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
-        qkv = ops.linear(h, self.w_qkv)
         table = self.position.rotary_table(h.device) if self.position is not None else None
-        if self.position is not None and table is None:
-            q = qkv[:, : self.q_size]
-            k = qkv[:, self.q_size : self.q_size + self.kv_size]
-            self.position.apply(q, k, step)
         cos, sin, rotary_dim = table if table is not None else (None, None, 0)
-        ops.qk_norm_rope_kv_write(
+        if self.position is not None and table is None:
+            qkv = ops.linear(h, self.w_qkv)
+            self.position.apply(qkv[:, : self.q_size], qkv[:, self.q_size : self.q_size + self.kv_size], step)
+        else:
+            qkv = ops.linear_for_rotation(h, self.w_qkv, self.head_dim, rotary_dim)   # may be partial sums: the next kernel adds them
+        q = ops.qk_norm_rope_kv_write(
             qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, cos, sin, rotary_dim, step.positions, step.token_row,
             cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
         )
         context = ops.paged_attention(
-            qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
+            q, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
         )
         return ops.linear_for_residual(context, self.w_o)

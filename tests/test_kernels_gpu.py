@@ -526,6 +526,48 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm):
     assert torch.equal(cache.k_pages[~written], k_before[~written]) and torch.equal(cache.v_pages[~written], v_before[~written])
 
 
+@pytest.mark.parametrize("tokens_each", [(1, 1, 1), (13, 9, 70)])
+@pytest.mark.parametrize("nq, nkv, d, norm, parts", [(8, 2, 128, True, 4), (6, 3, 64, True, 3), (4, 1, 256, False, 1)])
+def test_qk_norm_rope_kv_write_from_partial_sums(tokens_each, nq, nkv, d, norm, parts):
+    """The fused QKV product may arrive as float32 partial sums over slices of k: the kernel adds
+    them up, q goes to a tensor of its own, k and v into the pages."""
+    from pylon_b200.kernels import ops
+
+    eps, page = 1e-6, 16
+    cache = Paged([tokens + 30 for tokens in tokens_each], list(tokens_each), nkv, d, page, torch.bfloat16, seed=4)
+    width = (nq + 2 * nkv) * d
+    pieces = torch.randn(parts, cache.tokens, width, device=DEVICE)
+    total = pieces.double().sum(0).reshape(cache.tokens, nq + 2 * nkv, d)
+    qw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    kw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    inv_freq = 1.0 / (10_000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angles = torch.arange(256, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)
+    cos, sin = torch.cos(angles).to(DEVICE), torch.sin(angles).to(DEVICE)
+    q = ops.qk_norm_rope_kv_write(pieces, qw, kw, eps, cos, sin, d, cache.positions, cache.token_row, cache.table, page,
+                                  cache.k_pages, cache.v_pages, nq, nkv, d)
+    assert q.shape == (cache.tokens, nq * d) and q.dtype == torch.bfloat16
+
+    def reference(x, weight):
+        if weight is not None:
+            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+        c, s2 = cos[cache.positions.long()].double().unsqueeze(1), sin[cache.positions.long()].double().unsqueeze(1)
+        first, second = x[..., : d // 2], x[..., d // 2 :]
+        return torch.cat((first * c - second * s2, second * c + first * s2), dim=-1)
+
+    tol = tolerance(torch.bfloat16)
+    torch.testing.assert_close(q.double().reshape(cache.tokens, nq, d), reference(total[:, :nq], qw), **tol)
+    want_k, want_v = reference(total[:, nq : nq + nkv], kw), total[:, nq + nkv :]
+    for t in range(cache.tokens):
+        r, pos = int(cache.token_row[t]), int(cache.positions[t])
+        p, slot = int(cache.table[r, pos // page]), pos % page
+        torch.testing.assert_close(cache.k_pages[p, :, slot].double(), want_k[t], **tol)
+        torch.testing.assert_close(cache.v_pages[p, :, slot].double(), want_v[t], **tol)
+    with pytest.raises(ops.KernelError, match="partial sums"):
+        ops.qk_norm_rope_kv_write(torch.zeros(2, cache.tokens, (nq + 2 * nkv) * 48, device=DEVICE), None, None, eps, None, None, 0, cache.positions,
+                                  cache.token_row, cache.table, page, torch.zeros(4, nkv, page, 48, device=DEVICE, dtype=torch.bfloat16),
+                                  torch.zeros(4, nkv, page, 48, device=DEVICE, dtype=torch.bfloat16), nq, nkv, 48)
+
+
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("vocab", [320, 151_936, 1000])
 def test_sample_argmax(vocab):
