@@ -30,12 +30,20 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels run in float32 or bfloat16, not {dtype}")
 
 
-def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+# The raw handle of torch's current stream, without building a Stream object (that costs some
+# 15 us of host time, and an eager step asks some 300 times).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _ptr(tensor: Optional[torch.Tensor]) -> c_void_p:
-    return c_void_p(0 if tensor is None else tensor.data_ptr())
+def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    """The address for a ``c_void_p`` parameter (ctypes takes an int, or None for null)."""
+    return None if tensor is None else tensor.data_ptr()
 
 
 def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
@@ -140,7 +148,14 @@ _SIGNATURES = {
 }
 
 
+_typed_libraries: dict[tuple, ctypes.CDLL] = {}
+
+
 def _library(source: str, defines: Optional[dict[str, int]] = None) -> ctypes.CDLL:
+    key = (source, tuple(sorted(defines.items())) if defines else ())
+    library = _typed_libraries.get(key)
+    if library is not None:
+        return library
     library = build.load(source, defines)
     if not getattr(library, "_pylon_typed", False):
         for name, argtypes in _SIGNATURES.get(source, {}).items():
@@ -148,6 +163,7 @@ def _library(source: str, defines: Optional[dict[str, int]] = None) -> ctypes.CD
             function.argtypes = argtypes
             function.restype = c_longlong if name.endswith("_floats") else c_int
         library._pylon_typed = True
+    _typed_libraries[key] = library
     return library
 
 

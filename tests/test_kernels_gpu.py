@@ -482,13 +482,14 @@ def test_attention_refuses_what_it_cannot_do():
 @pytest.mark.parametrize("nq, nkv, d, rotary, page, norm", [
     (4, 2, 16, 16, 16, True), (6, 3, 32, 32, 8, True), (32, 8, 128, 128, 256, True), (5, 5, 64, 32, 4, True),
     (2, 1, 80, 80, 24, False), (3, 1, 256, 64, 16, True),
-    (4, 2, 64, 64, 16, True), (2, 2, 256, 256, 8, True), (8, 4, 128, 128, 64, False),     # the vector form
+    (4, 2, 64, 64, 16, True), (2, 2, 256, 256, 8, True), (8, 4, 128, 128, 64, False), (7, 1, 128, 128, 16, True),    # the vector forms
 ])
-def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm):
+@pytest.mark.parametrize("kv_lens, q_lens", [([40, 9, 70], [13, 9, 1]), ([100, 9, 70], [77, 9, 1])])   # few tokens, many
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm, kv_lens, q_lens):
     from pylon_b200.kernels import ops
 
     eps = 1e-5
-    cache = Paged([40, 9, 70], [13, 9, 1], nkv, d, page, dtype, seed=2)
+    cache = Paged(kv_lens, q_lens, nkv, d, page, dtype, seed=2)
     k_before, v_before = cache.k_pages.clone(), cache.v_pages.clone()
     qkv = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(dtype)
     original = qkv.clone()
