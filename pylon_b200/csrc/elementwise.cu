@@ -258,6 +258,39 @@ __global__ void qk_norm_rope_kv_write_kernel(
   }
 }
 
+// q/k RMSNorm alone, in place on qkv [T, (nq + 2 nkv) * d]: for position encodings that are not a rotation by a table and
+// therefore run between the norms and the cache write.  One warp per (token, q or k head).
+template <typename T, int MAX_PER_LANE>
+__global__ void qk_norm_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                               int nq, int nkv, int d, int num_tokens) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int normed = nq + nkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)num_tokens * normed) return;
+  const int t = (int)(item / normed), head = (int)(item % normed);
+  const float* weight = head < nq ? q_weight : k_weight;
+  if (!weight) return;
+  T* src = qkv + ((size_t)t * (nq + 2 * nkv) + head) * d;
+  float x[MAX_PER_LANE];
+  float sumsq = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAX_PER_LANE; ++k) {
+    const int e = lane + 32 * k;
+    x[k] = e < d ? to_float<T>(src[e]) : 0.f;
+    sumsq += x[k] * x[k];
+  }
+  sumsq = warp_sum(sumsq);
+  const float inv = rsqrtf(sumsq / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < MAX_PER_LANE; ++k) {
+    const int e = lane + 32 * k;
+    if (e < d) src[e] = from_float<T>(x[k] * inv * weight[e]);
+  }
+}
+
 // Vector form for head sizes 64, 128 and 256 with the rotation over the whole head: lane l holds
 // the CHUNK = d / 32 consecutive elements l * CHUNK .., loaded and stored as one vector; its
 // rotation partners (d / 2 further) sit in lane l ^ 16 and come by shuffle.
@@ -719,6 +752,32 @@ extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, con
                                               table_width, page_size, (__nv_bfloat16*)k_pages,
                                               (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
   PYLON_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
+}
+
+template <typename T>
+static int launch_qk_norm(T* qkv, const float* qw, const float* kw, float eps, int nq, int nkv, int d, int num_tokens, cudaStream_t stream) {
+  const int warps = 4;
+  const long long items = (long long)num_tokens * (nq + nkv);
+  const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+#define PYLON_LAUNCH_QK_NORM(N) launch_dependent(qk_norm_kernel<T, N>, dim3(blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps, nq, nkv, d, num_tokens)
+  if (d <= 32) PYLON_LAUNCH_QK_NORM(1);
+  else if (d <= 64) PYLON_LAUNCH_QK_NORM(2);
+  else if (d <= 128) PYLON_LAUNCH_QK_NORM(4);
+  else if (d <= 256) PYLON_LAUNCH_QK_NORM(8);
+  else PYLON_LAUNCH_QK_NORM(16);
+#undef PYLON_LAUNCH_QK_NORM
+  PYLON_CHECK_LAUNCH("qk_norm");
+}
+
+// RMSNorm of every q and k head of qkv [num_tokens, (nq + 2 nkv) * d], in place (a null weight leaves its heads alone).
+extern "C" int pylon_qk_norm(void* qkv, const float* q_weight, const float* k_weight, float eps, int nq, int nkv, int d, int num_tokens,
+                             int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0 || (!q_weight && !k_weight)) return 0;
+  if (d < 1 || d > 512) PYLON_REFUSE("qk_norm: head size %d is outside 1..512", d);
+  if (nq < 0 || nkv < 1) PYLON_REFUSE("qk_norm: heads %d/%d", nq, nkv);
+  if (dtype == PYLON_DTYPE_F32) return launch_qk_norm<float>((float*)qkv, q_weight, k_weight, eps, nq, nkv, d, num_tokens, stream);
+  if (dtype == PYLON_DTYPE_BF16) return launch_qk_norm<__nv_bfloat16>((__nv_bfloat16*)qkv, q_weight, k_weight, eps, nq, nkv, d, num_tokens, stream);
+  PYLON_REFUSE("qk_norm: unknown dtype %d", dtype);
 }
 
 // The same for bfloat16 with the projections given as `parts` float32 partial sums [parts, num_tokens, (nq + 2 nkv) * d]

@@ -108,6 +108,7 @@ _SIGNATURES = {
         "pylon_qk_norm_rope_kv_write_parts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p],
+        "pylon_qk_norm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
@@ -310,6 +311,21 @@ def qk_norm_rope_kv_write(
         _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
         _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
         k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _stream()))
+    return qkv
+
+
+def qk_norm(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float, nq: int, nkv: int, head_dim: int) -> torch.Tensor:
+    """RMSNorm of every q and k head of ``qkv [T, (nq + 2 nkv) * d]`` in place, without rotation or
+    cache write: for position encodings that run as a step of their own between the norms and
+    :func:`qk_norm_rope_kv_write` (called without weights and tables, it then only writes the cache)."""
+    _need_cuda(qkv, q_weight, k_weight)
+    _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + 2 * nkv) * head_dim, "qk_norm: qkv must be contiguous [T, (nq + 2 nkv) * d]")
+    for weight in (q_weight, k_weight):
+        if weight is not None:
+            _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "qk_norm: norm weights must be float32 [d]")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_qk_norm(_ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), nq, nkv, head_dim, qkv.shape[0],
+                                          _dtype_code(qkv.dtype), _stream()))
     return qkv
 
 

@@ -80,13 +80,19 @@ class GroupedQueryAttention(Mixer):
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
         table = self.position.rotary_table(h.device) if self.position is not None else None
         cos, sin, rotary_dim = table if table is not None else (None, None, 0)
+        q_norm, k_norm = self.q_norm, self.k_norm
         if self.position is not None and table is None:
+            # An encoding that is not a rotation by a table runs as a step of its own, on normalised q and k and
+            # before k goes into the cache; the fused kernel below is left with the cache write.
             qkv = ops.linear(h, self.w_qkv)
+            if q_norm is not None:
+                ops.qk_norm(qkv, q_norm, k_norm, self.qk_norm_eps, self.n_heads, self.n_kv_heads, self.head_dim)
+                q_norm = k_norm = None
             self.position.apply(qkv[:, : self.q_size], qkv[:, self.q_size : self.q_size + self.kv_size], step)
         else:
             qkv = ops.linear_for_rotation(h, self.w_qkv, self.head_dim, rotary_dim)   # may be partial sums: the next kernel adds them
         q = ops.qk_norm_rope_kv_write(
-            qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, cos, sin, rotary_dim, step.positions, step.token_row,
+            qkv, q_norm, k_norm, self.qk_norm_eps or 0.0, cos, sin, rotary_dim, step.positions, step.token_row,
             cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
         )
         context = ops.paged_attention(

@@ -156,6 +156,9 @@ class PositionEncoding(Part):
         return None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, step: StepView) -> None:
+        """For encodings without such a table: change ``q [T, heads * d]`` and ``k [T, kv_heads * d]``
+        (views with a row stride; already normalised if the mixer has q/k norms) in place, before
+        ``k`` is written into the cache."""
         raise NotImplementedError
 
 

@@ -527,6 +527,26 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, rotary, page, norm, kv_lens, q
     assert torch.equal(cache.k_pages[~written], k_before[~written]) and torch.equal(cache.v_pages[~written], v_before[~written])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq, nkv, d, tokens", [(4, 2, 16, 5), (5, 1, 80, 33), (32, 8, 128, 70), (3, 3, 272, 9)])
+def test_qk_norm_alone(dtype, nq, nkv, d, tokens):
+    """RMSNorm of the q and k heads in place; v and, with a missing weight, that kind of head stay as they are."""
+    from pylon_b200.kernels import ops
+
+    eps = 1e-5
+    torch.manual_seed(tokens)
+    original = torch.randn(tokens, (nq + 2 * nkv) * d, device=DEVICE).to(dtype)
+    qw, kw = torch.rand(d, device=DEVICE) + 0.5, torch.rand(d, device=DEVICE) + 0.5
+    heads = original.double().reshape(tokens, -1, d)
+    norm = lambda x, weight: x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+    for q_weight, k_weight in ((qw, kw), (None, kw)):
+        qkv = ops.qk_norm(original.clone(), q_weight, k_weight, eps, nq, nkv, d).double().reshape(tokens, -1, d)
+        want_q = norm(heads[:, :nq], q_weight) if q_weight is not None else heads[:, :nq]
+        torch.testing.assert_close(qkv[:, :nq], want_q, **(tolerance(dtype) if q_weight is not None else dict(rtol=0, atol=0)))
+        torch.testing.assert_close(qkv[:, nq : nq + nkv], norm(heads[:, nq : nq + nkv], k_weight), **tolerance(dtype))
+        torch.testing.assert_close(qkv[:, nq + nkv :], heads[:, nq + nkv :], rtol=0, atol=0)
+
+
 @pytest.mark.parametrize("tokens_each", [(1, 1, 1), (13, 9, 70)])
 @pytest.mark.parametrize("nq, nkv, d, norm, parts", [(8, 2, 128, True, 4), (6, 3, 64, True, 3), (4, 1, 256, False, 1)])
 def test_qk_norm_rope_kv_write_from_partial_sums(tokens_each, nq, nkv, d, norm, parts):

@@ -301,3 +301,218 @@ def test_toy_model_with_state_window_and_a_layer_run_twice(toy_folder, cutting, 
     if cutting != "whole":
         # the windowed group never needed as many pages at once as the full one
         assert windowed.pool.acquired_total >= full.pool.acquired_total > 0
+
+
+# ---------------------------------------------------------------------------------------
+# a second made-up architecture: a feed-forward with routing and another position encoding
+# ---------------------------------------------------------------------------------------
+def register_routed_toy_parts():
+    """Defined here, not in the framework: a feed-forward that routes each token to one of a few
+    small experts, and a rotary encoding over neighbouring pairs (2j, 2j + 1), which is no
+    rotation by the framework's table layout and therefore runs through ``apply``."""
+    from pylon_b200.kernels import ops
+    from pylon_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding, TensorDecl
+
+    if "toy_routed" in FEED_FORWARDS.kinds():
+        return
+
+    @FEED_FORWARDS.register("toy_routed")
+    class Routed(FeedForward):
+        """delta = p_e * down_e(gelu(up_e(h))) for the expert e with the largest router logit; p = softmax of
+        the logits, which are formed in float32."""
+
+        def __init__(self, width: int, intermediate: int, experts: int) -> None:
+            self.width, self.intermediate, self.experts = width, intermediate, experts
+            self.router = None
+            self.up, self.down = [], []
+
+        def tensors(self):
+            decls = [TensorDecl("router.weight", (self.experts, self.width), "vector")]
+            for e in range(self.experts):
+                decls += [TensorDecl(f"experts.{e}.up.weight", (self.intermediate, self.width)),
+                          TensorDecl(f"experts.{e}.down.weight", (self.width, self.intermediate))]
+            return decls
+
+        def load(self, tensors, dtype, device):
+            self.router = tensors["router.weight"].contiguous()
+            self.up = [tensors[f"experts.{e}.up.weight"].contiguous() for e in range(self.experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"].contiguous() for e in range(self.experts)]
+
+        def forward(self, h, step):
+            logits = h.float() @ self.router.t()
+            probabilities = torch.softmax(logits, dim=-1)
+            chosen = torch.argmax(logits, dim=-1)
+            out = torch.zeros_like(h)
+            for e in range(self.experts):
+                rows = torch.nonzero(chosen == e).squeeze(1)
+                if rows.numel() == 0:
+                    continue
+                hidden = torch.nn.functional.gelu(ops.linear(h[rows].contiguous(), self.up[e]).float()).to(h.dtype)
+                out[rows] = (ops.linear(hidden, self.down[e]).float() * probabilities[rows, e].unsqueeze(1)).to(h.dtype)
+            return out
+
+    @POSITION_ENCODINGS.register("toy_neighbour_pairs")
+    class NeighbourPairs(PositionEncoding):
+        def __init__(self, head_dim: int, theta: float) -> None:
+            self.head_dim, self.theta = head_dim, theta
+
+        def apply(self, q, k, step):
+            tokens = q.shape[0]
+            inv_freq = 1.0 / (self.theta ** (torch.arange(0, self.head_dim, 2, dtype=torch.float32, device=q.device) / self.head_dim))
+            angles = step.positions[:tokens].float().unsqueeze(1) * inv_freq.unsqueeze(0)
+            cos, sin = torch.cos(angles).unsqueeze(1), torch.sin(angles).unsqueeze(1)     # [T, 1, d/2]
+            for x in (q, k):
+                pairs = x.unflatten(1, (-1, self.head_dim // 2, 2)).float()                  # [T, heads, d/2, 2]
+                even, odd = pairs[..., 0], pairs[..., 1]
+                x.copy_(torch.stack((even * cos - odd * sin, odd * cos + even * sin), dim=-1).flatten(1).to(x.dtype))
+
+
+@dataclass(frozen=True)
+class RoutedToyConfig:
+    """Layer 0: attention with q/k norms and the neighbour-pair rotation, then the routed feed-forward;
+    layer 1: the same attention and a SwiGLU feed-forward."""
+
+    architecture = "RoutedToyForCausalLM"
+    vocab_size: int = 150
+    width: int = 80
+    heads: int = 6
+    kv_heads: int = 3
+    head_dim: int = 16
+    intermediate: int = 72
+    experts: int = 3
+    eps: float = 1e-5
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: data[k] for k in ("vocab_size", "width", "heads", "kv_heads", "head_dim", "intermediate", "experts", "eps")})
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], **self.__dict__}
+
+
+def routed_toy_spec(config: RoutedToyConfig, max_positions: Optional[int] = None):
+    from pylon_b200.parts import LayerSpec, ModelSpec, PartSpec
+    from pylon_b200.parts.spec import RunSpec
+
+    norm = PartSpec("rmsnorm", {"width": config.width, "eps": config.eps})
+    attention = PartSpec("gqa_attention", {
+        "width": config.width, "n_heads": config.heads, "n_kv_heads": config.kv_heads, "head_dim": config.head_dim,
+        "qk_norm_eps": config.eps, "position": PartSpec("toy_neighbour_pairs", {"head_dim": config.head_dim, "theta": 100.0}),
+    })
+    routed = PartSpec("toy_routed", {"width": config.width, "intermediate": config.intermediate, "experts": config.experts})
+    dense = PartSpec("swiglu", {"width": config.width, "intermediate": config.intermediate})
+    block = lambda ffn: PartSpec("prenorm", {"mixer": attention, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm})
+    return ModelSpec(
+        width=config.width, vocab_size=config.vocab_size, max_positions=max_positions or 512, embedding_name="embed.weight",
+        lm_head_name="head.weight", final_norm=norm, final_norm_prefix="norm.",
+        layers=(LayerSpec("layers.0.", block(routed)), LayerSpec("layers.1.", block(dense))), order=(RunSpec(0), RunSpec(1)),
+    )
+
+
+def routed_toy_plain_forward(config: RoutedToyConfig, w: Mapping[str, torch.Tensor], tokens: Sequence[int]):
+    """Whole sequence, no cache; returns the logits and the smallest gap between the two largest router logits."""
+    ids = torch.as_tensor(list(tokens))
+    x = w["embed.weight"][ids]
+    count, d = len(ids), config.head_dim
+    inv_freq = 1.0 / (100.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angles = (torch.arange(count, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)).to(x.dtype)
+    cos, sin = torch.cos(angles), torch.sin(angles)                                        # [T, d/2]
+
+    def rotate(heads):                                                                     # [n, T, d]
+        even, odd = heads[..., 0::2], heads[..., 1::2]
+        return torch.stack((even * cos - odd * sin, odd * cos + even * sin), dim=-1).flatten(-2)
+
+    def attention(h, prefix):
+        project = lambda name, n: (h @ w[prefix + f"self_attn.{name}_proj.weight"].T).reshape(count, n, d).transpose(0, 1)
+        q = rotate(plain.rms_norm(project("q", config.heads), w[prefix + "self_attn.q_norm.weight"], config.eps))
+        k = rotate(plain.rms_norm(project("k", config.kv_heads), w[prefix + "self_attn.k_norm.weight"], config.eps))
+        context = plain.causal_attention(q, k, project("v", config.kv_heads))
+        return context.transpose(0, 1).reshape(count, -1) @ w[prefix + "self_attn.o_proj.weight"].T
+
+    smallest_gap = float("inf")
+
+    def routed(h, prefix):
+        nonlocal smallest_gap
+        logits = h @ w[prefix + "mlp.router.weight"].T
+        top2 = torch.topk(logits, 2, dim=-1).values
+        smallest_gap = min(smallest_gap, float((top2[:, 0] - top2[:, 1]).min()))
+        probabilities, chosen = torch.softmax(logits, dim=-1), torch.argmax(logits, dim=-1)
+        out = torch.zeros_like(h)
+        for t in range(count):
+            e = int(chosen[t])
+            hidden = torch.nn.functional.gelu(h[t] @ w[prefix + f"mlp.experts.{e}.up.weight"].T)
+            out[t] = probabilities[t, e] * (hidden @ w[prefix + f"mlp.experts.{e}.down.weight"].T)
+        return out
+
+    for layer in (0, 1):
+        prefix = f"layers.{layer}."
+        x = x + attention(plain.rms_norm(x, w[prefix + "input_layernorm.weight"], config.eps), prefix)
+        h = plain.rms_norm(x, w[prefix + "post_attention_layernorm.weight"], config.eps)
+        x = x + (routed(h, prefix) if layer == 0 else plain.swiglu_part(h, w, prefix))
+    return plain.rms_norm(x, w["norm.weight"], config.eps) @ w["head.weight"].T, smallest_gap
+
+
+@pytest.fixture(scope="module")
+def routed_toy_folder(tmp_path_factory):
+    """Random weights, except that the routing is made decisive: the embedding of token t carries a strong
+    component in coordinate t mod experts, and expert e's router row reads that coordinate.  A token whose two
+    largest router logits nearly tie would be routed differently by a rounding error, and one such token spoils
+    every later position of its sequence."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from pylon_b200.config import register_architecture
+    from pylon_b200.config.registry import ARCHITECTURES
+    from pylon_b200.weights import write_random_model
+
+    register_routed_toy_parts()
+    register_architecture(RoutedToyConfig.architecture, RoutedToyConfig, routed_toy_spec)
+    config = RoutedToyConfig()
+    folder = tmp_path_factory.mktemp("routed_toy")
+    write_random_model(config, 23, folder)
+    path = str(folder / "model.safetensors")
+    with safe_open(path, framework="pt") as handle:
+        tensors = {name: handle.get_tensor(name) for name in handle.keys()}
+    embedding = tensors["embed.weight"].float()
+    embedding[:, : config.experts] = 0.0
+    embedding[torch.arange(config.vocab_size), torch.arange(config.vocab_size) % config.experts] = 0.25
+    tensors["embed.weight"] = embedding.to(torch.bfloat16)
+    router = torch.zeros(config.experts, config.width)
+    router[torch.arange(config.experts), torch.arange(config.experts)] = 0.4
+    tensors["layers.0.mlp.router.weight"] = router.to(torch.bfloat16)
+    save_file(tensors, path, metadata={"format": "pt"})
+    yield folder
+    ARCHITECTURES.pop(RoutedToyConfig.architecture, None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
+def test_toy_model_with_routed_feed_forward_and_another_position_encoding(routed_toy_folder, cutting, dtype):
+    """Different feed-forwards in different layers, one of them routing tokens to experts, and a
+    position encoding that the attention part cannot fuse: it runs between the q/k norms and the
+    cache write.  Registered, built from a model folder and stepped through the engine."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine
+
+    config = RoutedToyConfig()
+    _, weights = plain.read_model(routed_toy_folder)
+    rng = np.random.default_rng(9)
+    requests = {f"r{i}": rng.integers(0, config.vocab_size, size=n).tolist() for i, n in enumerate((57, 12, 40, 83, 21))}
+    expected = {}
+    for rid, tokens in requests.items():
+        logits, gap = routed_toy_plain_forward(config, weights, tokens)
+        assert gap > 0.5, "the routing of the test model is meant to be decisive"
+        expected[rid] = plain.as_numpy(logits)
+    builders = {"whole": trace_tools.whole, "tail_one_by_one": trace_tools.tail_one_by_one,
+                "changing_portions": trace_tools.changing_portions, "mixed": trace_tools.mixed}
+    steps = builders[cutting](requests)
+    page = 16
+    engine = Engine(routed_toy_folder, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=trace_tools.pool_tokens(steps, page),
+                                                    max_context=128, max_batch_size=4))
+    got = trace_tools.run_in_process(engine, steps)
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
+    for rid in requests:
+        np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, **tol)
+    # every expert had work: the comparison covered all of them
+    used = {int(t) % config.experts for tokens in requests.values() for t in tokens}
+    assert used == set(range(config.experts))
