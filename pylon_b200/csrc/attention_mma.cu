@@ -422,6 +422,22 @@ __device__ __forceinline__ void att_tma_load(void* dst, const CUtensorMap* map, 
                ::"r"(smem_address(dst)), "l"((unsigned long long)map), "r"(smem_address(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// Thread-block clusters: the address of one's own shared-memory location in another block of the cluster, a load from
+// there, and the cluster's barrier (release/acquire: what a block wrote to its shared memory before is visible after).
+__device__ __forceinline__ unsigned cluster_address(const void* own, unsigned rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_address(own)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float cluster_load(unsigned address) {
+  float value;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(value) : "r"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
 // Tiles of 64 keys that a row of decoded tokens (at most SMALL_ROWS packed query rows) walks
 // per KV head, and the first of them; 0 for every other row.
 __device__ __forceinline__ int decode_row_tiles(const AttentionParams& p, int row, int* first_tile) {
@@ -464,7 +480,13 @@ __device__ __forceinline__ int run_of(int tile, int total, int used) { return (i
 //
 // map_k, map_v (TMA form only): the page pools as matrices [pages x KV heads x page size, D]
 // with boxes of 64 rows x 64 values.
-template <bool TMA>
+//
+// CLUSTER > 0 (TMA form, launches with so few (row, KV head) pairs that CLUSTER blocks for each are all resident): the
+// blocks of a thread-block cluster share one pair, each walks an equal share of its tiles, and the partial results are
+// combined through distributed shared memory: every block reads all blocks' results for its slice of the head's values.
+// No scratch, fence, counter or second trip to L2; with one request the combination of 16 partial results per head
+// was most of the kernel's time.
+template <bool TMA, int CLUSTER = 0>
 __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v) {
   using Tiles = DecodeTiles<TMA>;
@@ -488,7 +510,13 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   }
   // The rows' lengths were written long before the kernel ahead of this one started, so the plan
   // can be made while that kernel finishes; the queries and the newest keys are its work.
-  if (warp == 0) {
+  const int cluster_pair = CLUSTER ? (int)blockIdx.x / (CLUSTER ? CLUSTER : 1) : 0, cluster_rank = CLUSTER ? (int)blockIdx.x % (CLUSTER ? CLUSTER : 1) : 0;
+  int cluster_first = 0, cluster_tiles = 0;
+  if (CLUSTER) {
+    cluster_tiles = decode_row_tiles(p, cluster_pair / p.nkv, &cluster_first);
+    if (cluster_tiles == 0) return;   // not a row of decoded tokens: the whole cluster leaves
+  }
+  if (!CLUSTER && warp == 0) {
     int unused;
     const int first_chunk = lane < p.num_rows ? decode_row_tiles(p, lane, &unused) : 0;   // kept: most launches have at most 32 rows
     int total = first_chunk, with_tiles = first_chunk > 0;
@@ -528,12 +556,13 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     if (lane == 0) { plan[0] = total; plan[1] = found_row; plan[2] = found_before; plan[3] = used; }
   }
   __syncthreads();
-  const int total_tiles = plan[0];
-  if (plan[1] < 0) return;
-  const int blocks_used = plan[3];
-  const int run_end = run_begin(blockIdx.x + 1, total_tiles, blocks_used);
+  const int total_tiles = CLUSTER ? 0 : plan[0];
+  if (!CLUSTER && plan[1] < 0) return;
+  const int blocks_used = CLUSTER ? 1 : plan[3];
+  const int run_end = CLUSTER ? 0 : run_begin(blockIdx.x + 1, total_tiles, blocks_used);
   const bool contiguous = p.page_size % BLOCK_N == 0;
-  int position = run_begin(blockIdx.x, total_tiles, blocks_used), row = plan[1], before = plan[2];
+  int position = CLUSTER ? 0 : run_begin(blockIdx.x, total_tiles, blocks_used), row = CLUSTER ? 0 : plan[1], before = CLUSTER ? 0 : plan[2];
+  bool cluster_share_taken = false;
   unsigned issued = 0, consumed = 0;   // tiles of this block so far: stage = count % DEC_STAGES
 
   // The next piece of this block's run: tiles [tile_begin, tile_end) of one (row, KV head).
@@ -542,6 +571,22 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     const int* table;
   };
   auto next_segment = [&](Segment& s) -> bool {
+    if (CLUSTER) {   // one segment: this block's share of the cluster's pair
+      if (cluster_share_taken) return false;
+      cluster_share_taken = true;
+      const int cluster_row = cluster_pair / p.nkv;
+      s.kv_head = cluster_pair % p.nkv;
+      s.tile_begin = cluster_first + (int)((long long)cluster_rank * cluster_tiles / (CLUSTER ? CLUSTER : 1));
+      s.tile_end = cluster_first + (int)((long long)(cluster_rank + 1) * cluster_tiles / (CLUSTER ? CLUSTER : 1));
+      s.pair = cluster_pair; s.first_block = 0; s.segments = CLUSTER;
+      s.q0 = p.q_start[cluster_row];
+      const int q_len = p.q_start[cluster_row + 1] - s.q0;
+      s.packed_rows = q_len * G;
+      s.kv_len = p.kv_len[cluster_row];
+      s.pos0 = s.kv_len - q_len;
+      s.table = p.block_table + (size_t)cluster_row * p.table_width;
+      return s.tile_end > s.tile_begin;
+    }
     while (position < run_end && row < p.num_rows) {
       int first_tile;
       const int row_tiles = decode_row_tiles(p, row, &first_tile);
@@ -746,7 +791,8 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
         }
         if (!att_mbar_wait(&tile_full[consumed % DEC_STAGES], (consumed / DEC_STAGES) & 1)) {
           if (p.error) atomicExch(p.error, 1);
-          return;   // every thread of the block gives up on the same copy
+          if (!CLUSTER) return;   // every thread of the block gives up on the same copy
+          break;                  // in a cluster the others wait for this block at the barrier: it goes there, its result void
         }
         if (tile * BLOCK_N + BLOCK_N > kv_len) {
           // Keys past the row's length are masked, but their values (whatever the page held) still
@@ -901,7 +947,27 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     }
     __syncthreads();
     const size_t slot = (size_t)pair + blockIdx.x;
-    for (int e = threadIdx.x; e < packed_rows * D; e += ATT_THREADS) {
+    if (CLUSTER) {
+      // The block's normalised result goes to the start of the stages, where the other blocks of the cluster find it:
+      // first into registers, since the merge buffers may lie in the same place.
+      float mine[SMALL_ROWS * D / ATT_THREADS];
+#pragma unroll
+      for (int i = 0; i < SMALL_ROWS * D / ATT_THREADS; ++i) {
+        const int e = threadIdx.x + i * ATT_THREADS, r = e / D, col = e % D;
+        mine[i] = 0.f;
+        if (e < packed_rows * D) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) mine[i] += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < SMALL_ROWS * D / ATT_THREADS; ++i) {
+        const int e = threadIdx.x + i * ATT_THREADS;
+        if (e < packed_rows * D) reinterpret_cast<float*>(stages)[e] = mine[i];
+      }
+    }
+    for (int e = threadIdx.x; !CLUSTER && e < packed_rows * D; e += ATT_THREADS) {
       const int r = e / D, col = e % D;
       float value = 0.f;
 #pragma unroll
@@ -916,7 +982,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       }
     }
 
-    if (segments > 1) {
+    if (!CLUSTER && segments > 1) {
       if (threadIdx.x == 0) {
         int* entry = pending[pending_count];
         entry[0] = pair; entry[1] = first_block; entry[2] = segments; entry[3] = q0; entry[4] = packed_rows; entry[5] = kv_head;
@@ -928,7 +994,53 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     current = following;
     have = have_following;
   }
-  publish_and_combine();
+  if (!CLUSTER) {
+    publish_and_combine();
+    return;
+  }
+
+  // The cluster's blocks combine their results: each block a share of the (packed row, value) elements, from all blocks'
+  // shared memory.
+  constexpr int SIZE = CLUSTER ? CLUSTER : 1;
+  if (!cluster_share_taken || current.tile_end <= current.tile_begin) {   // no tiles for this block: nothing visible in its share
+    if (threadIdx.x < SMALL_ROWS) row_lse[threadIdx.x] = -INFINITY;
+  }
+  if (!waited) {   // only a block without tiles comes here without having waited
+    grid_dependency_wait();
+    allow_dependents();
+  }
+  __syncthreads();
+  cluster_barrier();
+  {
+    const int cluster_row = cluster_pair / p.nkv;
+    const int q0 = p.q_start[cluster_row];
+    const int packed_rows = (p.q_start[cluster_row + 1] - q0) * G;
+    const int kv_head = cluster_pair % p.nkv;
+    for (int e = cluster_rank * ATT_THREADS + threadIdx.x; e < packed_rows * D; e += SIZE * ATT_THREADS) {   // dealt out by the hundred
+      const int r = e / D, col = e % D;
+      float lse[SIZE], part[SIZE];
+#pragma unroll
+      for (int c = 0; c < SIZE; ++c) {
+        lse[c] = cluster_load(cluster_address(&row_lse[r], c));
+        part[c] = cluster_load(cluster_address(reinterpret_cast<float*>(stages) + r * D + col, c));
+      }
+      float top = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < SIZE; ++c) top = fmaxf(top, lse[c]);
+      float sum = 0.f, total = 0.f;
+#pragma unroll
+      for (int c = 0; c < SIZE; ++c) {
+        if (lse[c] == -INFINITY) continue;   // a block without visible keys: whatever lies in its buffer does not count
+        const float weight = fast_exp2(lse[c] - top);
+        sum += weight * part[c];
+        total += weight;
+      }
+      const size_t token = (size_t)q0 + r / G;
+      const int head = kv_head * G + r % G;
+      p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(total > 0.f ? sum / total : 0.f);
+    }
+  }
+  cluster_barrier();   // nobody leaves while its shared memory is being read
 }
 
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
@@ -1034,6 +1146,15 @@ static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
 constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
 constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA : DEC_SMEM_GATHER;
 
+static int decode_sm_count() {
+  static int count = [] {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) value = 0;
+    return value;
+  }();
+  return count;
+}
+
 // Blocks of the decode kernel: as many as are resident at once, of the form that needs more
 // shared memory.
 extern "C" int pylon_attention_decode_blocks() {
@@ -1069,12 +1190,16 @@ extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_to
 // scratch and counters may be null when num_splits = 1 and no row can have 16 packed rows or fewer
 // (one row and max_q * group > 16).  error: null, or one int in device memory that a kernel sets
 // non-zero when its bounded wait for a TMA copy ran out (the output is then void).  skip_large != 0: rows with
-// more than 16 packed query rows are left alone (another kernel writes them).
+// more than 16 packed query rows are left alone (another kernel writes them).  rows_alike != 0: the caller knows that
+// the rows of decoded tokens hold about equally many keys; with few of them, each (row, KV head) pair then gets a
+// thread-block cluster of its own (with rows of very different lengths that would leave most blocks idle: the result is
+// right either way).
 extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
                                          const int* block_table, int table_width, int page_size, int num_pages,
                                          int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
-                                         int max_q, int num_splits, int decode_blocks, int skip_large, int* error, cudaStream_t stream) {
+                                         int max_q, int num_splits, int decode_blocks, int skip_large, int rows_alike, int* error,
+                                         cudaStream_t stream) {
   if (num_rows <= 0 || total_tokens <= 0) return 0;
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_mma: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 1 || table_width < 1 || window < 0 || max_q < 1 || num_splits < 1)
@@ -1104,6 +1229,11 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
       err = cudaFuncSetAttribute(paged_attention_mma_kernel<WIDE_TILES ? 2 : 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_2);
     if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_GATHER);
     if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA);
+#define PYLON_CLUSTER_CASE(N)                                                                                                   \
+    if (err == cudaSuccess && TMA_HEAD)                                                                                         \
+      err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA);
+    PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
+#undef PYLON_CLUSTER_CASE
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
   }
@@ -1149,7 +1279,22 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
     if (tma) {
       if (!page_pool_map(&map_k, k_pages, pool_rows) || !page_pool_map(&map_v, v_pages, pool_rows))
         PYLON_REFUSE("paged_attention_mma: the tensor maps of the page pools could not be made");
-      launch_dependent(paged_attention_decode_kernel<TMA_HEAD>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_TMA, stream, p, map_k, map_v);
+      // Few pairs of about equal length: a cluster of blocks for each, as large as leaves two blocks to an SM (with three,
+      // clusters measured slower than the runs: 3.23 against 2.97 ms a step at batch 8) and within the caller's blocks.
+      const long long pairs = (long long)num_rows * nkv;
+      int size = 0;
+      if (TMA_HEAD && rows_alike) {
+        const long long room = 2LL * decode_sm_count() / pairs;
+        size = room >= 8 ? 8 : room >= 6 ? 6 : room >= 4 ? 4 : room >= 3 ? 3 : room >= 2 ? 2 : 0;
+        if (pairs * size > decode_blocks) size = 0;
+      }
+#define PYLON_CLUSTER_CASE(N)                                                                                                   \
+      if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), DEC_SMEM_TMA, \
+                                              stream, N, p, map_k, map_v);
+      PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
+#undef PYLON_CLUSTER_CASE
+      if (size == 0)
+        launch_dependent(paged_attention_decode_kernel<TMA_HEAD>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_TMA, stream, p, map_k, map_v);
     } else {
       launch_dependent(paged_attention_decode_kernel<false>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_GATHER, stream, p, map_k, map_v);
     }

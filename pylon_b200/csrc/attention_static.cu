@@ -123,6 +123,6 @@ extern "C" int pylon_paged_attention_mma_static(const void* q, long long q_strid
   float* scratch = static_scratch_address(&counters, &error);
   if (scratch == nullptr) return -2;
   return pylon_paged_attention_mma(q, q_stride, k_pages, v_pages, out, scratch, counters, q_start, kv_len, block_table, table_width,
-                                   page_size, num_pages, nq, nkv, window, scale, num_rows, total_tokens, max_q, num_splits, decode_blocks, 0, error,
-                                   stream);
+                                   page_size, num_pages, nq, nkv, window, scale, num_rows, total_tokens, max_q, num_splits, decode_blocks, 0,
+                                   0 /* nothing is known about the rows' lengths */, error, stream);
 }

@@ -141,6 +141,27 @@ inline cudaError_t launch_dependent(void (*kernel)(KernelArgs...), dim3 grid, di
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same with the grid's blocks grouped into thread-block clusters of `cluster` along x (the grid's x a multiple of it).
+template <LaunchKind KIND = LAUNCH_OTHER, typename... KernelArgs, typename... Args>
+inline cudaError_t launch_dependent_cluster(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster,
+                                            Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled(KIND) ? 2 : 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 }  // namespace pylon
 
 // One copy per shared library (each library is built from one translation unit; weak in case

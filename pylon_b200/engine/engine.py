@@ -137,18 +137,27 @@ class Engine:
         if self.step_function.graphs is None:
             raise RuntimeError("cuda_graphs is off")
         sizes = list(batch_sizes) if batch_sizes is not None else list(range(1, self.config.max_batch_size + 1))
+        graphs = self.step_function.graphs
         with torch.cuda.device(self.device):
-            for size in sizes:
-                if size in self.step_function.graphs.captured or size > min(self.cache.free_slots(), min(self.cache.free_pages(), default=size)):
-                    continue
-                requests = [self.cache.open(("capture", size, i), 1) for i in range(size)]
-                try:
-                    self.step_function([StepEntry(request, [0], (0,)) for request in requests])
-                finally:
-                    for request in requests:
-                        self.cache.close(request)
+            try:
+                for size in sizes:
+                    if size > min(self.cache.free_slots(), min(self.cache.free_pages(), default=size)):
+                        continue
+                    # both forms of the step: for requests of about equal length, and (from two requests on) for any
+                    for alike in ((True,) if size == 1 else (True, False)):
+                        if size in (graphs.captured_alike if alike else graphs.captured):
+                            continue
+                        graphs.force_alike = alike
+                        requests = [self.cache.open(("capture", size, i), 1) for i in range(size)]
+                        try:
+                            self.step_function([StepEntry(request, [0], (0,)) for request in requests])
+                        finally:
+                            for request in requests:
+                                self.cache.close(request)
+            finally:
+                graphs.force_alike = None
             torch.cuda.synchronize(self.device)
-        return sorted(self.step_function.graphs.captured)
+        return sorted(set(graphs.captured) | set(graphs.captured_alike))
 
     # -- generation --------------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, request_id: Optional[object] = None) -> object:

@@ -1,4 +1,4 @@
-"""Decode steps replayed from CUDA graphs, one graph per batch size.
+"""Decode steps replayed from CUDA graphs, one or two graphs per batch size.
 
 A step in which every request brings one token and wants its logits has the same launches
 every time; only the small integer arrays of the step (tokens, positions, lengths, block
@@ -6,7 +6,10 @@ tables) change.  Such a step is captured once per batch size into a ``torch.cuda
 over a static copy of those arrays; afterwards a step is one pinned-to-device copy and one
 graph launch.  Kernels read every length from the device, so a graph captured at one
 context length serves all of them: the decode attention divides the key tiles among its
-blocks inside the kernel, from the lengths of the step at hand.
+blocks inside the kernel, from the lengths of the step at hand.  What a graph does freeze is
+the form of its launches, and the decode attention has two: one for any lengths, and a faster
+one for a few requests of about equal length (``StepView.rows_alike``).  So a batch size may
+have two graphs, and each step replays the one that fits its requests' lengths.
 
 As in raun6k/Pylon (src/pylon/decode/graph.py:157-242): one graph per exact batch size, no
 padding to a larger one; a size whose capture failed is not tried again and runs eagerly;
@@ -40,7 +43,9 @@ class DecodeGraphs:
         self.step_function = weakref.proxy(step_function)
         self.cache = step_function.cache
         self.device = step_function.device
-        self.captured: dict[int, CapturedStep] = {}
+        self.captured: dict[int, CapturedStep] = {}         # by batch size: for requests of any lengths
+        self.captured_alike: dict[int, CapturedStep] = {}   # by batch size: for requests of about equal length
+        self.force_alike: Optional[bool] = None             # set while graphs are captured ahead of use
         self.failed: set[int] = set()
         self.pool = None
         self.max_context = step_function.max_positions
@@ -53,10 +58,10 @@ class DecodeGraphs:
     def _layout(self, batch: int) -> StepLayout:
         return StepLayout(tokens=batch, rows=batch, logits=batch, table_widths=self.widths)
 
-    def capture(self, entries: Sequence[StepEntry]) -> Optional[CapturedStep]:
-        """Captures the graph of ``len(entries)`` rows, using ``entries`` (already prepared in
-        the cache) as the example step.  Returns ``None`` and remembers the size if capture
-        fails."""
+    def capture(self, entries: Sequence[StepEntry], alike: bool) -> Optional[CapturedStep]:
+        """Captures the graph of ``len(entries)`` rows, in the form for requests of about equal
+        length or in the one for any lengths, using ``entries`` (already prepared in the cache)
+        as the example step.  Returns ``None`` and remembers the size if capture fails."""
         from pylon_b200.kernels import ops
 
         batch = len(entries)
@@ -67,6 +72,7 @@ class DecodeGraphs:
         function.fill(entries, layout, host.numpy())
         static_buffer.copy_(host, non_blocking=True)
         step, tables = function.view(static_buffer, layout, 1, self.max_context)
+        step.rows_alike = alike
         caches = self.cache.layer_caches(tables)
         collector_was_on = gc.isenabled()
         gc.disable()   # destroying an old graph or a pinned buffer in mid-capture would invalidate it
@@ -93,7 +99,7 @@ class DecodeGraphs:
             if collector_was_on:
                 gc.enable()
         captured = CapturedStep(graph, layout, static_buffer, logits, launches)
-        self.captured[batch] = captured
+        (self.captured_alike if alike else self.captured)[batch] = captured
         return captured
 
     def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -104,9 +110,10 @@ class DecodeGraphs:
         batch = len(entries)
         if batch in self.failed:
             return None
-        captured = self.captured.get(batch)
+        alike = self.step_function.rows_alike(entries) if self.force_alike is None else self.force_alike
+        captured = (self.captured_alike if alike else self.captured).get(batch)
         if captured is None:
-            captured = self.capture(entries)
+            captured = self.capture(entries, alike)
             if captured is None:
                 return None
             # the capture itself launched nothing; fall through to the first replay

@@ -110,6 +110,13 @@ class StepFunction:
             buffer[base : base + table.size] = table.reshape(-1)
         return max_q, max_kv
 
+    @staticmethod
+    def rows_alike(entries: Sequence[StepEntry]) -> bool:
+        """Whether the requests of the step hold about equally many tokens after it: the longest
+        at most an eighth above the mean (see :class:`~pylon_b200.parts.base.StepView`)."""
+        lengths = [entry.request.length + len(entry.tokens) for entry in entries]
+        return max(lengths) * len(lengths) * 8 <= sum(lengths) * 9
+
     def validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -187,4 +194,5 @@ class StepFunction:
         device_buffer = host.to(self.device, non_blocking=True)
         step, tables = self.view(device_buffer, layout, max_q, max_kv)
         step.row_tokens = tuple(len(entry.tokens) for entry in entries)
+        step.rows_alike = self.rows_alike(entries)
         return self.model.forward(step, self.cache.layer_caches(tables))

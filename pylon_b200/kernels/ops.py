@@ -135,7 +135,7 @@ _SIGNATURES = {
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "pylon_attention_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
         "pylon_attention_decode_blocks": [],
     },
@@ -612,6 +612,7 @@ def paged_attention(
     decode_blocks: Optional[int] = None,
     prefill_kernel: Optional[str] = None,
     row_tokens: Optional[Sequence[int]] = None,
+    rows_alike: bool = False,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
@@ -627,7 +628,10 @@ def paged_attention(
     ``row_tokens``: the rows' token counts on the host, if the caller has them: the kernel
     for prompt portions then launches blocks only for the rows that are its own (a step that
     mixes one portion with 63 decoded rows would otherwise start 63 rows of blocks that find
-    nothing to do).  Returns ``[T, nq * d]``.
+    nothing to do).  ``rows_alike``: the caller knows that the rows hold about equally many tokens;
+    a step of a few decoded rows then gives every (row, KV head) pair a thread-block cluster of
+    its own, whose blocks combine their results through distributed shared memory (right for any
+    lengths, but slow if they differ much).  Returns ``[T, nq * d]``.
 
     bfloat16 with a head size that is a multiple of 16 up to 256 runs on the tensor cores
     (built per head size on first use): prompt portions on ``tcgen05.mma`` with the accumulators
@@ -691,7 +695,7 @@ def paged_attention(
         _check(library, library.pylon_paged_attention_mma(
             _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(counters), _ptr(q_start), _ptr(kv_len),
             _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
-            int(max_q), splits, blocks, int(use_tcgen05), _ptr(attention_error_word(q.device)), _stream()))
+            int(max_q), splits, blocks, int(use_tcgen05), int(bool(rows_alike)), _ptr(attention_error_word(q.device)), _stream()))
         return out
     _need(d <= 512, f"paged_attention: head size {d} is larger than 512")
     library = _library("attention_simple.cu")

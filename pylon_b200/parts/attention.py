@@ -98,5 +98,6 @@ class GroupedQueryAttention(Mixer):
         context = ops.paged_attention(
             q, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
+            rows_alike=step.rows_alike,
         )
         return ops.linear_for_residual(context, self.w_o)

@@ -107,6 +107,9 @@ class StepView:
     step is replayed from a CUDA graph).
     row_tokens: the number of tokens each row brings, as host integers, for parts that plan
     their launches on the host; ``None`` when the step is replayed from a CUDA graph.
+    rows_alike: the requests of the step hold about equally many tokens (within an eighth of the
+    longest), so that work dealt out evenly by row is dealt out evenly; a hint, never needed for
+    a right result.
     """
 
     token_ids: torch.Tensor
@@ -124,6 +127,7 @@ class StepView:
     dtype: torch.dtype
     device: torch.device
     row_tokens: Optional[tuple] = None
+    rows_alike: bool = False
 
 
 # ---------------------------------------------------------------------------------------

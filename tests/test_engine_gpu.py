@@ -171,10 +171,14 @@ def test_graphs_can_be_captured_ahead_of_use(tiny_folders):
     assert engine.capture_decode_graphs([1, 2, 3]) == [1, 2, 3]
     engine.cache.check()
     assert engine.cache.free_slots() == 4 and engine.cache.free_pages() == [g.pool.num_pages for g in engine.cache.groups]
-    before = dict(engine.step_function.graphs.captured)
+    graphs = engine.step_function.graphs
+    # both forms of a step: for requests of about equal length (every size) and for any lengths (from two requests on)
+    assert sorted(graphs.captured_alike) == [1, 2, 3] and sorted(graphs.captured) == [2, 3]
+    before, before_alike = dict(graphs.captured), dict(graphs.captured_alike)
     results = engine.generate(prompts_for(name), SamplingParams(max_new_tokens=4, temperature=0.0))
     assert all(len(r.output_ids) == 4 for r in results)
-    assert all(engine.step_function.graphs.captured[size] is graph for size, graph in before.items())   # reused, not recaptured
+    assert all(graphs.captured[size] is graph for size, graph in before.items())               # reused, not recaptured
+    assert all(graphs.captured_alike[size] is graph for size, graph in before_alike.items())
     with pytest.raises(RuntimeError, match="cuda_graphs"):
         engine_for(tiny_folders[name], name, "bfloat16").capture_decode_graphs([1])
 

@@ -396,6 +396,42 @@ def test_paged_attention(case, mode):
     assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0   # no wait for a TMA copy ran out
 
 
+@pytest.mark.parametrize("rows, nkv, group, d, page, window", [
+    (1, 8, 4, 128, 256, None),     # one request: clusters of 8
+    (3, 2, 4, 128, 64, None),
+    (5, 8, 2, 64, 64, None),       # 40 pairs: clusters of 6
+    (8, 8, 4, 128, 256, None),     # 64 pairs: clusters of 4
+    (11, 8, 1, 64, 128, 90),       # 88 pairs: clusters of 3, a window
+    (30, 4, 2, 128, 64, None),     # 120 pairs: clusters of 2
+    (40, 4, 2, 64, 64, None),      # 160 pairs: too many for clusters, the runs
+])
+@pytest.mark.parametrize("lengths", ["equal", "ragged", "short"])
+def test_decode_attention_in_clusters(rows, nkv, group, d, page, window, lengths):
+    """Rows of decoded tokens with the hint that they are about equally long: every (row, KV head)
+    pair gets a cluster of blocks that combine through distributed shared memory.  The result
+    must be right whatever the lengths are: equal, very different (the hint was wrong), and
+    shorter than a cluster has blocks (blocks without tiles), with rows of two tokens among them."""
+    from pylon_b200.kernels import ops
+
+    nq = nkv * group
+    if lengths == "equal":
+        kv_lens = [700 + (i % 3) for i in range(rows)]
+    elif lengths == "ragged":
+        kv_lens = [1 + (211 * i) % 900 for i in range(rows)]
+    else:
+        kv_lens = [1 + (37 * i) % 130 for i in range(rows)]
+    q_lens = [2 if (i % 4 == 1 and kv_lens[i] >= 2 and 2 * group <= 16) else 1 for i in range(rows)]
+    cache = Paged(kv_lens, q_lens, nkv, d, page, torch.bfloat16, seed=rows)
+    fused = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    expected = attention_reference(fused[:, : nq * d].reshape(cache.tokens, nq, d), cache, nq, nkv, d, window, scale)
+    for alike in (True, False):
+        out = ops.paged_attention(fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table,
+                                  nq, max(q_lens), max(kv_lens), window=window, rows_alike=alike)
+        torch.testing.assert_close(out.double(), expected, rtol=2e-2, atol=2e-2)
+    assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0
+
+
 @pytest.mark.parametrize("mode", ["float32", "bfloat16_mma", "bfloat16_mma_splits"])
 def test_attention_finds_one_far_key_among_hundreds(mode):
     """Random keys would hide a wrong page: here one key far back dominates the softmax,

@@ -83,7 +83,7 @@ def test_decode_steps_replayed_from_cuda_graphs(name, cutting, dtype, tiny_folde
     got = trace_tools.run_in_process(engine, steps)
     compare(got, expected[name], dtype)
     graphs = engine.step_function.graphs
-    assert graphs.captured and not graphs.failed
+    assert (graphs.captured or graphs.captured_alike) and not graphs.failed
 
 
 @pytest.mark.parametrize("name", ["tinyA", "tinyB"])
