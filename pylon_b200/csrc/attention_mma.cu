@@ -377,6 +377,10 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
 // a page and is addressed with one table look-up; otherwise keys are gathered one by one.
 // -----------------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 2;   // two stages leave room for three blocks per SM: warps in flight matter more than depth
+// The cluster form runs with two blocks per SM at most and would have room for a third stage, but then only two blocks fit
+// an SM at all, and clusters that have to be placed whole on one GPC no longer find room at once: 3.88 ms a step instead of
+// 3.25 at batch 12, 2.75 instead of 2.49 at batch 4 (2.11 instead of 2.14 at batch 1).
+constexpr int DEC_CLUSTER_STAGES = 2;
 
 // Two ways to bring a 64-key tile into shared memory.  With a head size that is a multiple of
 // 64 and pages that are multiples of 64 keys, TMA copies the tile (one elected thread, boxes of
@@ -384,12 +388,12 @@ constexpr int DEC_STAGES = 2;   // two stages leave room for three blocks per SM
 // this way reaches 5.9 TB/s where per-thread 16-byte cp.async copies reached 3.4.  Otherwise
 // every thread gathers 16-byte pieces with cp.async into rows padded by 8 values.
 constexpr bool TMA_HEAD = D % 64 == 0;
-template <bool TMA>
+template <bool TMA, int STAGES = DEC_STAGES>
 struct DecodeTiles {
   static constexpr int ROW = TMA ? D : LD;                        // values between two keys of a box / a padded row
   static constexpr int TILE = BLOCK_N * ROW;                      // one 64-key tile of keys or of values
   static constexpr int STAGE = 2 * TILE;                          // keys then values
-  static constexpr size_t STAGE_BYTES = (size_t)DEC_STAGES * STAGE * sizeof(__nv_bfloat16);
+  static constexpr size_t STAGE_BYTES = (size_t)STAGES * STAGE * sizeof(__nv_bfloat16);
   // stages (1024-byte aligned for the swizzle), query tile, two mbarriers
   static constexpr size_t SMEM = (TMA ? 1024 : 0) + STAGE_BYTES + (size_t)SMALL_ROWS * LD * sizeof(__nv_bfloat16) + (TMA ? 64 : 0);
   static_assert(STAGE * sizeof(__nv_bfloat16) >= 4 * SMALL_ROWS * D * sizeof(float), "the warps' outputs are merged in one idle stage");
@@ -489,12 +493,13 @@ __device__ __forceinline__ int run_of(int tile, int total, int used) { return (i
 template <bool TMA, int CLUSTER = 0>
 __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v) {
-  using Tiles = DecodeTiles<TMA>;
+  constexpr int STAGES = CLUSTER ? DEC_CLUSTER_STAGES : DEC_STAGES;
+  using Tiles = DecodeTiles<TMA, STAGES>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* smem_base = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023) : smem_raw;
-  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_base);                 // [DEC_STAGES][2][64 keys]
-  __nv_bfloat16* q_tile = stages + DEC_STAGES * Tiles::STAGE;                          // [16][LD]
-  uint64_t* tile_full = reinterpret_cast<uint64_t*>(q_tile + SMALL_ROWS * LD);         // [DEC_STAGES], TMA form
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_base);                 // [STAGES][2][64 keys]
+  __nv_bfloat16* q_tile = stages + STAGES * Tiles::STAGE;                          // [16][LD]
+  uint64_t* tile_full = reinterpret_cast<uint64_t*>(q_tile + SMALL_ROWS * LD);         // [STAGES], TMA form
   __shared__ int plan[4];   // tiles of the launch; the row this block starts in; tiles before that row; blocks with a run
   __shared__ int pending[DEC_PENDING][6];   // segments to publish: pair, first block, segments, q0, packed rows, KV head
   __shared__ bool pending_last[DEC_PENDING];
@@ -505,7 +510,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   const int G = p.group;
   if (TMA && threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < DEC_STAGES; ++s) att_mbar_init(&tile_full[s], 1);
+    for (int s = 0; s < STAGES; ++s) att_mbar_init(&tile_full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   // The rows' lengths were written long before the kernel ahead of this one started, so the plan
@@ -563,7 +568,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   const bool contiguous = p.page_size % BLOCK_N == 0;
   int position = CLUSTER ? 0 : run_begin(blockIdx.x, total_tiles, blocks_used), row = CLUSTER ? 0 : plan[1], before = CLUSTER ? 0 : plan[2];
   bool cluster_share_taken = false;
-  unsigned issued = 0, consumed = 0;   // tiles of this block so far: stage = count % DEC_STAGES
+  unsigned issued = 0, consumed = 0;   // tiles of this block so far: stage = count % STAGES
 
   // The next piece of this block's run: tiles [tile_begin, tile_end) of one (row, KV head).
   struct Segment {
@@ -613,7 +618,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   };
   // Starts the copy of one tile into the next stage of the ring.
   auto issue_tile = [&](const Segment& s, int tile) {
-    __nv_bfloat16* dst = stages + (issued % DEC_STAGES) * Tiles::STAGE;
+    __nv_bfloat16* dst = stages + (issued % STAGES) * Tiles::STAGE;
     if (TMA) {
       if (threadIdx.x == 0) {
         // A tile lies in one page.  Without a page for it the row coordinate points past the
@@ -622,7 +627,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
         const int page = s.table[key0 / p.page_size];
         const bool page_ok = page >= 0 && page < p.num_pages;
         const int y = page_ok ? (page * p.nkv + s.kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
-        uint64_t* bar = &tile_full[issued % DEC_STAGES];
+        uint64_t* bar = &tile_full[issued % STAGES];
         att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
 #pragma unroll
         for (int box = 0; box < D / 64; ++box) {
@@ -747,7 +752,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
         // of them as the ring has stages are asked for before this kernel waits for that one.  The queries and the
         // newest keys are its work.
         if (TMA) {
-          while (issued_ahead < DEC_STAGES && tile_begin + issued_ahead < tile_end && (tile_begin + issued_ahead + 1) * BLOCK_N <= pos0) {
+          while (issued_ahead < STAGES && tile_begin + issued_ahead < tile_end && (tile_begin + issued_ahead + 1) * BLOCK_N <= pos0) {
             issue_tile(current, tile_begin + issued_ahead);
             ++issued_ahead;
           }
@@ -758,10 +763,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       }
       load_query(current);
       if (TMA) cp_async_commit();   // otherwise the first tile's group carries the query
-      if (issued_ahead == 0) {
-#pragma unroll
-        for (int s = 0; s < DEC_STAGES - 1; ++s) issue(tile_begin + s);
-      }
+      for (int s = issued_ahead; s < STAGES - 1; ++s) issue(tile_begin + s);   // the ring runs STAGES - 1 tiles ahead
     }
 
     const bool upper_rows_unused = packed_rows <= 8;
@@ -772,24 +774,24 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
 
     bool tile_prefetched = false;   // the following segment's first tile is on its way
     for (int tile = tile_begin; tile < tile_end; ++tile) {
-      if (tile + DEC_STAGES - 1 < tile_begin + issued_ahead) {
+      if (tile + STAGES - 1 < tile_begin + issued_ahead) {
         // asked for before the wait
-      } else if (TMA && DEC_STAGES == 2 && tile + 1 == tile_end && have_following) {
+      } else if (TMA && STAGES == 2 && tile + 1 == tile_end && have_following) {
         // The ring has a free stage and this segment no tile for it: the following segment's
         // first tile comes in while this one's last tile is multiplied and the warps are merged.
         issue_tile(following, following.tile_begin);
         tile_prefetched = true;
       } else {
-        issue(tile + DEC_STAGES - 1);
+        issue(tile + STAGES - 1);
       }
-      const __nv_bfloat16* ks = stages + (consumed % DEC_STAGES) * Tiles::STAGE;
+      const __nv_bfloat16* ks = stages + (consumed % STAGES) * Tiles::STAGE;
       const __nv_bfloat16* vs = ks + Tiles::TILE;
       if (TMA) {
         if (tile == tile_begin) {
           cp_async_wait<0>();
           __syncthreads();   // the query tile is in
         }
-        if (!att_mbar_wait(&tile_full[consumed % DEC_STAGES], (consumed / DEC_STAGES) & 1)) {
+        if (!att_mbar_wait(&tile_full[consumed % STAGES], (consumed / STAGES) & 1)) {
           if (p.error) atomicExch(p.error, 1);
           if (!CLUSTER) return;   // every thread of the block gives up on the same copy
           break;                  // in a cluster the others wait for this block at the barrier: it goes there, its result void
@@ -806,7 +808,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
           __syncthreads();
         }
       } else {
-        cp_async_wait<DEC_STAGES - 1>();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
       }
       ++consumed;
@@ -900,7 +902,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     // query tile, which every warp has read; its first tile went into the stage that is not the
     // one read last (where the merge happens).
     prefetched = false;
-    if (TMA && DEC_STAGES == 2 && have_following) {
+    if (TMA && STAGES == 2 && have_following) {
       load_query(following);
       cp_async_commit();
       if (!tile_prefetched) issue_tile(following, following.tile_begin);
@@ -908,7 +910,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     }
 
     // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
-    __nv_bfloat16* idle_stage = stages + ((consumed + DEC_STAGES - 1) % DEC_STAGES) * Tiles::STAGE;   // the stage read last
+    __nv_bfloat16* idle_stage = stages + ((consumed + STAGES - 1) % STAGES) * Tiles::STAGE;   // the stage read last
     float* merge_o = reinterpret_cast<float*>(idle_stage);             // [4][16][D]: exactly one stage of the TMA form
     __syncthreads();
 #pragma unroll
@@ -1144,6 +1146,7 @@ static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
 }
 
 constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
+constexpr size_t DEC_SMEM_CLUSTER = DecodeTiles<TMA_HEAD, DEC_CLUSTER_STAGES>::SMEM;
 constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA : DEC_SMEM_GATHER;
 
 static int decode_sm_count() {
@@ -1231,7 +1234,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
     if (err == cudaSuccess) err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA);
 #define PYLON_CLUSTER_CASE(N)                                                                                                   \
     if (err == cudaSuccess && TMA_HEAD)                                                                                         \
-      err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_TMA);
+      err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_CLUSTER);
     PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
@@ -1289,7 +1292,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
         if (pairs * size > decode_blocks) size = 0;
       }
 #define PYLON_CLUSTER_CASE(N)                                                                                                   \
-      if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), DEC_SMEM_TMA, \
+      if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), DEC_SMEM_CLUSTER, \
                                               stream, N, p, map_k, map_v);
       PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
