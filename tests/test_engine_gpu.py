@@ -183,6 +183,28 @@ def test_graphs_can_be_captured_ahead_of_use(tiny_folders):
         engine_for(tiny_folders[name], name, "bfloat16").capture_decode_graphs([1])
 
 
+def test_a_decode_step_replays_the_graph_that_fits_its_lengths(tiny_folders):
+    """Two requests of equal length decode from the graph captured for such steps, two of very
+    different lengths from the other one; the tokens are those of eager steps either way."""
+    from pylon_b200.sampling import SamplingParams
+
+    name = "tinyC"
+    rng = np.random.default_rng(3)
+    vocab = TINY_CONFIGS[name]["vocab_size"]
+    greedy = SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True)
+    equal = [rng.integers(0, vocab, size=40).tolist() for _ in range(2)]
+    ragged = [rng.integers(0, vocab, size=n).tolist() for n in (150, 9)]
+    plain_engine = engine_for(tiny_folders[name], name, "bfloat16")
+    engine = engine_for(tiny_folders[name], name, "bfloat16", cuda_graphs=True)
+    graphs = engine.step_function.graphs
+    got = engine.generate(equal, [greedy] * 2)
+    assert sorted(graphs.captured_alike) == [2] and not graphs.captured
+    assert [r.output_ids for r in got] == [r.output_ids for r in plain_engine.generate(equal, [greedy] * 2)]
+    got = engine.generate(ragged, [greedy] * 2)
+    assert sorted(graphs.captured) == [2] and not graphs.failed
+    assert [r.output_ids for r in got] == [r.output_ids for r in plain_engine.generate(ragged, [greedy] * 2)]
+
+
 def test_command_line(tiny_folders, tmp_path):
     name = "tinyA"
     cfg, weights = plain.read_model(tiny_folders[name])

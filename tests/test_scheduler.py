@@ -234,3 +234,22 @@ def test_sampling_options_are_checked():
         SamplingParams(top_p=0.0)
     defaults = SamplingParams()
     assert (defaults.max_new_tokens, defaults.temperature, defaults.top_p) == (256, 0.2, 0.95)
+
+
+def test_rows_alike_is_a_matter_of_the_longest_against_the_mean():
+    """The hint the step function gives the parts: the requests of a step hold about equally many
+    tokens after it when the longest is at most an eighth above the mean."""
+    from types import SimpleNamespace
+
+    from pylon_b200.engine.step import StepFunction
+
+    def entries(*pairs):   # (tokens held, tokens brought)
+        return [SimpleNamespace(request=SimpleNamespace(length=held), tokens=[0] * brought) for held, brought in pairs]
+
+    assert StepFunction.rows_alike(entries((4000, 1)))
+    assert StepFunction.rows_alike(entries((4095, 1), (4095, 1), (4090, 1)))
+    assert StepFunction.rows_alike(entries((0, 1), (0, 1)))
+    assert StepFunction.rows_alike(entries((800, 1), (1000, 1)))            # 1001 against a mean of 901
+    assert not StepFunction.rows_alike(entries((700, 1), (1000, 1)))        # 1001 against a mean of 851
+    assert not StepFunction.rows_alike(entries((4000, 1), (10, 1), (10, 1)))
+    assert StepFunction.rows_alike(entries((2000, 48), (2047, 1)))           # what a request brings counts as held
