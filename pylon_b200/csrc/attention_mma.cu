@@ -1147,7 +1147,29 @@ static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
 
 constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
 constexpr size_t DEC_SMEM_CLUSTER = DecodeTiles<TMA_HEAD, DEC_CLUSTER_STAGES>::SMEM;
+static bool clusters_of_16() {
+  static const bool allowed = [] {
+    if (!TMA_HEAD) return false;
+    auto kernel = paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? 16 : 0>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_CLUSTER) != cudaSuccess) { cudaGetLastError(); return false; }
+    // does the device place such a cluster at all?
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(16); config.blockDim = dim3(ATT_THREADS); config.dynamicSmemBytes = DEC_SMEM_CLUSTER;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 16; attribute[0].val.clusterDim.y = 1; attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute; config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) { cudaGetLastError(); return false; }
+    return clusters >= 1;
+  }();
+  return allowed;
+}
 constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA : DEC_SMEM_GATHER;
+
+// Clusters of 16 blocks are beyond the portable size: the kernel has to opt in, and the device may refuse.
+static bool clusters_of_16();
 
 static int decode_sm_count() {
   static int count = [] {
@@ -1235,7 +1257,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
 #define PYLON_CLUSTER_CASE(N)                                                                                                   \
     if (err == cudaSuccess && TMA_HEAD)                                                                                         \
       err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_CLUSTER);
-    PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
+    PYLON_CLUSTER_CASE(16) PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
@@ -1282,19 +1304,19 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
     if (tma) {
       if (!page_pool_map(&map_k, k_pages, pool_rows) || !page_pool_map(&map_v, v_pages, pool_rows))
         PYLON_REFUSE("paged_attention_mma: the tensor maps of the page pools could not be made");
-      // Few pairs of about equal length: a cluster of blocks for each, as large as leaves two blocks to an SM (with three,
+      // Few pairs of about equal length: a cluster of blocks for each (16 where the device places such clusters), as large as leaves two blocks to an SM (with three,
       // clusters measured slower than the runs: 3.23 against 2.97 ms a step at batch 8) and within the caller's blocks.
       const long long pairs = (long long)num_rows * nkv;
       int size = 0;
       if (TMA_HEAD && rows_alike) {
         const long long room = 2LL * decode_sm_count() / pairs;
-        size = room >= 8 ? 8 : room >= 6 ? 6 : room >= 4 ? 4 : room >= 3 ? 3 : room >= 2 ? 2 : 0;
+        size = (room >= 16 && clusters_of_16()) ? 16 : room >= 8 ? 8 : room >= 6 ? 6 : room >= 4 ? 4 : room >= 3 ? 3 : room >= 2 ? 2 : 0;
         if (pairs * size > decode_blocks) size = 0;
       }
 #define PYLON_CLUSTER_CASE(N)                                                                                                   \
       if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), DEC_SMEM_CLUSTER, \
                                               stream, N, p, map_k, map_v);
-      PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
+      PYLON_CLUSTER_CASE(16) PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
       if (size == 0)
         launch_dependent(paged_attention_decode_kernel<TMA_HEAD>, dim3(decode_blocks), dim3(ATT_THREADS), DEC_SMEM_TMA, stream, p, map_k, map_v);

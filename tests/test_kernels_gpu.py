@@ -397,8 +397,9 @@ def test_paged_attention(case, mode):
 
 
 @pytest.mark.parametrize("rows, nkv, group, d, page, window", [
-    (1, 8, 4, 128, 256, None),     # one request: clusters of 8
+    (1, 8, 4, 128, 256, None),     # one request: clusters of 16
     (3, 2, 4, 128, 64, None),
+    (3, 8, 4, 128, 64, None),      # 24 pairs: clusters of 8
     (5, 8, 2, 64, 64, None),       # 40 pairs: clusters of 6
     (8, 8, 4, 128, 256, None),     # 64 pairs: clusters of 4
     (11, 8, 1, 64, 128, 90),       # 88 pairs: clusters of 3, a window
