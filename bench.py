@@ -328,6 +328,38 @@ def prefill_flops(cfg: dict, tokens: int) -> float:
     return cfg["num_hidden_layers"] * (per_layer + attention) + head
 
 
+METRIC = "decode tokens/s, Qwen3-4B shape, batch 8, context 4096"
+
+
+def headline_config(layers: int, batch: int, cuda_graphs: bool, peak_source: str) -> dict:
+    fields = QWEN3_4B
+    return {
+        "model": "Qwen3-4B shape", "layers": layers, "layers_of_model": fields["num_hidden_layers"],
+        "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
+        "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
+        "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
+        "parallelism": "single GPU", "cuda_graphs": cuda_graphs, "l2": "inputs larger than L2 (8 GB of weights per step)",
+        "peaks": peak_source, "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
+    }
+
+
+def run_reference_arm(args) -> int:
+    """raun6k/Pylon itself on the same workload: see baseline/reference_arm.py."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("reference_arm", ROOT / "baseline" / "reference_arm.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    peak = peaks()
+    shared = {
+        "context": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS, "clock_sampler": ClockSampler, "peaks": peak,
+        "prefill_flops": lambda tokens: prefill_flops(QWEN3_4B, tokens), "metric": METRIC,
+        "baseline_tokens_per_second": BASELINE_TOKENS_PER_SECOND,
+        "config": headline_config(QWEN3_4B["num_hidden_layers"], args.batch, True, peak["source"]),
+    }
+    return module.run(args, shared)
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -345,8 +377,7 @@ def main() -> int:
     args = parser.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "raun6k/Pylon does not install offline: its build backend uv_build is not in the wheelhouse"}))
-        return 0
+        return run_reference_arm(args)
     if args.gpus != 1:
         print("bench.py measures a single-GPU engine; --gpus must be 1")
         return 2
@@ -398,7 +429,7 @@ def main() -> int:
     achieved = (weight_bytes + kv_bytes) / (decode["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(fields, PREFILL_TOKENS)
     record = {
-        "metric": "decode tokens/s, Qwen3-4B shape, batch 8, context 4096",
+        "metric": METRIC,
         "value": round(decode["tokens_per_second"], 1),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -410,14 +441,7 @@ def main() -> int:
         "vs_baseline": round(decode["tokens_per_second"] / BASELINE_TOKENS_PER_SECOND, 2),
         "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids, caches filled by real prefill",
-        "config": {
-            "model": "Qwen3-4B shape", "layers": args.layers, "layers_of_model": QWEN3_4B["num_hidden_layers"],
-            "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
-            "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
-            "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-            "parallelism": "single GPU", "cuda_graphs": engine_config.cuda_graphs, "l2": "inputs larger than L2 (8 GB of weights per step)",
-            "peaks": peak["source"], "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
-        },
+        "config": headline_config(args.layers, args.batch, engine_config.cuda_graphs, peak["source"]),
         "clocks": clocks,
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": decode["launches"],

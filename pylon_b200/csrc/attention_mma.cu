@@ -519,7 +519,10 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   int cluster_first = 0, cluster_tiles = 0;
   if (CLUSTER) {
     cluster_tiles = decode_row_tiles(p, cluster_pair / p.nkv, &cluster_first);
-    if (cluster_tiles == 0) return;   // not a row of decoded tokens: the whole cluster leaves
+    if (cluster_tiles == 0) {   // not a row of decoded tokens: the whole cluster leaves
+      grid_dependency_wait();   // a grid must not end before the grid ahead of it has: the next kernel's wait sees only this one
+      return;
+    }
   }
   if (!CLUSTER && warp == 0) {
     int unused;
@@ -562,7 +565,10 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
   }
   __syncthreads();
   const int total_tiles = CLUSTER ? 0 : plan[0];
-  if (!CLUSTER && plan[1] < 0) return;
+  if (!CLUSTER && plan[1] < 0) {   // no run for this block
+    grid_dependency_wait();   // a grid must not end before the grid ahead of it has: the next kernel's wait sees only this one
+    return;
+  }
   const int blocks_used = CLUSTER ? 1 : plan[3];
   const int run_end = CLUSTER ? 0 : run_begin(blockIdx.x + 1, total_tiles, blocks_used);
   const bool contiguous = p.page_size % BLOCK_N == 0;

@@ -187,11 +187,13 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   const int q_len = p.q_start[row + 1] - q0;
   const int G = p.group;
   const int packed_rows = q_len * G;
-  if (packed_rows <= 0 || (p.skip_small && packed_rows <= FA_SMALL_ROWS)) return;
+  // A block that has nothing to do still waits for the kernel ahead before it leaves: if every block left at once, this
+  // grid would end before that kernel, and the next kernel's wait, which sees only this grid, would let it read too early.
+  if (packed_rows <= 0 || (p.skip_small && packed_rows <= FA_SMALL_ROWS)) { grid_dependency_wait(); return; }
   // Later query tiles see more keys: hand them out first (the query tile runs slowest in the grid, so the longest
   // blocks of all heads and rows start first).
   const int q_tiles = (packed_rows + FA_BM - 1) / FA_BM;
-  if ((int)blockIdx.z >= q_tiles) return;
+  if ((int)blockIdx.z >= q_tiles) { grid_dependency_wait(); return; }
   const int m0 = (q_tiles - 1 - (int)blockIdx.z) * FA_BM;
   const int kv_len = p.kv_len[row];
   const int pos0 = kv_len - q_len;   // position of the row's first new token
@@ -204,6 +206,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if ((fa_smem(smem) & 1023u) != 0) {   // the swizzle arithmetic below assumes it
     if (threadIdx.x == 0) atomicExch(p.error, 4);
+    grid_dependency_wait();
     return;
   }
   if (threadIdx.x == 0) {

@@ -358,7 +358,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   const int heads = nq + 2 * nkv;
   const int groups = (heads + HPW - 1) / HPW;
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
-  if (item >= (long long)num_tokens * groups) return;
+  if (item >= (long long)num_tokens * groups) { grid_dependency_wait(); return; }
   const int t = (int)(item / groups), head_begin = (int)(item % groups) * HPW;
   // Position, page and angles are the step's own data, not the work of the kernel before this one: they are looked up
   // while that kernel finishes.
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(128, 5) qk_norm_rope_kv_write_wide_kernel(
   const int heads = nq + 2 * nkv;
   const int groups = (heads + PER_WARP - 1) / PER_WARP;
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
-  if (item >= (long long)num_tokens * groups) return;
+  if (item >= (long long)num_tokens * groups) { grid_dependency_wait(); return; }
   const int t = (int)(item / groups), head_begin = (int)(item % groups) * PER_WARP;
   const int sub = lane / LANES, column = (lane % LANES) * 8;   // this lane's head within a pass, its eight columns
   // Position, page and angles are the step's own data: looked up while the kernel before this one finishes.

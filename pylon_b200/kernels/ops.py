@@ -662,6 +662,8 @@ def paged_attention(
         any_large = max_q * group > 16
         # Rows of decoded tokens can occur unless the step is one long row.
         maybe_small = not any_large or rows > 1
+        if row_tokens is not None and len(row_tokens) == rows and all(count * group > 16 for count in row_tokens):
+            maybe_small = False   # the host knows that every row is a prompt portion: no launch of the decode kernel
         # Prompt portions go to the tcgen05 kernel where it exists: head size 64 or 128, pages of a multiple of 64 keys.
         if prefill_kernel is None:
             prefill_kernel = "tcgen05" if d in (64, 128) and page_size % 64 == 0 and num_splits in (None, 1) else "mma"
