@@ -1,10 +1,13 @@
 """The cache manager: pages of keys and values with a block table per request, in groups,
 and slots of fixed-size state per request.
 
-* Runs of the model whose mixers need the same kind of key/value cache (same KV heads, head
-  size and window) form a **group**.  Each group has pages of its own: one pool of page
-  numbers, one device tensor ``[runs, 2, pages, kv_heads, page_size, head_dim]``, and for
-  every request one table *logical page -> physical page*.
+* Runs of the model whose mixers need the same kind of key/value cache (same KV heads, row
+  widths and window) form a **group**.  Each group has pages of its own: one pool of page
+  numbers - as many pages as that group needs, which for a windowed group is far fewer than
+  for one that keeps everything -, a device tensor of key rows ``[runs, pages, kv_heads,
+  page_size, head_dim]``, one of value rows of the width the group's mixers ask for (or none,
+  for a mixer that keeps one row per token), and for every request one table *logical page ->
+  physical page*.
 * Pages are acquired just before the step that writes them (all of a step or none), given
   back when the request is closed, and — in a windowed group — as soon as every position
   on them lies behind the window of every token still to come.  Free pages are reused
@@ -21,7 +24,7 @@ garbage-collector finalizers, and there are groups, windows and state slots.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Iterable, Optional, Sequence
+from typing import Iterable, Mapping, Optional, Sequence, Union
 
 import numpy as np
 import torch
@@ -86,7 +89,8 @@ class CacheGroup:
     runs: list[int]                      # positions in the model's run order
     pool: PagePool
     page_size: int
-    storage: Optional[torch.Tensor] = None   # [runs, 2, pages, kv_heads, page_size, head_dim]
+    keys: Optional[torch.Tensor] = None      # [runs, pages, kv_heads, page_size, head_dim]
+    values: Optional[torch.Tensor] = None    # [runs, pages, kv_heads, page_size, value width]; None if the need has no value rows
 
     def pages_for(self, tokens: int) -> int:
         return (tokens + self.page_size - 1) // self.page_size
@@ -101,9 +105,10 @@ class CacheGroup:
         span = min(capacity, self.need.window - 1 + max(1, max_step_tokens))
         return min(full, self.pages_for(span) + 1)
 
-    def bytes_per_token(self) -> int:
-        element = 0 if self.storage is None else self.storage.element_size()
-        return len(self.runs) * 2 * self.need.n_kv_heads * self.need.head_dim * element
+    def bytes_per_token(self, element_size: Optional[int] = None) -> int:
+        if element_size is None:
+            element_size = 0 if self.keys is None else self.keys.element_size()
+        return len(self.runs) * self.need.n_kv_heads * (self.need.head_dim + self.need.value_width) * element_size
 
 
 @dataclass
@@ -122,6 +127,24 @@ class RequestCache:
         return [page for page in self.tables[group] if page >= 0]
 
 
+def group_page_counts(needs: Sequence[Optional[CacheNeed]], page_size: int, pool_tokens: int, max_requests: int,
+                      longest_request: int, max_step_tokens: int) -> dict[KVNeed, int]:
+    """Pages per group for a pool that holds ``pool_tokens`` tokens: a group that keeps every key gets
+    ``pool_tokens / page_size`` pages; a windowed group gets what ``max_requests`` requests of
+    ``longest_request`` tokens can hold at once (window plus one step's tokens each), if that is fewer."""
+    counts: dict[KVNeed, int] = {}
+    full = max(1, -(-int(pool_tokens) // page_size))
+    for need in needs:
+        if need is None or need.kv is None or need.kv in counts:
+            continue
+        pages = full
+        if need.kv.window is not None:
+            probe = CacheGroup(need.kv, [], PagePool(1), page_size)
+            pages = min(full, max_requests * probe.lifetime_pages(longest_request, max_step_tokens))
+        counts[need.kv] = max(1, pages)
+    return counts
+
+
 # ---------------------------------------------------------------------------------------
 class CacheManager:
     def __init__(
@@ -130,14 +153,15 @@ class CacheManager:
         cache_of: Sequence[Optional[int]],
         *,
         page_size: int,
-        num_pages: int,
+        num_pages: Union[int, Mapping[KVNeed, int]],
         max_requests: int,
         dtype: torch.dtype = torch.bfloat16,
         device: Optional[torch.device] = None,
     ) -> None:
         """``needs[i]`` / ``cache_of[i]`` describe run ``i`` of the model's order: what its
-        mixer keeps, or which earlier run's cache it reads.  Every group gets ``num_pages``
-        pages of ``page_size`` tokens.  ``device=None`` keeps the books only."""
+        mixer keeps, or which earlier run's cache it reads.  ``num_pages``: how many pages of
+        ``page_size`` tokens each group gets - one number for all, or a number per
+        :class:`KVNeed` (see :func:`group_page_counts`).  ``device=None`` keeps the books only."""
         if page_size < 1:
             raise ValueError("page size must be positive")
         if max_requests < 1:
@@ -161,7 +185,8 @@ class CacheManager:
             if need.kv is not None:
                 if need.kv not in by_need:
                     by_need[need.kv] = len(self.groups)
-                    self.groups.append(CacheGroup(need.kv, [], PagePool(num_pages), self.page_size))
+                    pages = num_pages if isinstance(num_pages, int) else num_pages[need.kv]
+                    self.groups.append(CacheGroup(need.kv, [], PagePool(pages), self.page_size))
                 group = by_need[need.kv]
                 self._group_of_run[run] = group
                 self._index_in_group[run] = len(self.groups[group].runs)
@@ -171,9 +196,10 @@ class CacheManager:
         if self.device is not None:
             for group in self.groups:
                 kv = group.need
-                group.storage = torch.zeros(
-                    (len(group.runs), 2, num_pages, kv.n_kv_heads, self.page_size, kv.head_dim), dtype=dtype, device=self.device
-                )
+                rows = (len(group.runs), group.pool.num_pages, kv.n_kv_heads, self.page_size)
+                group.keys = torch.zeros((*rows, kv.head_dim), dtype=dtype, device=self.device)
+                if kv.value_width:
+                    group.values = torch.zeros((*rows, kv.value_width), dtype=dtype, device=self.device)
             for run, state in enumerate(self._state_needs):
                 if state is not None:
                     self._states[run] = torch.zeros((self.max_requests, *state.shape), dtype=state.dtype, device=self.device)
@@ -292,6 +318,26 @@ class CacheManager:
         del self._open[request.request_id]
         self._free_slots.append(request.slot)
 
+    # -- fixed-size state across a step that may fail ------------------------------------------
+    def has_state(self) -> bool:
+        return any(state is not None for state in self._states)
+
+    def save_state(self, requests: Sequence[RequestCache]) -> Optional[list]:
+        """Copies of the state slots of ``requests`` (``None`` if no run keeps a state): what
+        :meth:`restore_state` puts back when the step that was to advance them did not happen."""
+        if not self.has_state() or self.device is None:
+            return None
+        slots = torch.tensor([request.slot for request in requests], dtype=torch.long, device=self.device)
+        return [slots] + [None if state is None else state.index_select(0, slots) for state in self._states]
+
+    def restore_state(self, saved: Optional[list]) -> None:
+        if saved is None:
+            return
+        slots = saved[0]
+        for state, copy in zip(self._states, saved[1:]):
+            if state is not None:
+                state.index_copy_(0, slots, copy)
+
     # -- what a step hands the kernels -----------------------------------------------------
     def block_table(self, requests: Sequence[RequestCache], group: int, width: Optional[int] = None) -> np.ndarray:
         """int32 ``[rows, width]`` tables of ``requests`` in ``group`` (-1 where no page)."""
@@ -316,9 +362,9 @@ class CacheManager:
             cache = LayerCache(page_size=self.page_size, state=self._states[run])
             group = self._group_of_run[run]
             if group is not None:
-                storage = self.groups[group].storage
                 index = self._index_in_group[run]
-                cache.k_pages, cache.v_pages = storage[index, 0], storage[index, 1]
+                cache.k_pages = self.groups[group].keys[index]
+                cache.v_pages = None if self.groups[group].values is None else self.groups[group].values[index]
                 cache.block_table = block_tables[group]
             caches.append(cache)
         return caches

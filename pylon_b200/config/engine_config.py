@@ -8,21 +8,35 @@ from __future__ import annotations
 
 import math
 import os
-from dataclasses import dataclass, replace
-from typing import Mapping, Optional
+from dataclasses import dataclass, fields, replace
+from typing import Callable, Mapping, Optional
 
 import torch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+_SWITCH_WORDS = {"1": True, "true": True, "0": False, "false": False}
 
 
-def _env_bool(env: Mapping[str, str], name: str, default: bool) -> bool:
-    value = env.get(name, str(default)).strip().lower()
-    if value in {"1", "true"}:
-        return True
-    if value in {"0", "false"}:
-        return False
-    raise ValueError(f"{name} must be true, false, 1, or 0.")
+def _whole_number(value: object) -> bool:
+    return isinstance(value, int) and not isinstance(value, bool)
+
+
+def _read_switch(text: str) -> bool:
+    word = text.strip().lower()
+    if word not in _SWITCH_WORDS:
+        raise ValueError(f"a switch takes one of {sorted(_SWITCH_WORDS)}, not {text!r}")
+    return _SWITCH_WORDS[word]
+
+
+# option -> (environment variable, how its text is read); the defaults are the dataclass's own
+_ENVIRONMENT: dict[str, tuple[str, Callable[[str], object]]] = {
+    "prefill_chunk_size": ("PYLON_PREFILL_CHUNK_SIZE", int),
+    "max_batch_size": ("PYLON_MAX_BATCH_SIZE", int),
+    "max_queue_size": ("PYLON_MAX_QUEUE_SIZE", int),
+    "max_gpu_utilization": ("PYLON_MAX_GPU_UTILIZATION", float),
+    "cuda_graphs": ("PYLON_CUDA_GRAPHS", _read_switch),
+    "admit_skip": ("PYLON_ADMIT_SKIP", int),
+}
 
 
 @dataclass(frozen=True)
@@ -44,18 +58,18 @@ class EngineConfig:
     def __post_init__(self) -> None:
         if self.dtype not in _DTYPES:
             raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {self.dtype!r}")
-        if isinstance(self.prefill_chunk_size, bool) or not isinstance(self.prefill_chunk_size, int) or self.prefill_chunk_size < 1:
-            raise ValueError("prefill_chunk_size must be a positive integer.")
-        if self.max_batch_size < 1:
-            raise ValueError("max_batch_size must be at least 1.")
-        if self.max_queue_size < 1:
-            raise ValueError("max_queue_size must be at least 1.")
-        if not math.isfinite(self.max_gpu_utilization) or not 0 < self.max_gpu_utilization <= 1:
-            raise ValueError("max_gpu_utilization must be greater than 0 and at most 1.")
-        if isinstance(self.admit_skip, bool) or not isinstance(self.admit_skip, int) or self.admit_skip < 0:
-            raise ValueError("admit_skip must be an integer of at least 0.")
-        if self.page_size < 1:
-            raise ValueError("page_size must be positive.")
+        lowest = {"prefill_chunk_size": 1, "max_batch_size": 1, "max_queue_size": 1, "page_size": 1, "admit_skip": 0}
+        for name, least in lowest.items():
+            value = getattr(self, name)
+            if not _whole_number(value) or value < least:
+                raise ValueError(f"{name} = {value!r}: a whole number, {least} or more, is needed")
+        share = self.max_gpu_utilization
+        if not isinstance(share, (int, float)) or isinstance(share, bool) or not math.isfinite(share) or not 0 < share <= 1:
+            raise ValueError(f"max_gpu_utilization = {share!r}: a share of the device's memory, above 0 and up to 1, is needed")
+        for name in ("max_cache_tokens", "max_context"):
+            value = getattr(self, name)
+            if value is not None and (not _whole_number(value) or value < 1):
+                raise ValueError(f"{name} = {value!r}: a whole number of tokens, 1 or more, or None")
 
     @property
     def torch_dtype(self) -> torch.dtype:
@@ -63,13 +77,22 @@ class EngineConfig:
 
     @classmethod
     def from_env(cls, env: Optional[Mapping[str, str]] = None, **overrides) -> "EngineConfig":
+        """The options the environment gives (``env``: a mapping; default ``os.environ``), then ``overrides``
+        that are not ``None``.  An option the environment does not name keeps its default."""
         env = os.environ if env is None else env
-        base = cls(
-            prefill_chunk_size=int(env.get("PYLON_PREFILL_CHUNK_SIZE", "2048")),
-            max_batch_size=int(env.get("PYLON_MAX_BATCH_SIZE", "32")),
-            max_queue_size=int(env.get("PYLON_MAX_QUEUE_SIZE", "32")),
-            max_gpu_utilization=float(env.get("PYLON_MAX_GPU_UTILIZATION", "0.90")),
-            cuda_graphs=_env_bool(env, "PYLON_CUDA_GRAPHS", False),
-            admit_skip=int(env.get("PYLON_ADMIT_SKIP", "4")),
-        )
-        return replace(base, **{key: value for key, value in overrides.items() if value is not None})
+        known = {f.name for f in fields(cls)}
+        found = {}
+        for option, (variable, read) in _ENVIRONMENT.items():
+            text = env.get(variable)
+            if text is None:
+                continue
+            try:
+                found[option] = read(text)
+            except ValueError as error:
+                raise ValueError(f"{variable}={text!r} cannot be read: {error}") from None
+        for option, value in overrides.items():
+            if option not in known:
+                raise TypeError(f"EngineConfig has no option {option!r}")
+            if value is not None:
+                found[option] = value
+        return replace(cls(), **found)

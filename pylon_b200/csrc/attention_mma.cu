@@ -104,6 +104,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bflo
     if (valid) {
       const int page = table[key / p.page_size];
       valid = page >= 0 && page < p.num_pages;
+      if ((page < -1 || page >= p.num_pages) && p.error) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // -1: no page (behind a window); anything else outside the pool: a broken table
       if (valid) src = pages + (((size_t)page * p.nkv + kv_head) * p.page_size + key % p.page_size) * D + col * 8;
     }
     cp_async_16(dst + r * LD + col * 8, src, valid);
@@ -117,6 +118,7 @@ __device__ __forceinline__ void load_kv_tile_contiguous(__nv_bfloat16* dst, cons
   const int key0 = tile * BLOCK_N;
   const int page = key0 < kv_len ? table[key0 / p.page_size] : -1;
   const bool page_ok = page >= 0 && page < p.num_pages;
+  if ((page < -1 || page >= p.num_pages) && threadIdx.x == 0 && p.error) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // a broken table; -1 is "no page"
   const __nv_bfloat16* base = page_ok ? pages + (((size_t)page * p.nkv + kv_head) * p.page_size + key0 % p.page_size) * D : pages;
 #pragma unroll
   for (int i = 0; i < BLOCK_N * CHUNKS / ATT_THREADS; ++i) {
@@ -632,6 +634,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
         const int key0 = tile * BLOCK_N;
         const int page = s.table[key0 / p.page_size];
         const bool page_ok = page >= 0 && page < p.num_pages;
+        if ((page < -1 || page >= p.num_pages) && p.error) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // a broken table; -1 is "no page"
         const int y = page_ok ? (page * p.nkv + s.kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
         uint64_t* bar = &tile_full[issued % STAGES];
         att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
@@ -1178,18 +1181,21 @@ constexpr size_t DEC_SMEM_MOST = DEC_SMEM_TMA > DEC_SMEM_GATHER ? DEC_SMEM_TMA :
 static bool clusters_of_16();
 
 static int decode_sm_count() {
-  static int count = [] {
+  static int counts[pylon::MAX_DEVICES] = {};
+  int& count = counts[pylon::current_device_slot()];
+  if (count == 0) {
     int device = 0, value = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) value = 0;
-    return value;
-  }();
+    count = value;
+  }
   return count;
 }
 
 // Blocks of the decode kernel: as many as are resident at once, of the form that needs more
 // shared memory.
 extern "C" int pylon_attention_decode_blocks() {
-  static int resident = 0;
+  static int resident_on[pylon::MAX_DEVICES] = {};
+  int& resident = resident_on[pylon::current_device_slot()];
   if (resident == 0) {
     int device = 0, sm_count = 0, per_sm = 0, per_sm_tma = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
@@ -1215,7 +1221,8 @@ extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_to
 // [num_pages, nkv, page_size, D]; out: bfloat16 [tokens, nq, D]; q_start: int32 [rows + 1];
 // kv_len: int32 [rows]; block_table: int32 [rows, table_width]; max_q: the longest row (or an
 // upper bound); num_splits: key/value splits of rows with more than 16 packed query rows;
-// decode_blocks: blocks of the kernel for the other rows (1 .. pylon_attention_decode_blocks());
+// decode_blocks: blocks of the kernel for the other rows (1 .. pylon_attention_decode_blocks()); 0 with several rows: the caller knows that
+// none of them is that short, and the tiled kernel takes them all;
 // scratch: float32, pylon_attention_scratch_floats() long, contents arbitrary; counters:
 // num_rows * nkv unsigned integers that are zero before the call (and zero again after it).
 // scratch and counters may be null when num_splits = 1 and no row can have 16 packed rows or fewer
@@ -1243,7 +1250,9 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   const int group = nq / nkv;
   const long long packed_max = (long long)max_q * group;
   const bool any_large = packed_max > SMALL_ROWS;
-  const bool maybe_small = !any_large || num_rows > 1;   // a lone large row leaves nothing for the decode kernel
+  // A lone large row leaves nothing for the decode kernel; nor does a caller who knows that every row is large and
+  // says so by asking for no decode blocks (the tiled kernel then takes every row, whatever its size).
+  const bool maybe_small = !any_large || (num_rows > 1 && decode_blocks > 0);
   const bool run_tiled = any_large && !skip_large;
   if (!run_tiled) num_splits = 1;                        // no row for the tiled kernel
   if (num_splits > 1 && scratch == nullptr) PYLON_REFUSE("paged_attention_mma: splits need scratch memory");
@@ -1253,7 +1262,8 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
     if (decode_blocks < 1 || decode_blocks > most) PYLON_REFUSE("paged_attention_mma: %d decode blocks, 1 to %d are possible", decode_blocks, most);
     if (scratch == nullptr || counters == nullptr) PYLON_REFUSE("paged_attention_mma: rows of decoded tokens need scratch memory and counters");
   }
-  static bool configured = false;
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(paged_attention_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATT_SMEM_1);
     if (err == cudaSuccess && WIDE_TILES)

@@ -17,7 +17,9 @@
 //  * The counters by which the blocks of a decoded row find out which of them is last are a
 //    second fixed array (PYLON_STATIC_COUNTERS entries; rows x KV heads beyond that are
 //    refused).  They start at zero when the library is loaded and every launch that runs to
-//    its end leaves them at zero.
+//    its end leaves them at zero.  A kernel that gives up a bounded wait (pylon_static_error_word()
+//    is then non-zero and that call's output void) can leave counters of the rows it shared
+//    behind: call pylon_static_reset() before the entry point is used again.
 //  * The first call on each device looks up the arrays' device addresses and raises the
 //    kernels' shared-memory limit.  Make that first call outside any stream capture; later
 //    calls only launch kernels and may be captured like any other launch.
@@ -40,7 +42,7 @@ static __device__ __align__(256) unsigned pylon_static_counters[PYLON_STATIC_COU
 static __device__ int pylon_static_error;   // set by a kernel whose bounded wait for a TMA copy ran out
 
 namespace {
-constexpr int MAX_DEVICES = 64;
+using pylon::MAX_DEVICES;
 float* scratch_of_device[MAX_DEVICES] = {nullptr};
 unsigned* counters_of_device[MAX_DEVICES] = {nullptr};
 int* error_of_device[MAX_DEVICES] = {nullptr};
@@ -94,6 +96,42 @@ extern "C" int pylon_static_error_word() {
   int value = -1;
   if (cudaMemcpyFromSymbol(&value, pylon_static_error, sizeof(int)) != cudaSuccess) return -1;
   return value;
+}
+
+// Puts the built-in counters and the error word of the current device back to zero.  For use after
+// pylon_static_error_word() came back non-zero: the kernel that gave up did not take part in the count of the rows it
+// shared, so their counters are not where the next call expects them.  Waits for the device first (nothing of an
+// earlier call may still be counting).  0, or -2 with an error text.  Allocates nothing.
+extern "C" int pylon_static_reset() {
+  unsigned* counters = nullptr;
+  int* error = nullptr;
+  if (static_scratch_address(&counters, &error) == nullptr) return -2;
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err == cudaSuccess) err = cudaMemset(counters, 0, sizeof(unsigned) * PYLON_STATIC_COUNTERS);
+  if (err == cudaSuccess) err = cudaMemset(error, 0, sizeof(int));
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  if (err != cudaSuccess) {
+    snprintf(pylon::last_error_buffer(), 512, "pylon_static_reset: %s", cudaGetErrorString(err));
+    return -2;
+  }
+  return 0;
+}
+
+// For tests of the error handling, which make no kernel give up: writes counter `pair` and the error word from the
+// host, as a kernel that ran out of patience would have left them.  0, or -2 with an error text.
+extern "C" int pylon_static_inject(int pair, unsigned count, int error_code) {
+  unsigned* counters = nullptr;
+  int* error = nullptr;
+  if (static_scratch_address(&counters, &error) == nullptr) return -2;
+  if (pair < 0 || pair >= (int)PYLON_STATIC_COUNTERS) PYLON_REFUSE("pylon_static_inject: counter %d of %u", pair, PYLON_STATIC_COUNTERS);
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err == cudaSuccess) err = cudaMemcpy(counters + pair, &count, sizeof(unsigned), cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = cudaMemcpy(error, &error_code, sizeof(int), cudaMemcpyHostToDevice);
+  if (err != cudaSuccess) {
+    snprintf(pylon::last_error_buffer(), 512, "pylon_static_inject: %s", cudaGetErrorString(err));
+    return -2;
+  }
+  return 0;
 }
 
 extern "C" int pylon_paged_attention_mma_static(const void* q, long long q_stride, const void* k_pages, const void* v_pages,

@@ -36,4 +36,11 @@ long long pylon_static_scratch_floats();
 // 0, or non-zero after a kernel of an earlier call on the current device gave up waiting for one of
 // its TMA copies (that call's output is void); -1 if the word cannot be read.  Synchronises the device.
 int pylon_static_error_word();
+
+// Zeroes the built-in counters and the error word of the current device (after the word was non-zero, before the
+// next call).  Synchronises the device; allocates nothing.  0, or -2 with an error text.
+int pylon_static_reset();
+
+// For tests of the error handling: writes one counter and the error word from the host.
+int pylon_static_inject(int pair, unsigned count, int error_code);
 }

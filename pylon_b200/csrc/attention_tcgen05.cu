@@ -243,6 +243,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         const int key0 = (first_tile + t) * FA_BN;
         const int page = table[key0 / p.page_size];
         const bool page_ok = page >= 0 && page < p.num_pages;
+        if (page < -1 || page >= p.num_pages) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // a broken table; -1 is "no page" (behind a window)
         const int y = page_ok ? (page * p.nkv + kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
         unsigned char* dst = stages + stage * FA_STAGE_BYTES;
         // The keys' half of a stage is free as soon as its scores are computed, a whole tile before the values' half.
@@ -509,7 +510,8 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   if (!error) PYLON_REFUSE("paged_attention_tcgen05: an error word is needed");
   const long long pool_rows = (long long)num_pages * nkv * page_size;
   if (pool_rows >= 2147483647LL - FA_BN) PYLON_REFUSE("paged_attention_tcgen05: the page pool has too many rows for a tensor map coordinate");
-  static bool configured = false;
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM);
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_tcgen05: %s", cudaGetErrorString(err));

@@ -13,10 +13,32 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+// Codes a kernel leaves in the error word it is given (0: all is well).  1 to 4: a bounded wait of the kernel ran out
+// or its shared memory was not where it must be (each kernel's own meaning).
+#define PYLON_ERROR_BAD_PAGE 5   // a block table named a page that the pool does not have: nothing was read or written there
 #define PYLON_DTYPE_F32 0
 #define PYLON_DTYPE_BF16 1
 
 namespace pylon {
+
+// What a library sets up once per device (function attributes, occupancy figures) is kept in small arrays indexed
+// by the current device's number.
+constexpr int MAX_DEVICES = 64;
+inline int current_device_slot() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0) device = 0;
+  return device % MAX_DEVICES;
+}
+// Multiprocessors of the current device (asked once per device): grid-stride kernels size their grids by it.
+inline int multiprocessors() {
+  static int counts[MAX_DEVICES] = {};
+  int& count = counts[current_device_slot()];
+  if (count == 0) {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) == cudaSuccess && cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) count = value;
+  }
+  return count > 0 ? count : 1;
+}
 
 // Text of the last refused call in this thread's library.
 inline char* last_error_buffer() {

@@ -16,13 +16,13 @@ namespace pylon {
 // -----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int width, int vocab) {
+                                    float* __restrict__ out, int width, int vocab, float scale) {
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host
   const T* row = table + (size_t)id * width;
   float* dst = out + (size_t)t * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float<T>(row[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float<T>(row[i]) * scale;   // scale is 1 for models that take the table as it is: exact
 }
 
 // -----------------------------------------------------------------------------------------
@@ -181,7 +181,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     int rotary_dim, int table_positions, const int* __restrict__ positions,
     const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width,
     int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
-    int d, int num_tokens) {
+    int d, int num_tokens, int* __restrict__ error) {
   extern __shared__ float exchange[];  // [warps per block][d]
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
@@ -198,7 +198,10 @@ __global__ void qk_norm_rope_kv_write_kernel(
   if (head >= nq) {
     const int row = token_row[t];
     const int page = block_table[(size_t)row * table_width + pos / page_size];
-    if (page < 0 || page >= num_pages) return;  // never for a prepared step; keeps memory safe
+    if (page < 0 || page >= num_pages) {   // never for a prepared step: nothing is written, and the host is told
+      if (lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
+      return;
+    }
     const int kv_head = (head - nq) % nkv;
     T* pages = head < nq + nkv ? k_pages : v_pages;
     page_dst = pages + (((size_t)page * nkv + kv_head) * page_size + pos % page_size) * d;
@@ -351,7 +354,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     const int* __restrict__ positions, const int* __restrict__ token_row, const int* __restrict__ block_table,
     int table_width, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv,
-    int num_tokens) {
+    int num_tokens, int* __restrict__ error) {
   constexpr int d = CHUNK * 32, half = d / 2;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -368,7 +371,8 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   if (head_begin + HPW > nq) {   // a key or value head among them
     const int row = token_row[t];
     const int page = block_table[(size_t)row * table_width + pos / page_size];
-    page_ok = page >= 0 && page < num_pages;   // always for a prepared step; keeps memory safe
+    page_ok = page >= 0 && page < num_pages;   // always for a prepared step: else nothing is written, and the host is told
+    if (!page_ok && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
     page_offset = ((size_t)(page_ok ? page : 0) * nkv * page_size + pos % page_size) * d + lane * CHUNK;
   }
   float c[CHUNK], s[CHUNK];
@@ -444,7 +448,7 @@ __global__ void __launch_bounds__(128, 5) qk_norm_rope_kv_write_wide_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
     const int* __restrict__ positions, const int* __restrict__ token_row, const int* __restrict__ block_table,
     int table_width, int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int num_pages,
-    int nq, int nkv, int num_tokens) {
+    int nq, int nkv, int num_tokens, int* __restrict__ error) {
   constexpr int LANES = D / 16, HEADS_PER_PASS = 32 / LANES, HALF = D / 2, PER_WARP = HEADS_PER_PASS * PASSES;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -461,7 +465,8 @@ __global__ void __launch_bounds__(128, 5) qk_norm_rope_kv_write_wide_kernel(
   if (head_begin + PER_WARP > nq) {   // a key or value head among them
     const int row = token_row[t];
     const int page = block_table[(size_t)row * table_width + pos / page_size];
-    page_ok = page >= 0 && page < num_pages;   // always for a prepared step; keeps memory safe
+    page_ok = page >= 0 && page < num_pages;   // always for a prepared step: else nothing is written, and the host is told
+    if (!page_ok && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
     page_offset = ((size_t)(page_ok ? page : 0) * nkv * page_size + pos % page_size) * D;
   }
   float c[8], s[8];
@@ -600,15 +605,35 @@ __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* _
 
 using namespace pylon;
 
+// y = x * scale, then (cap > 0) y = cap * tanh(y / cap): what some architectures do to their logits.
+__global__ void logit_transform_kernel(float* __restrict__ logits, size_t n, float scale, float cap) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float y = logits[i] * scale;
+    if (cap > 0.f) y = cap * tanhf(y / cap);
+    logits[i] = y;
+  }
+}
+
+extern "C" int pylon_logit_transform(float* logits, long long n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const long long most = (long long)pylon::multiprocessors() * 16;
+  const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
+  logit_transform_kernel<<<blocks, threads, 0, stream>>>(logits, (size_t)n, scale, cap);
+  PYLON_CHECK_LAUNCH("logit_transform");
+}
+
 extern "C" int pylon_embed_gather(const int* ids, const void* table, float* out, int num_tokens, int width,
-                                  int vocab, int dtype, cudaStream_t stream) {
+                                  int vocab, int dtype, float scale, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (width <= 0 || vocab <= 0) PYLON_REFUSE("embed_gather: width %d, vocab %d", width, vocab);
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == PYLON_DTYPE_F32)
-    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab);
+    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, scale);
   else if (dtype == PYLON_DTYPE_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab);
+    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, scale);
   else
     PYLON_REFUSE("embed_gather: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("embed_gather");
@@ -650,7 +675,8 @@ extern "C" int pylon_add_parts_rmsnorm(float* residual, const float* delta_parts
 extern "C" int pylon_residual_add(float* residual, const void* delta, long long n, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = 256;
-  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  const long long most = (long long)pylon::multiprocessors() * 16;
+  const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
   if (dtype == PYLON_DTYPE_F32)
     residual_add_kernel<float><<<blocks, threads, 0, stream>>>(residual, (const float*)delta, (size_t)n);
   else if (dtype == PYLON_DTYPE_BF16)
@@ -665,7 +691,7 @@ static int launch_qk_norm_rope(T* qkv, const float* qkv_parts, int parts, long l
                                const float* sin_t, int rotary_dim, int table_positions, const int* positions,
                                const int* token_row, const int* block_table, int table_width, int page_size,
                                T* k_pages, T* v_pages, int num_pages, int nq, int nkv, int d, int num_tokens,
-                               cudaStream_t stream) {
+                               int* error, cudaStream_t stream) {
   const int warps = 4;
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
   const int blocks = (int)((items + warps - 1) / warps);
@@ -688,7 +714,7 @@ static int launch_qk_norm_rope(T* qkv, const float* qkv_parts, int parts, long l
 #define PYLON_LAUNCH_QK_WIDE(D_)                                                                                              \
         launch_dependent(qk_norm_rope_kv_write_wide_kernel<D_, PASSES>, dim3(wide_blocks), dim3(warps * 32), 0, stream, qkv, qw, kw, eps, \
                          cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages,   \
-                         v_pages, num_pages, nq, nkv, num_tokens)
+                         v_pages, num_pages, nq, nkv, num_tokens, error)
         if (d == 64) PYLON_LAUNCH_QK_WIDE(64);
         else if (d == 128) PYLON_LAUNCH_QK_WIDE(128);
         else PYLON_LAUNCH_QK_WIDE(256);
@@ -705,11 +731,11 @@ static int launch_qk_norm_rope(T* qkv, const float* qkv_parts, int parts, long l
       if (many)                                                                                                           \
         launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 4>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qkv_parts, parts, part_stride, q_out, qw, kw, eps,  \
                          cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
-                         v_pages, num_pages, nq, nkv, num_tokens);                                                         \
+                         v_pages, num_pages, nq, nkv, num_tokens, error);                                                  \
       else                                                                                                                \
         launch_dependent(qk_norm_rope_kv_write_vec_kernel<T, C, 1>, dim3(vec_blocks), dim3(warps * 32), 0, stream, qkv, qkv_parts, parts, part_stride, q_out, qw, kw, eps,  \
                          cos_used, sin_t, table_positions, positions, token_row, block_table, table_width, page_size, k_pages, \
-                         v_pages, num_pages, nq, nkv, num_tokens);                                                         \
+                         v_pages, num_pages, nq, nkv, num_tokens, error);                                                  \
     } while (0)
     if (d == 64) PYLON_LAUNCH_QK_VEC(2);
     else if (d == 128) PYLON_LAUNCH_QK_VEC(4);
@@ -720,7 +746,7 @@ static int launch_qk_norm_rope(T* qkv, const float* qkv_parts, int parts, long l
 #define PYLON_LAUNCH_QK(N)                                                                              \
   launch_dependent(qk_norm_rope_kv_write_kernel<T, N>, dim3(blocks), dim3(warps * 32), smem, stream,    \
       qkv, qw, kw, eps, cos_t, sin_t, rotary_dim, table_positions, positions, token_row, block_table,   \
-      table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, num_tokens)
+      table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, num_tokens, error)
   if (d <= 32) PYLON_LAUNCH_QK(1);
   else if (d <= 64) PYLON_LAUNCH_QK(2);
   else if (d <= 128) PYLON_LAUNCH_QK(4);
@@ -735,7 +761,7 @@ extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, con
                                            int table_positions, const int* positions, const int* token_row,
                                            const int* block_table, int table_width, int page_size,
                                            void* k_pages, void* v_pages, int num_pages, int nq, int nkv, int d,
-                                           int num_tokens, int dtype, cudaStream_t stream) {
+                                           int num_tokens, int dtype, int* error, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (d < 2 || d > 512) PYLON_REFUSE("qk_norm_rope_kv_write: head size %d is outside 2..512", d);
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1))
@@ -745,12 +771,12 @@ extern "C" int pylon_qk_norm_rope_kv_write(void* qkv, const float* q_weight, con
   if (dtype == PYLON_DTYPE_F32)
     return launch_qk_norm_rope<float>((float*)qkv, nullptr, 0, 0, nullptr, q_weight, k_weight, eps, cos_table, sin_table, rotary_dim,
                                       table_positions, positions, token_row, block_table, table_width, page_size,
-                                      (float*)k_pages, (float*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
+                                      (float*)k_pages, (float*)v_pages, num_pages, nq, nkv, d, num_tokens, error, stream);
   if (dtype == PYLON_DTYPE_BF16)
     return launch_qk_norm_rope<__nv_bfloat16>((__nv_bfloat16*)qkv, nullptr, 0, 0, nullptr, q_weight, k_weight, eps, cos_table, sin_table,
                                               rotary_dim, table_positions, positions, token_row, block_table,
                                               table_width, page_size, (__nv_bfloat16*)k_pages,
-                                              (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, num_tokens, stream);
+                                              (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, num_tokens, error, stream);
   PYLON_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
 }
 
@@ -788,7 +814,7 @@ extern "C" int pylon_qk_norm_rope_kv_write_parts(const float* qkv_parts, int par
                                                  int table_positions, const int* positions, const int* token_row,
                                                  const int* block_table, int table_width, int page_size, void* k_pages,
                                                  void* v_pages, int num_pages, int nq, int nkv, int d, int num_tokens,
-                                                 cudaStream_t stream) {
+                                                 int* error, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (!qkv_parts || parts < 1 || !q_out) PYLON_REFUSE("qk_norm_rope_kv_write_parts: %d parts", parts);
   if (nq < 0 || nkv < 1 || page_size < 1 || table_width < 1)
@@ -797,7 +823,7 @@ extern "C" int pylon_qk_norm_rope_kv_write_parts(const float* qkv_parts, int par
   return launch_qk_norm_rope<__nv_bfloat16>(nullptr, qkv_parts, parts, (long long)num_tokens * (nq + 2 * nkv) * d, (__nv_bfloat16*)q_out, q_weight,
                                             k_weight, eps, cos_table, sin_table, rotary_dim, table_positions, positions, token_row, block_table,
                                             table_width, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d,
-                                            num_tokens, stream);
+                                            num_tokens, error, stream);
 }
 
 extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int interleaved, int dtype,
@@ -807,7 +833,8 @@ extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int 
   if (interleaved && inter % 8) PYLON_REFUSE("swiglu: the interleaved layout needs an intermediate size that is a multiple of 8, not %d", inter);
   const size_t total = (size_t)num_tokens * inter;
   const int threads = 256;
-  auto grid = [&](size_t n) { size_t b = (n + threads - 1) / threads; return (int)(b < 148 * 32 ? b : 148 * 32); };
+  const size_t most = (size_t)pylon::multiprocessors() * 32;
+  auto grid = [&](size_t n) { size_t b = (n + threads - 1) / threads; return (int)(b < most ? b : most); };
   if (dtype == PYLON_DTYPE_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
     launch_dependent(swiglu_bf16x8_kernel, dim3(grid(total / 8)), dim3(threads), 0, stream, (const uint4*)gate_up, (uint4*)out, inter / 8, total / 8, interleaved);
   } else if (dtype == PYLON_DTYPE_BF16) {

@@ -170,7 +170,8 @@ static int launch_skinny(const __nv_bfloat16* x, const __nv_bfloat16* w, OutT* y
   constexpr size_t smem = (size_t)WARPS * NT * 16 * MT * 8 * sizeof(float);
   auto kernel = gemm_skinny_kernel<MT, NT, WARPS, UNROLL, OutT>;
   if (smem > 48 * 1024) {
-    static bool configured = false;
+    static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
     if (!configured) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (err != cudaSuccess) PYLON_REFUSE("gemm_skinny: %s", cudaGetErrorString(err));

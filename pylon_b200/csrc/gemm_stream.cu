@@ -237,7 +237,8 @@ template <int MT, int FORM>
 static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, void* y, int M, int N, int K, long long ldy, int parts, int slabs,
                          int* error, cudaStream_t stream) {
   auto kernel = gemm_stream_kernel<MT, FORM>;
-  static bool configured = false;
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamRing<MT>::SMEM);
     if (err != cudaSuccess) PYLON_REFUSE("gemm_stream: %s", cudaGetErrorString(err));

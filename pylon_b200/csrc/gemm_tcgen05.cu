@@ -322,7 +322,8 @@ template <int BN, bool SWIGLU>
 static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __nv_bfloat16* c, int M, int N, int K, long long ldc,
                           int* error, int sm_count, cudaStream_t stream) {
   auto kernel = gemm_tcgen05_kernel<BN, SWIGLU>;
-  static bool configured = false;
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShared<BN>::BYTES);
     if (err != cudaSuccess) PYLON_REFUSE("gemm_tcgen05: %s", cudaGetErrorString(err));

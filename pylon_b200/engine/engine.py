@@ -17,7 +17,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from pylon_b200.cache.manager import CacheManager, RequestCache
+from pylon_b200.cache.manager import CacheManager, RequestCache, group_page_counts
 from pylon_b200.config.engine_config import EngineConfig
 from pylon_b200.config.registry import ARCHITECTURES, read_config
 from pylon_b200.engine.scheduler import GenerationResult, Scheduler
@@ -82,42 +82,54 @@ class Engine:
             needs = self.model.cache_needs()
             cache_of = [run.cache_of for run in self.spec.order]
             page_size = self.config.page_size
-            num_pages = self._pool_pages(needs, dtype, page_size)
+            page_counts = self._pool_pages(needs, dtype, page_size)
             self.cache = CacheManager(
-                needs, cache_of, page_size=page_size, num_pages=num_pages,
+                needs, cache_of, page_size=page_size, num_pages=page_counts,
                 max_requests=self.config.max_batch_size, dtype=dtype, device=self.device,
             )
-        self.max_context = min(self.spec.max_positions, num_pages * page_size)
+        # a request can be as long as the groups that keep every key have room for
+        keeps_all = [group.pool.num_pages * page_size for group in self.cache.groups if group.need.window is None]
+        self.max_context = min([self.spec.max_positions] + keeps_all)
         self.step_function = StepFunction(self.model, self.cache)
         if self.config.cuda_graphs:
             self.step_function.enable_graphs()
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(
-            self.cache, self.step_function, self.sampler,
+            self.cache, self._checked_step, self._checked_sample,
             max_batch_size=self.config.max_batch_size, prefill_chunk_size=self.config.prefill_chunk_size,
             max_queue_size=self.config.max_queue_size, admit_skip=self.config.admit_skip, seed=self.config.seed,
         )
         self._next_id = 0
 
     # -- sizing ----------------------------------------------------------------------------
-    def _pool_pages(self, needs, dtype: torch.dtype, page_size: int) -> int:
+    def _pool_pages(self, needs, dtype: torch.dtype, page_size: int) -> dict:
+        """Pages for every cache group (by its :class:`~pylon_b200.parts.base.KVNeed`).  With ``max_cache_tokens`` the
+        pool holds that many tokens; else it takes what is left of the allowed share of the device after the weights,
+        less room for the activations of one full step (raun6k/Pylon sizes its pool the same way,
+        src/pylon/kv/budget.py:70-113).  A windowed group is given only what ``max_batch_size`` requests can hold of it
+        at once, and the groups that keep everything share the rest."""
+        slots, chunk, longest = self.config.max_batch_size, self.config.prefill_chunk_size, self.spec.max_positions
         if self.config.max_cache_tokens is not None:
-            return max(1, math.ceil(self.config.max_cache_tokens / page_size))
+            return group_page_counts(needs, page_size, self.config.max_cache_tokens, slots, longest, chunk)
         element = torch.empty((), dtype=dtype).element_size()
-        per_token = sum(2 * need.kv.n_kv_heads * need.kv.head_dim * element for need in needs if need is not None and need.kv is not None)
+        most = group_page_counts(needs, page_size, longest * slots, slots, longest, chunk)   # what could ever be used
+        page_bytes: dict = {}
+        for need in needs:
+            if need is not None and need.kv is not None:
+                row_bytes = need.kv.n_kv_heads * (need.kv.head_dim + need.kv.value_width) * element
+                page_bytes[need.kv] = page_bytes.get(need.kv, 0) + row_bytes * page_size
+        if not page_bytes:
+            return {}
         free, total = torch.cuda.mem_get_info(self.device)
-        # What is left of the allowed share of the device after the weights, less room for
-        # activations of one full step (raun6k/Pylon sizes its pool the same way,
-        # src/pylon/kv/budget.py:70-113).
-        activation_room = self.config.prefill_chunk_size * self.spec.width * 64
+        activation_room = chunk * self.spec.width * 64
         budget = int(total * self.config.max_gpu_utilization) - (total - free) - activation_room
-        if per_token == 0:
-            return 1
-        pages = budget // (per_token * page_size)
-        limit = math.ceil(self.spec.max_positions / page_size) * self.config.max_batch_size
-        if pages < 1:
+        windowed = {kv: pages for kv, pages in most.items() if kv.window is not None}
+        budget -= sum(pages * page_bytes[kv] for kv, pages in windowed.items())
+        shared = sum(size for kv, size in page_bytes.items() if kv.window is None)
+        pages = budget // shared if shared else 0
+        if budget < 0 or (shared and pages < 1):
             raise RuntimeError("no memory is left for the cache after loading the weights")
-        return int(min(pages, limit))
+        return {kv: (count if kv.window is not None else int(min(pages, count))) for kv, count in most.items()}
 
     # -- the step function, for callers that batch themselves --------------------------------
     def open(self, request_id: object, capacity: int) -> RequestCache:
@@ -178,10 +190,21 @@ class Engine:
             return self._tick()
 
     def _tick(self) -> list[GenerationResult]:
-        results = self.scheduler.tick()
-        # the tick has read its tokens back, so the device is idle: a 16-byte look at the kernels' error words
+        return self.scheduler.tick()
+
+    # What the scheduler calls.  A kernel that gave up one of its bounded waits leaves a void result and an error word;
+    # the words are looked at (a 16-byte read) where the device has just been waited for anyway, and inside the
+    # scheduler's own error handling, so that the requests of a void step fail instead of going on with its tokens.
+    def _checked_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        logits = self.step_function(entries)
+        if logits is None:   # nothing will be sampled from this step: look now
+            ops.raise_on_kernel_errors(self.device)
+        return logits
+
+    def _checked_sample(self, logits, params, randoms) -> list[int]:
+        tokens = self.sampler(logits, params, randoms)   # reads the tokens back: the step is done
         ops.raise_on_kernel_errors(self.device)
-        return results
+        return tokens
 
     def default_stop_ids(self) -> tuple[int, ...]:
         return tuple(self.spec.eos_token_ids)
@@ -223,13 +246,13 @@ class Engine:
     def _validate(self, prompt: Sequence[int], params: SamplingParams) -> None:
         vocab = self.spec.vocab_size
         if len(prompt) < 1:
-            raise ValueError("A request prompt must contain at least one token.")
+            raise ValueError("an empty prompt: a request needs at least one token to start from")
         for token in prompt:
             if isinstance(token, bool) or not isinstance(token, int) or not 0 <= token < vocab:
-                raise ValueError(f"Token IDs must be between 0 and {vocab - 1:,}.")
+                raise ValueError(f"{token!r} is not a token id of this model: ids are whole numbers from 0 to {vocab - 1}")
         needed = len(prompt) + params.max_new_tokens
         if needed > self.max_context:
-            raise ValueError(f"Request needs {needed:,} cache positions, but the engine supports {self.max_context:,}.")
+            raise ValueError(f"prompt plus max_new_tokens is {needed} tokens; this engine was set up for requests of up to {self.max_context}")
 
 
 def generate(

@@ -78,8 +78,11 @@ class DecodeGraphs:
         gc.disable()   # destroying an old graph or a pinned buffer in mid-capture would invalidate it
         try:
             # One eager run first: libraries are built and loaded, kernels configured, the
-            # allocator warmed.  It writes the same cache slots the captured run writes again.
+            # allocator warmed.  It writes the same cache slots the replay writes again; a state
+            # of fixed size, which a second run would advance twice, is put back after it.
+            saved_state = self.cache.save_state([entry.request for entry in entries])
             function.model.forward(step, caches)
+            self.cache.restore_state(saved_state)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launches[0]

@@ -41,9 +41,11 @@ from pylon_b200.sampling.sampler import RequestRandom
 
 logger = logging.getLogger("pylon_b200")   # key=value lines, as raun6k/Pylon logs its scheduler (src/pylon/scheduler/admit.py:16-57)
 
-PREFILL_MAX_WAIT_SECONDS = 0.1
-ADMIT_SKIP_WAIT_SECONDS = 0.1
-FULL_BATCH_PREFILL_WAIT_SECONDS = 0.1
+# How long a request is made to wait by the three policies below before it goes first, in seconds
+# (raun6k/Pylon uses 100 ms for each: src/pylon/scheduler/admit.py:8, src/pylon/scheduler/batch.py:3, src/pylon/engine.py:27).
+ADMISSION_PATIENCE = 0.1     # a waiting request this old is not overtaken at admission
+PROMPT_PATIENCE = 0.1        # a prompt that made no progress for this long gets the next portion
+FULL_BATCH_PATIENCE = 0.1    # with every slot decoding, prompts are held back this long at most
 
 
 class QueueFullError(RuntimeError):
@@ -78,7 +80,7 @@ class Request:
     prompt_offset: int = 0
     pending_token: Optional[int] = None
     output_ids: list[int] = field(default_factory=list)
-    prefill_wait_started: float = 0.0
+    prompt_progress_at: float = 0.0     # when the prompt last got a portion (or was queued)
     admitted_at: float = 0.0
     first_token_at: Optional[float] = None
     last_token_at: Optional[float] = None
@@ -88,6 +90,10 @@ class Request:
     @property
     def capacity(self) -> int:
         return len(self.prompt) + self.sampling.max_new_tokens
+
+    @property
+    def prompt_left(self) -> int:
+        return len(self.prompt) - self.prompt_offset
 
     @property
     def prefilling(self) -> bool:
@@ -130,7 +136,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.active: list[Request] = []
         self.finished: list[GenerationResult] = []
-        self.head_skips = 0
+        self.overtakes = 0    # admissions that passed the oldest waiting request
         self.ticks = 0
         self._submitted = 0
         self.last_step: list[tuple[object, int]] = []   # (request id, tokens) of the last step, for tests and logs
@@ -138,10 +144,10 @@ class Scheduler:
     # -- intake ------------------------------------------------------------------------
     def add(self, request_id: object, prompt: Sequence[int], sampling: SamplingParams, stop_ids: Sequence[int] = ()) -> Request:
         if len(self.waiting) >= self.max_queue_size:
-            raise QueueFullError("The generation waiting queue is full.")
+            raise QueueFullError(f"{len(self.waiting)} requests are waiting already, which is max_queue_size; try again when one has started")
         prompt = [int(t) for t in prompt]
         if not prompt:
-            raise ValueError("A request prompt must contain at least one token.")
+            raise ValueError("an empty prompt: a request needs at least one token to start from")
         capacity = len(prompt) + sampling.max_new_tokens
         needed = self.cache.lifetime_pages(capacity, self.prefill_chunk_size)
         for g, group in enumerate(self.cache.groups):
@@ -192,19 +198,22 @@ class Scheduler:
                 return False
         return True
 
-    def _select_waiting(self, now: float) -> Optional[tuple[Request, bool]]:
-        head = self.waiting[0]
-        if self._fits(head):
-            return head, False
-        if now - head.enqueued_at >= ADMIT_SKIP_WAIT_SECONDS or self.admit_skip <= 0:
-            return None
-        skips = 0
-        for request in list(self.waiting)[1:]:
+    def _next_admission(self, now: float) -> Optional[tuple[Request, bool]]:
+        """The waiting request that may start now and whether it overtakes the oldest one, or ``None``.
+
+        The queue is walked from its oldest request: the first that fits goes.  The walk ends at a
+        request that does not fit and has run out of patience (nobody overtakes it), and after
+        ``admit_skip`` younger requests that did not fit either."""
+        passed_over = 0
+        for place, request in enumerate(self.waiting):
             if self._fits(request):
-                return request, True
-            if now - request.enqueued_at >= ADMIT_SKIP_WAIT_SECONDS or skips >= self.admit_skip:
+                return request, place > 0
+            if now - request.enqueued_at >= ADMISSION_PATIENCE:
                 return None
-            skips += 1
+            if place > 0:
+                passed_over += 1
+            if passed_over > self.admit_skip or self.admit_skip == 0:
+                return None
         return None
 
     def admit(self) -> None:
@@ -212,51 +221,52 @@ class Scheduler:
             logger.debug("admission_blocked request_id=%s reason=slots", self.waiting[0].request_id)
         while self.waiting and len(self.active) < self.max_batch_size:
             now = self.clock()
-            selected = self._select_waiting(now)
+            selected = self._next_admission(now)
             if selected is None:
                 logger.debug("admission_blocked request_id=%s reason=memory", self.waiting[0].request_id)
                 return
-            request, skipped_head = selected
+            request, overtakes = selected
             self.waiting.remove(request)
             request.cache = self.cache.open(request.request_id, request.capacity)
             request.reservation = self.cache.lifetime_pages(request.capacity, self.prefill_chunk_size)
             request.admitted_at = now
-            request.prefill_wait_started = request.enqueued_at
+            request.prompt_progress_at = request.enqueued_at
             self.active.append(request)
-            if skipped_head:
-                self.head_skips += 1
-                logger.info("admission_skipped_head request_id=%s admitted=%s head_skips=%s", self.waiting[0].request_id, request.request_id, self.head_skips)
+            if overtakes:
+                self.overtakes += 1
+                logger.info("admission_overtook request_id=%s admitted=%s overtakes=%s", self.waiting[0].request_id, request.request_id, self.overtakes)
 
     # -- building a step -------------------------------------------------------------------
-    def _choose_prefill(self, pending: list[Request], budget: int, now: float) -> Request:
-        aged = [r for r in pending if now - r.prefill_wait_started >= PREFILL_MAX_WAIT_SECONDS]
-        if aged:
-            return min(aged, key=lambda r: r.prefill_wait_started)
-        fitting = [r for r in pending if len(r.prompt) - r.prompt_offset <= budget]
-        return (fitting or pending)[0]
+    def _portion_rank(self, request: Request, budget: int, now: float) -> tuple[int, float]:
+        """Sort key of a prompt that waits for its next portion (the smallest goes first): prompts out of
+        patience before all others, the longest wait first; then those whose rest fits the budget, so that
+        they begin to decode; then the rest.  Equal keys keep the order of admission."""
+        stalled = now - request.prompt_progress_at
+        if stalled >= PROMPT_PATIENCE:
+            return (0, -stalled)
+        return (1, 0.0) if request.prompt_left <= budget else (2, 0.0)
 
-    def _prefill_portions(self, now: float) -> list[tuple[Request, list[int]]]:
-        pending = [r for r in self.active if r.prefilling]
-        chosen = []
+    def _cut_portions(self, now: float) -> list[tuple[Request, list[int]]]:
+        """Portions of the waiting prompts for this tick: at most ``prefill_chunk_size`` tokens in all, cut anywhere."""
+        candidates = [request for request in self.active if request.prefilling]
+        portions = []
         budget = self.prefill_chunk_size
-        while pending and budget > 0:
-            request = self._choose_prefill(pending, budget, now)
-            pending.remove(request)
-            count = min(budget, len(request.prompt) - request.prompt_offset)
-            chosen.append((request, request.prompt[request.prompt_offset : request.prompt_offset + count]))
-            budget -= count
-        return chosen
+        while candidates and budget > 0:
+            request = min(candidates, key=lambda candidate: self._portion_rank(candidate, budget, now))
+            candidates.remove(request)
+            begin = request.prompt_offset
+            size = min(budget, request.prompt_left)
+            portions.append((request, request.prompt[begin : begin + size]))
+            budget -= size
+        return portions
 
     def build_step(self) -> tuple[list[Request], list[list[int]]]:
         now = self.clock()
         decoding = [r for r in self.active if r.pending_token is not None]
-        waiting_prompts = [r.prefill_wait_started for r in self.active if r.prefilling]
-        hold_off = (
-            len(decoding) == self.max_batch_size
-            and waiting_prompts
-            and now - min(waiting_prompts) < FULL_BATCH_PREFILL_WAIT_SECONDS
-        )
-        portions = [] if hold_off else self._prefill_portions(now)
+        stalled_since = [r.prompt_progress_at for r in self.active if r.prefilling]
+        # every slot decodes: prompts wait, so that the step stays a graph replay, until the oldest runs out of patience
+        hold_off = len(decoding) == self.max_batch_size and stalled_since and now - min(stalled_since) < FULL_BATCH_PATIENCE
+        portions = [] if hold_off else self._cut_portions(now)
         selected = decoding + [request for request, _ in portions]
         chunks = [[r.pending_token] for r in decoding] + [tokens for _, tokens in portions]
         return selected, chunks
@@ -306,7 +316,7 @@ class Scheduler:
         for request, chunk in zip(selected, chunks):
             if request.pending_token is None:
                 request.prompt_offset += len(chunk)
-                request.prefill_wait_started = now
+                request.prompt_progress_at = now
                 request.prefill_seconds += elapsed
             else:
                 request.inter_token_seconds.append(elapsed)

@@ -160,11 +160,14 @@ class StepFunction:
         """Runs the step; returns logits ``[wanted, vocab]`` in the order of the entries and of
         their ``want`` lists, or ``None`` if nothing is wanted.  The cache is advanced only
         after every launch was enqueued; if preparing or launching fails, the requests hold
-        what they held before."""
+        what they held before: their pages, and (where a mixer keeps a state of fixed size) a
+        copy of their state slots taken before the first launch."""
         self.validate(entries)
         batch = [(entry.request, len(entry.tokens)) for entry in entries]
         self.cache.prepare(batch)          # all pages of the step, or OutOfPages and nothing
+        saved_state = None
         try:
+            saved_state = self.cache.save_state([request for request, _ in batch])   # None for models without state
             logits = None
             if self.graphs is not None and self.graphs.applies(entries):
                 logits = self.graphs.run(entries)
@@ -173,6 +176,7 @@ class StepFunction:
         except BaseException:
             for request, _ in batch:
                 self.cache.rollback(request)
+            self.cache.restore_state(saved_state)
             raise
         for request, _ in batch:
             self.cache.commit(request)

@@ -71,43 +71,76 @@ def _check(library: ctypes.CDLL, code: int) -> None:
 # Kernels that wait on mbarriers (TMA copies, tensor-core completion) bound every wait; one that
 # runs out sets its word here instead of hanging, and the result of that launch is void.  One
 # tensor per device: [tcgen05 product, attention, TMA-fed decode product, unused].
-_error_word_storage: dict[str, torch.Tensor] = {}
-_ERROR_WORD_NAMES = ("tcgen05 product", "attention", "TMA-fed decode product")
+_error_word_storage: dict[int, torch.Tensor] = {}
+_ERROR_WORD_NAMES = ("tcgen05 product", "attention", "TMA-fed decode product", "cache write")
+BAD_PAGE_CODE = 5   # PYLON_ERROR_BAD_PAGE of csrc/common.cuh: a block table named a page that the pool does not have
+
+
+def _device_index(device: torch.device | str) -> int:
+    """``cuda`` and ``cuda:N`` name the same device when N is the current one: buffers kept per device go by the number."""
+    device = torch.device(device)
+    return torch.cuda.current_device() if device.index is None else device.index
+
+
+def _multiprocessors(device: torch.device | str) -> int:
+    """How many multiprocessors ``device`` has (asked once): grids, splits and tile choices are sized by it."""
+    index = _device_index(device)
+    if index not in _multiprocessor_counts:
+        _multiprocessor_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _multiprocessor_counts[index]
+
+
+_multiprocessor_counts: dict[int, int] = {}
 
 
 def _error_words(device: torch.device) -> torch.Tensor:
-    key = str(device)
+    key = _device_index(device)
     if key not in _error_word_storage:
-        _error_word_storage[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _error_word_storage[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _error_word_storage[key]
+
+
+def cache_write_error_word(device: torch.device) -> torch.Tensor:
+    """The int32 word the kernel that writes new keys and values into their pages sets when the block
+    table names a page the pool does not have (nothing is written there).  Zero in every healthy run."""
+    return _error_words(device)[3:4]
 
 
 def raise_on_kernel_errors(device: torch.device) -> None:
     """Reads the error words of ``device`` (a 16-byte copy that waits for the work queued so
-    far) and raises if a kernel gave up one of its bounded waits since the last call; the
-    words are cleared, so the next call reports only what happens from now on."""
-    key = str(device)
+    far) and raises if, since the last call, a kernel gave up one of its bounded waits or met a
+    block table that names a page outside the pool.  The words are cleared, so the next call
+    reports only what happens from now on; and the counters by which the blocks of a decode
+    attention find the last of them are put back to zero, since a block that gave up never
+    took part in the count of the rows it shared, and the next launch must find zeros."""
+    key = _device_index(device)
     if key not in _error_word_storage:
         return   # no kernel that can set them has run
     words = _error_word_storage[key].cpu().tolist()
     if any(words):
         _error_word_storage[key].zero_()
-        what = ", ".join(f"{name} (code {code})" for name, code in zip(_ERROR_WORD_NAMES, words) if code)
-        raise KernelError(f"a bounded wait ran out in: {what}; the results of that step are void")
+        for (index, _purpose), buffer in _counter_buffers.items():
+            if index == key:
+                buffer.zero_()
+        what = ", ".join(
+            f"{name} ({'a block table names a page outside the pool' if code == BAD_PAGE_CODE else 'a bounded wait ran out'}, code {code})"
+            for name, code in zip(_ERROR_WORD_NAMES, words) if code)
+        raise KernelError(f"kernel error in: {what}; the results of that step are void")
 
 
 _SIGNATURES = {
     "elementwise.cu": {
-        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "pylon_logit_transform": [c_void_p, c_longlong, c_float, c_float, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "pylon_residual_add": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
         "pylon_add_parts_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "pylon_qk_norm_rope_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                        c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "pylon_qk_norm_rope_kv_write_parts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                              c_int, c_void_p],
+                                              c_int, c_void_p, c_void_p],
         "pylon_qk_norm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -181,8 +214,8 @@ def build_all() -> list[str]:
 # ---------------------------------------------------------------------------------------
 # embedding, norms, residual
 # ---------------------------------------------------------------------------------------
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``."""
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``, times ``scale``."""
     _need_cuda(ids, table, out)
     _need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), "embed_gather: ids must be contiguous int32 [T]")
     _need(table.dim() == 2 and table.is_contiguous(), "embed_gather: table must be contiguous [vocab, width]")
@@ -191,8 +224,18 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
         out = torch.empty((tokens, width), dtype=torch.float32, device=table.device)
     _need(out.dtype == torch.float32 and out.shape == (tokens, width) and out.is_contiguous(), "embed_gather: out must be contiguous float32 [T, width]")
     library = _library("elementwise.cu")
-    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), _stream()))
+    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), _stream()))
     return out
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
+    """In place on float32 ``logits``: ``y = x * scale``, then with a ``softcap`` c: ``y = c * tanh(y / c)``."""
+    _need_cuda(logits)
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logit_transform: logits must be contiguous float32")
+    _need(softcap is None or softcap > 0, "logit_transform: a soft cap must be positive")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_logit_transform(_ptr(logits), logits.numel(), float(scale), float(softcap or 0.0), _stream()))
+    return logits
 
 
 def add_rmsnorm(
@@ -305,12 +348,12 @@ def qk_norm_rope_kv_write(
         _check(library, library.pylon_qk_norm_rope_kv_write_parts(
             _ptr(qkv), qkv.shape[0], _ptr(q), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
             _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
-            k_pages.shape[0], nq, nkv, head_dim, tokens, _stream()))
+            k_pages.shape[0], nq, nkv, head_dim, tokens, _ptr(cache_write_error_word(k_pages.device)), _stream()))
         return q
     _check(library, library.pylon_qk_norm_rope_kv_write(
         _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim, table_positions,
         _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
-        k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _stream()))
+        k_pages.shape[0], nq, nkv, head_dim, tokens, _dtype_code(qkv.dtype), _ptr(cache_write_error_word(k_pages.device)), _stream()))
     return qkv
 
 
@@ -380,22 +423,22 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
         return linear_skinny(x, w, out_dtype)   # few rows (decode): our weight-streaming kernel
     if out_dtype == torch.bfloat16:
-        if _tcgen05_fills_the_sms(m, n) and k % 8 == 0 and n % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
+        if _tcgen05_fills_the_sms(m, n, _multiprocessors(x.device)) and k % 8 == 0 and n % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
             return linear_tcgen05(x, w)
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
 
 
-def _tcgen05_fills_the_sms(m: int, n: int) -> bool:
+def _tcgen05_fills_the_sms(m: int, n: int, sms: int) -> bool:
     """Whether a persistent block per SM over 128 x 256 tiles wastes under a fifth of its
     rounds: there our kernel is level with the library's, elsewhere the library (which
     splits such products differently) is ahead."""
     if m < TCGEN05_MIN_ROWS:
         return False
     tiles = -(-m // 128) * -(-n // 256)
-    rounds = -(-tiles // _SM_COUNT)
-    return tiles >= 0.8 * rounds * _SM_COUNT
+    rounds = -(-tiles // sms)
+    return tiles >= 0.8 * rounds * sms
 
 
 STREAM_MAX_ROWS = 32   # up to this many rows the TMA-fed kernel beats the library (it takes up to 64)
@@ -451,7 +494,7 @@ def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int]
     n = w.shape[0]
     slabs, k_boxes = -(-n // 64), -(-k // 64)
     if parts is None:
-        parts = max(1, min(STREAM_MAX_PARTS, k_boxes, (3 * _SM_COUNT) // slabs))
+        parts = max(1, min(STREAM_MAX_PARTS, k_boxes, (3 * _multiprocessors(x.device)) // slabs))
     y = torch.empty((parts, m, n), dtype=torch.float32, device=x.device)
     library = _library("gemm_stream.cu")
     _check(library, library.pylon_gemm_stream_partial(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), parts,
@@ -518,7 +561,7 @@ def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> to
     y = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
     library = _library("gemm_tcgen05.cu")
     _check(library, library.pylon_gemm_tcgen05_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), int(swiglu),
-                                                    _ptr(tcgen05_error_word(x.device)), _SM_COUNT, _stream()))
+                                                    _ptr(tcgen05_error_word(x.device)), _multiprocessors(x.device), _stream()))
     return y
 
 # Small integer buffers kernels use to find out which of their blocks finishes last.  They
@@ -528,12 +571,17 @@ _counter_buffers: dict[tuple, torch.Tensor] = {}
 
 
 def _zeroed_counters(device: torch.device, purpose: str, count: int) -> torch.Tensor:
-    key = (str(device), purpose)
+    key = (_device_index(device), purpose)
     buffer = _counter_buffers.get(key)
     if buffer is None or buffer.numel() < count:
+        if buffer is not None:
+            _retired_counter_buffers.append(buffer)   # a captured graph may still hold its address
         buffer = torch.zeros(max(count, 1 << 16), dtype=torch.int32, device=device)
         _counter_buffers[key] = buffer
     return buffer
+
+
+_retired_counter_buffers: list[torch.Tensor] = []
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -572,9 +620,9 @@ def attention_error_word(device: torch.device) -> torch.Tensor:
     return _error_words(device)[1:2]
 
 
-def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int) -> int:
+def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: int, sms: int) -> int:
     """How many key/value splits the tiled attention kernel uses for rows with more than 16
-    packed query rows (tokens x group).
+    packed query rows (tokens x group), on a device with ``sms`` multiprocessors.
 
     Steps with long rows (prefill) have enough query tiles to fill the GPU and use one; a few
     short portions over a long context are split so that two blocks per SM have work.  Rows
@@ -584,12 +632,9 @@ def attention_splits(num_rows: int, nkv: int, group: int, max_q: int, max_kv: in
         return 1
     kv_tiles = max(1, -(-max_kv // 64))
     blocks = num_rows * nkv * -(-max_q * group // 64)
-    if blocks >= _SM_COUNT or kv_tiles == 1:
+    if blocks >= sms or kv_tiles == 1:
         return 1
-    return int(max(1, min(kv_tiles, 64, 2 * _SM_COUNT // blocks)))
-
-
-_SM_COUNT = 148
+    return int(max(1, min(kv_tiles, 64, 2 * sms // blocks)))
 
 
 def paged_attention(
@@ -683,7 +728,7 @@ def paged_attention(
                 _ptr(attention_error_word(q.device)), _stream()))
             if not maybe_small:
                 return out
-        splits = 1 if use_tcgen05 else (attention_splits(rows, nkv, group, max_q, max_kv) if num_splits is None else int(num_splits))
+        splits = 1 if use_tcgen05 else (attention_splits(rows, nkv, group, max_q, max_kv, _multiprocessors(q.device)) if num_splits is None else int(num_splits))
         blocks = 0
         if maybe_small:
             blocks = library.pylon_attention_decode_blocks() if decode_blocks is None else int(decode_blocks)

@@ -4,7 +4,8 @@ Embedding, the layers in their run order, final norm and vocabulary head.  The c
 no architecture: which parts a layer has, their sizes and the order of the runs all come
 from the spec.  The data flow is raun6k/Pylon's packed forward
 (src/pylon/model/model.py:124-144): embed, blocks, then norm and head only at the rows
-whose logits are wanted.
+whose logits are wanted.  Two things architectures do around that flow are constants of the
+spec: a factor on the embedding rows, and a factor and a soft cap on the logits.
 """
 from __future__ import annotations
 
@@ -87,11 +88,14 @@ class DecoderModel:
         """Runs the step's tokens; returns float32 logits ``[num_logits, vocab]`` at
         ``step.logit_rows`` (``None`` when no logits are wanted: the head is skipped).
         ``caches[i]`` belongs to run ``i`` of the order (a shared cache appears twice)."""
-        residual = ops.embed_gather(step.token_ids, self.embedding)
+        residual = ops.embed_gather(step.token_ids, self.embedding, scale=self.spec.embedding_scale)
         stream = ResidualStream(residual)
         for position, run in enumerate(self.spec.order):
             self.blocks[run.layer].forward(stream, step, caches[position])
         if step.num_logits == 0:
             return None
         hidden = self.final_norm.apply(stream, rows=step.logit_rows)
-        return ops.linear(hidden, self.lm_head, out_dtype=torch.float32)
+        logits = ops.linear(hidden, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap is not None:
+            ops.logit_transform(logits, self.spec.logit_scale, self.spec.logit_softcap)
+        return logits

@@ -51,7 +51,10 @@ class TensorDecl:
 # ---------------------------------------------------------------------------------------
 @dataclass(frozen=True)
 class KVNeed:
-    """Paged keys and values: one key and one value vector per KV head and token.
+    """Paged rows per token: for each of ``n_kv_heads`` heads a key row of ``head_dim`` numbers and a
+    value row of ``value_dim`` numbers (``None``: as wide as the key; ``0``: no value rows at all -
+    a mixer that keeps one row per token, such as a compressed latent, asks for one head of
+    that width and no values).
 
     ``window``: a query at position p reads keys at positions (p - window, p]; ``None``
     reads all of them.  Layers whose KVNeed is equal share a page pool (a cache group).
@@ -60,6 +63,11 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -80,8 +88,8 @@ class CacheNeed:
 class LayerCache:
     """What the cache manager hands a mixer for one layer and one step.
 
-    ``k_pages`` / ``v_pages``: ``[num_pages, n_kv_heads, page_size, head_dim]`` of this
-    layer.  ``block_table``: int32 ``[rows, width]``, logical page of a row -> physical page
+    ``k_pages``: ``[num_pages, n_kv_heads, page_size, head_dim]`` of this layer; ``v_pages``
+    likewise with the value rows' width, or ``None`` if the mixer asked for no value rows.  ``block_table``: int32 ``[rows, width]``, logical page of a row -> physical page
     (-1 where the row holds none, e.g. behind a window).  ``state``: ``[slots, *shape]``;
     a row's state is ``state[step.slots[row]]``.
     """

@@ -62,6 +62,9 @@ class ModelSpec:
     order: tuple[Union[RunSpec, int], ...]
     eos_token_ids: tuple[int, ...] = ()
     ignored_tensors: tuple[str, ...] = ()   # checkpoint names that may be present and are not used
+    embedding_scale: float = 1.0            # the embedding rows are multiplied by it as they enter the residual stream
+    logit_scale: float = 1.0                # the logits are multiplied by it,
+    logit_softcap: Optional[float] = None   # then, with a cap c, squashed to c * tanh(logit / c)
 
     def __post_init__(self) -> None:
         runs = tuple(run if isinstance(run, RunSpec) else RunSpec(int(run)) for run in self.order)

@@ -98,6 +98,37 @@ def test_groups_have_pages_of_their_own_and_windows_give_pages_back():
     assert cache.free_pages() == [10, 10]
 
 
+def test_each_group_gets_the_pages_it_needs():
+    from pylon_b200.cache.manager import group_page_counts
+
+    full, windowed, latent = KVNeed(2, 8), KVNeed(2, 8, window=6), KVNeed(1, 24, value_dim=0)
+    needs = [CacheNeed(kv=full), CacheNeed(kv=windowed), CacheNeed(kv=full), None, CacheNeed(kv=latent), CacheNeed(state=StateNeed((4,)))]
+    # a pool of 400 tokens in pages of 4; three requests of up to 64 tokens, steps of up to 8 tokens
+    counts = group_page_counts(needs, page_size=4, pool_tokens=400, max_requests=3, longest_request=64, max_step_tokens=8)
+    # window 6 and a step of 8 tokens span 13 positions: 4 pages and one for the misalignment, per request
+    assert counts == {full: 100, windowed: 3 * 5, latent: 100}
+    cache = CacheManager(needs, [None, None, None, 1, None, None], page_size=4, num_pages=counts, max_requests=3)
+    assert [group.pool.num_pages for group in cache.groups] == [100, 15, 100]
+    assert cache.lifetime_pages(64, 8) == [16, 5, 16]
+    # three requests at once never need more of the windowed group than it has
+    live = [cache.open(name, 64) for name in "abc"]
+    for _ in range(8):
+        cache.prepare([(request, 8) for request in live])
+        for request in live:
+            cache.commit(request)
+        cache.check()
+    assert all(request.length == 64 for request in live)
+    # a pool that is small anyway is not made larger for a window
+    assert group_page_counts(needs, 4, 40, 3, 64, 8)[windowed] == 10
+
+
+def test_rows_without_values_and_rows_of_other_widths_count_their_bytes():
+    needs = [CacheNeed(kv=KVNeed(2, 8)), CacheNeed(kv=KVNeed(1, 24, value_dim=0)), CacheNeed(kv=KVNeed(2, 8, value_dim=4))]
+    cache = CacheManager(needs, [None, None, None], page_size=4, num_pages=3, max_requests=1)
+    assert [group.need.value_width for group in cache.groups] == [8, 0, 4]
+    assert [group.bytes_per_token(2) for group in cache.groups] == [2 * (8 + 8) * 2, 24 * 2, 2 * (8 + 4) * 2]
+
+
 def test_state_slots_without_pages():
     needs = [CacheNeed(state=StateNeed((3, 5))), CacheNeed(kv=KVNeed(1, 4))]
     cache = CacheManager(needs, [None, None], page_size=4, num_pages=2, max_requests=2)

@@ -88,9 +88,9 @@ def test_one_call_generate_and_stop_ids(tiny_folders):
     config = EngineConfig(dtype="float32", page_size=8, max_cache_tokens=256, max_batch_size=2)
     results = engine_module.generate(tiny_folders[name], [prompt], SamplingParams(max_new_tokens=6, temperature=0.0, stop_ids=(stop,)), config)
     assert results[0].finish_reason == "eos" and results[0].output_ids == free_run[:first_stop]
-    with pytest.raises(ValueError, match="Token IDs"):
+    with pytest.raises(ValueError, match="not a token id"):
         engine_module.generate(tiny_folders[name], [[10_000]], SamplingParams(max_new_tokens=1), config)
-    with pytest.raises(ValueError, match="cache positions"):
+    with pytest.raises(ValueError, match="set up for requests of up to"):
         engine_module.generate(tiny_folders[name], [[1] * 300], SamplingParams(max_new_tokens=10), config)
 
 
@@ -203,6 +203,45 @@ def test_a_decode_step_replays_the_graph_that_fits_its_lengths(tiny_folders):
     got = engine.generate(ragged, [greedy] * 2)
     assert sorted(graphs.captured) == [2] and not graphs.failed
     assert [r.output_ids for r in got] == [r.output_ids for r in plain_engine.generate(ragged, [greedy] * 2)]
+
+
+def test_a_void_step_fails_its_requests_and_the_engine_goes_on(tiny_folders):
+    """A kernel that gives up a bounded wait leaves its error word set and its step's result void.  The engine looks at
+    the words before it accepts a step's tokens: the requests of that step fail with the kernel error and give back what
+    they held; requests that come afterwards run as if nothing had happened.  (The word is set from the host, while a step
+    is being sampled: no kernel is made to give up.)"""
+    from pylon_b200.kernels import ops
+    from pylon_b200.sampling import SamplingParams
+
+    name = "tinyB"
+    cfg, weights = plain.read_model(tiny_folders[name])
+    prompts = prompts_for(name)[:2]
+    engine = engine_for(tiny_folders[name], name, "float32")
+    greedy = SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True)
+    healthy_sampler, calls = engine.sampler, []
+
+    class Sampler:
+        def __call__(self, logits, params, randoms):
+            calls.append(len(params))
+            if len(calls) == 2:   # the second sampled step is the void one
+                ops.attention_error_word(engine.device).fill_(1)
+                ops._zeroed_counters(engine.device, "attention", 8)[:8] = 3
+            return healthy_sampler(logits, params, randoms)
+
+    engine.sampler = Sampler()
+    for prompt in prompts:
+        engine.submit(prompt, greedy)
+    results = []
+    while engine.scheduler.has_work():
+        results += engine.tick()
+    assert len(results) == 2 and all(result.finish_reason == "error" and isinstance(result.error, ops.KernelError) for result in results)
+    assert all(len(result.output_ids) == 1 for result in results)       # the first step's token was accepted, the void step's was not
+    engine.cache.check()
+    assert engine.cache.free_pages() == [g.pool.num_pages for g in engine.cache.groups] and engine.cache.free_slots() == 4
+    assert int(ops._zeroed_counters(engine.device, "attention", 8).abs().sum().item()) == 0
+    engine.sampler = healthy_sampler
+    again = engine.generate(prompts, greedy)
+    assert [r.output_ids for r in again] == [plain.generate_greedy(cfg, weights, prompt, 5) for prompt in prompts]
 
 
 def test_command_line(tiny_folders, tmp_path):

@@ -270,10 +270,69 @@ def test_kernel_error_words_are_reported_once():
     device = torch.device(DEVICE)
     ops.raise_on_kernel_errors(device)            # nothing pending after the tests before this one
     ops.attention_error_word(device).fill_(3)
-    with pytest.raises(ops.KernelError, match="attention \\(code 3\\)"):
+    with pytest.raises(ops.KernelError, match="attention \\(a bounded wait ran out, code 3\\)"):
         ops.raise_on_kernel_errors(device)
     ops.raise_on_kernel_errors(device)            # cleared
     assert int(ops.tcgen05_error_word(device).item()) == 0 and int(ops.stream_error_word(device).item()) == 0
+    # "cuda" and "cuda:0" name the same words
+    ops.attention_error_word(torch.device("cuda", torch.cuda.current_device())).fill_(1)
+    assert int(ops.attention_error_word(torch.device("cuda")).item()) == 1
+    with pytest.raises(ops.KernelError):
+        ops.raise_on_kernel_errors(torch.device("cuda"))
+
+
+def test_after_a_kernel_error_the_decode_attention_counts_from_zero_again():
+    """A block of the decode attention that gives up never takes part in the count of the rows it shared, so their
+    counters are left above zero.  The check that reports the error puts them back; the next launch is right.
+    (Counters and word are written from the host here: no kernel is made to give up.)"""
+    from pylon_b200.kernels import ops
+
+    device = torch.device(DEVICE)
+    nq, nkv, d = 8, 2, 64
+    cache = Paged([700, 640, 90, 513], [1, 1, 1, 1], nkv, d, 64, torch.bfloat16, seed=4)
+    fused = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(torch.bfloat16)
+    run = lambda: ops.paged_attention(fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len,
+                                      cache.table, nq, 1, max(cache.kv_lens))
+    want = attention_reference(fused[:, : nq * d].reshape(cache.tokens, nq, d), cache, nq, nkv, d, None, 1.0 / math.sqrt(d))
+    torch.testing.assert_close(run().double(), want, rtol=2e-2, atol=2e-2)
+    ops.raise_on_kernel_errors(device)
+    counters = ops._zeroed_counters(device, "attention", len(cache.kv_lens) * nkv)
+    assert int(counters.abs().sum().item()) == 0           # a launch that runs to its end leaves them at zero
+    counters[: len(cache.kv_lens) * nkv] = 1               # what a block that gave up would leave behind
+    ops.attention_error_word(device).fill_(1)
+    with pytest.raises(ops.KernelError, match="attention"):
+        ops.raise_on_kernel_errors(device)
+    assert int(counters.abs().sum().item()) == 0
+    torch.testing.assert_close(run().double(), want, rtol=2e-2, atol=2e-2)
+    ops.raise_on_kernel_errors(device)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_block_table_that_names_a_page_outside_the_pool_is_reported(dtype):
+    """The kernels never follow such an entry (they skip the access), and they say so: the cache write sets its
+    error word, the attention sets its own; in both cases the check raises and the memory around the pool is untouched."""
+    from pylon_b200.kernels import ops
+
+    device = torch.device(DEVICE)
+    ops.raise_on_kernel_errors(device)
+    nq, nkv, d, page = 4, 2, 64, 64
+    cache = Paged([70, 130], [3, 2], nkv, d, page, dtype, seed=9)
+    num_pages = cache.k_pages.shape[0]
+    qkv = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(dtype)
+    broken = cache.table.clone()
+    broken[0, 1] = num_pages + 7          # the page the first row's new tokens would be written to
+    k_before, v_before = cache.k_pages.clone(), cache.v_pages.clone()
+    ops.qk_norm_rope_kv_write(qkv.clone(), None, None, 0.0, None, None, 0, cache.positions, cache.token_row, broken, page,
+                              cache.k_pages, cache.v_pages, nq, nkv, d)
+    with pytest.raises(ops.KernelError, match="cache write \\(a block table names a page outside the pool, code 5\\)"):
+        ops.raise_on_kernel_errors(device)
+    written = (cache.k_pages != k_before).flatten(1).any(1) | (cache.v_pages != v_before).flatten(1).any(1)
+    assert written.nonzero().flatten().tolist() == [int(cache.table[1, 2])]   # only the second row's page was written
+    if dtype == torch.bfloat16:
+        ops.paged_attention(qkv, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, broken, nq, 3, 130)
+        with pytest.raises(ops.KernelError, match="attention \\(a block table names a page outside the pool, code 5\\)"):
+            ops.raise_on_kernel_errors(device)
+    ops.raise_on_kernel_errors(device)
 
 
 def test_skinny_gemm_refuses():

@@ -143,9 +143,9 @@ def test_attention_part_whole_and_in_two_steps(dtype, heads, kv_heads, dim, wind
 # models put together in the test
 # ---------------------------------------------------------------------------------------
 def register_toy_parts():
-    """A mixer with a state of its own (running mean of its inputs) — defined here, not in the
-    framework."""
-    from pylon_b200.parts import MIXERS, CacheNeed, Mixer, StateNeed, TensorDecl
+    """Two mixers defined here, not in the framework: one with a state of its own (running mean of its
+    inputs), one that keeps a single latent row per token in the pages and no value rows."""
+    from pylon_b200.parts import MIXERS, CacheNeed, KVNeed, Mixer, StateNeed, TensorDecl
     from pylon_b200.kernels import ops
 
     if "toy_running_mean" in MIXERS.kinds():
@@ -169,21 +169,56 @@ def register_toy_parts():
             return CacheNeed(state=StateNeed((self.width,), torch.float32))
 
         def forward(self, h, step, cache):
-            starts = step.q_start.tolist()
-            slots = step.slots.tolist()
-            means = torch.empty_like(h, dtype=torch.float32)
-            for r in range(step.num_rows):
-                a, b = starts[r], starts[r + 1]
-                running = cache.state[slots[r]] + torch.cumsum(h[a:b].float(), dim=0)
-                cache.state[slots[r]] = running[-1]
-                means[a:b] = running / (step.positions[a:b].float() + 1.0).unsqueeze(1)
+            # On the device from end to end (no look at the host), so that a decode step can be captured in a CUDA graph.
+            rows = step.token_row[: h.shape[0]].long()
+            starts, slots = step.q_start.long(), step.slots.long()
+            total = torch.cumsum(h.float(), dim=0)
+            before_row = torch.where((starts[:-1] > 0).unsqueeze(1), total[(starts[:-1] - 1).clamp(min=0)], torch.zeros_like(total[:1]))
+            running = cache.state[slots][rows] + total - before_row[rows]
+            cache.state.index_copy_(0, slots, running[starts[1:] - 1])
+            means = running / (step.positions[: h.shape[0]].float() + 1.0).unsqueeze(1)
             return ops.linear(means.to(h.dtype), self.w)
+
+    @MIXERS.register("toy_latent")
+    class LatentAttention(Mixer):
+        """Keeps ONE row per token, a latent c_t = Wc h_t, and no value rows: delta_t = Wo sum_j softmax_j(q_t . c_j / sqrt(L)) c_j
+        over j <= t with q_t = Wq h_t.  The rows live in the manager's pages (one head of width L, value width 0)."""
+
+        def __init__(self, width: int, latent: int) -> None:
+            self.width, self.latent = width, latent
+            self.wc = self.wq = self.wo = None
+
+        def tensors(self):
+            return (TensorDecl("c_proj.weight", (self.latent, self.width)), TensorDecl("q_proj.weight", (self.latent, self.width)),
+                    TensorDecl("o_proj.weight", (self.width, self.latent)))
+
+        def load(self, tensors, dtype, device):
+            self.wc, self.wq, self.wo = (tensors[name].contiguous() for name in ("c_proj.weight", "q_proj.weight", "o_proj.weight"))
+
+        def cache_need(self):
+            return CacheNeed(kv=KVNeed(1, self.latent, value_dim=0))
+
+        def forward(self, h, step, cache):
+            assert cache.v_pages is None and cache.k_pages.shape[1:] == (1, cache.page_size, self.latent)
+            tokens, page = h.shape[0], cache.page_size
+            c, q = ops.linear(h, self.wc), ops.linear(h, self.wq)
+            positions = step.positions[:tokens].long()
+            tables = cache.block_table[step.token_row[:tokens].long()].long()                      # [T, W]
+            own_page = tables.gather(1, (positions // page).unsqueeze(1)).squeeze(1)
+            cache.k_pages[own_page, 0, positions % page] = c                                       # write first, then read
+            rows = cache.k_pages[tables.clamp(min=0)].reshape(tokens, -1, self.latent).float()      # [T, W * page, L]
+            scores = torch.einsum("tl,tkl->tk", q.float(), rows) / math.sqrt(self.latent)
+            visible = torch.arange(rows.shape[1], device=h.device).unsqueeze(0) <= positions.unsqueeze(1)
+            weights = torch.softmax(scores.masked_fill(~visible, float("-inf")), dim=-1)
+            context = torch.einsum("tk,tkl->tl", weights, torch.where(visible.unsqueeze(2), rows, torch.zeros_like(rows)))
+            return ops.linear(context.to(h.dtype), self.wo)
 
 
 @dataclass(frozen=True)
 class ToyConfig:
     """A made-up architecture for the tests: layer 0 mixes with the running mean, layer 1 with
-    windowed attention, layer 2 with full attention; the order runs layer 0 twice."""
+    windowed attention, layer 2 with full attention, layer 3 with attention over one latent row per
+    token; the order runs layer 0 twice.  The embedding is scaled and the logits are soft-capped."""
 
     architecture = "ToyForCausalLM"
     vocab_size: int = 200
@@ -194,10 +229,14 @@ class ToyConfig:
     intermediate: int = 88
     window: int = 11
     eps: float = 1e-5
+    latent: int = 24
+    embedding_scale: float = 1.75
+    logit_softcap: float = 0.6
 
     @classmethod
     def from_dict(cls, data):
-        return cls(**{k: data[k] for k in ("vocab_size", "width", "heads", "kv_heads", "head_dim", "intermediate", "window", "eps")})
+        return cls(**{k: data[k] for k in ("vocab_size", "width", "heads", "kv_heads", "head_dim", "intermediate", "window", "eps", "latent",
+                                           "embedding_scale", "logit_softcap")})
 
     def to_dict(self):
         return {"architectures": [self.architecture], **self.__dict__}
@@ -225,17 +264,19 @@ def toy_spec(config: ToyConfig, max_positions: Optional[int] = None):
         LayerSpec("layers.0.", block(PartSpec("toy_running_mean", {"width": config.width}))),
         LayerSpec("layers.1.", block(attention(config.window))),
         LayerSpec("layers.2.", block(attention(None))),
+        LayerSpec("layers.3.", block(PartSpec("toy_latent", {"width": config.width, "latent": config.latent}))),
     )
     return ModelSpec(
         width=config.width, vocab_size=config.vocab_size, max_positions=positions, embedding_name="embed.weight", lm_head_name="head.weight",
-        final_norm=norm, final_norm_prefix="norm.", layers=layers, order=(RunSpec(0), RunSpec(1), RunSpec(0), RunSpec(2)),
+        final_norm=norm, final_norm_prefix="norm.", layers=layers, order=(RunSpec(0), RunSpec(1), RunSpec(0), RunSpec(2), RunSpec(3)),
+        embedding_scale=config.embedding_scale, logit_scale=2.0, logit_softcap=config.logit_softcap,
     )
 
 
 def toy_plain_forward(config: ToyConfig, w: Mapping[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
     """The toy model on a whole sequence, from the plain implementation's functions."""
     ids = torch.as_tensor(list(tokens))
-    x = w["embed.weight"][ids]
+    x = w["embed.weight"][ids] * config.embedding_scale
     cos, sin = plain.rope_tables(config.head_dim, 10_000.0, torch.arange(len(ids)), x.dtype)
     cfg = {"num_attention_heads": config.heads, "num_key_value_heads": config.kv_heads, "head_dim": config.head_dim, "rms_norm_eps": config.eps}
 
@@ -243,16 +284,28 @@ def toy_plain_forward(config: ToyConfig, w: Mapping[str, torch.Tensor], tokens: 
         means = torch.cumsum(h, dim=0) / torch.arange(1, len(h) + 1, dtype=h.dtype).unsqueeze(1)
         return means @ w[prefix + "self_attn.mix.weight"].T
 
+    def latent_attention(h, prefix):
+        c, q = h @ w[prefix + "self_attn.c_proj.weight"].T, h @ w[prefix + "self_attn.q_proj.weight"].T
+        scores = q @ c.T / math.sqrt(config.latent)
+        causal = torch.tril(torch.ones(len(h), len(h), dtype=torch.bool))
+        return torch.softmax(scores.masked_fill(~causal, float("-inf")), dim=-1) @ c @ w[prefix + "self_attn.o_proj.weight"].T
+
     def run(x, layer, window):
         prefix = f"layers.{layer}."
         h = plain.rms_norm(x, w[prefix + "input_layernorm.weight"], config.eps)
-        x = x + (running_mean(h, prefix) if layer == 0 else plain.attention_part(h, w, prefix, cfg, cos, sin, window))
+        if layer == 0:
+            x = x + running_mean(h, prefix)
+        elif layer == 3:
+            x = x + latent_attention(h, prefix)
+        else:
+            x = x + plain.attention_part(h, w, prefix, cfg, cos, sin, window)
         h = plain.rms_norm(x, w[prefix + "post_attention_layernorm.weight"], config.eps)
         return x + plain.swiglu_part(h, w, prefix)
 
-    for layer, window in ((0, None), (1, config.window), (0, None), (2, None)):
+    for layer, window in ((0, None), (1, config.window), (0, None), (2, None), (3, None)):
         x = run(x, layer, window)
-    return plain.rms_norm(x, w["norm.weight"], config.eps) @ w["head.weight"].T
+    logits = (plain.rms_norm(x, w["norm.weight"], config.eps) @ w["head.weight"].T) * 2.0
+    return config.logit_softcap * torch.tanh(logits / config.logit_softcap)
 
 
 @pytest.fixture(scope="module")
@@ -287,20 +340,86 @@ def test_toy_model_with_state_window_and_a_layer_run_twice(toy_folder, cutting, 
                 "changing_portions": trace_tools.changing_portions, "mixed": trace_tools.mixed}
     steps = builders[cutting](requests)
     page = 8
+    # no portion of these cuttings but a whole prompt is longer than 24 tokens: the pools are sized for steps of that many
+    chunk = 24 if cutting in ("changing_portions", "mixed") else 128
     engine = Engine(toy_folder, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=trace_tools.pool_tokens(steps, page),
-                                             max_context=128, max_batch_size=4))
-    assert len(engine.cache.groups) == 2                        # windowed and full attention: pages of their own
+                                             max_context=128, max_batch_size=4, prefill_chunk_size=chunk))
+    assert len(engine.cache.groups) == 3        # windowed attention, full attention, latent rows: pages of their own
     assert engine.cache.state_bytes_per_request() == 2 * config.width * 4   # one state per run of layer 0
+    latent = next(g for g in engine.cache.groups if g.need.value_width == 0)
+    assert latent.values is None and latent.keys.shape[2:] == (1, page, config.latent)
+    element = 4 if dtype == "float32" else 2
+    assert engine.cache.bytes_per_token() == (2 * 2 * config.kv_heads * config.head_dim + config.latent) * element
     got = trace_tools.run_in_process(engine, steps)
     tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
     for rid in requests:
         np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, **tol)
     windowed = next(g for g in engine.cache.groups if g.need.window is not None)
-    full = next(g for g in engine.cache.groups if g.need.window is None)
+    full = next(g for g in engine.cache.groups if g.need.window is None and g.need.value_width)
     assert windowed.pool.free_count == windowed.pool.num_pages and full.pool.free_count == full.pool.num_pages
     if cutting != "whole":
         # the windowed group never needed as many pages at once as the full one
         assert windowed.pool.acquired_total >= full.pool.acquired_total > 0
+    if chunk == 24:
+        # and was given fewer: four requests of window + one step's tokens each, not the whole pool
+        assert windowed.pool.num_pages == min(full.pool.num_pages, 4 * (-(-(config.window - 1 + chunk) // page) + 1))
+        assert cutting != "mixed" or windowed.pool.num_pages < full.pool.num_pages
+
+
+@pytest.mark.parametrize("cutting", ["tail_one_by_one", "mixed"])
+def test_toy_model_decodes_from_cuda_graphs(toy_folder, cutting):
+    """Every mixer of the toy model runs on the device from end to end, so its decode steps are captured.  Capturing a
+    step runs it once eagerly first; the running-mean mixer's state must not be advanced by that run as well."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine
+
+    config = ToyConfig()
+    _, weights = plain.read_model(toy_folder)
+    rng = np.random.default_rng(6)
+    requests = {f"g{i}": rng.integers(0, config.vocab_size, size=n).tolist() for i, n in enumerate((50, 33, 71, 40))}
+    expected = {rid: plain.as_numpy(toy_plain_forward(config, weights, tokens)) for rid, tokens in requests.items()}
+    steps = (trace_tools.tail_one_by_one if cutting == "tail_one_by_one" else trace_tools.mixed)(requests)
+    engine = Engine(toy_folder, EngineConfig(dtype="float32", page_size=8, max_cache_tokens=trace_tools.pool_tokens(steps, 8),
+                                             max_context=128, max_batch_size=4, cuda_graphs=True))
+    got = trace_tools.run_in_process(engine, steps)
+    for rid in requests:
+        np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, rtol=1e-4, atol=1e-5)
+    graphs = engine.step_function.graphs
+    assert (graphs.captured or graphs.captured_alike) and not graphs.failed
+
+
+def test_a_failed_step_leaves_pages_and_state_as_they_were(toy_folder):
+    """A step that fails after some of its layers ran (here: the last block raises, once) must leave its requests as
+    they were: the pages it acquired go back, and the running-mean state, which its first layers advanced, is restored;
+    the same step then gives the logits it should."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine, StepEntry
+
+    config = ToyConfig()
+    _, weights = plain.read_model(toy_folder)
+    rng = np.random.default_rng(7)
+    tokens = {"a": rng.integers(0, config.vocab_size, size=40).tolist(), "b": rng.integers(0, config.vocab_size, size=27).tolist()}
+    expected = {rid: plain.as_numpy(toy_plain_forward(config, weights, ids)) for rid, ids in tokens.items()}
+    engine = Engine(toy_folder, EngineConfig(dtype="float32", page_size=8, max_cache_tokens=256, max_context=128, max_batch_size=4))
+    live = {rid: engine.open(rid, 128) for rid in tokens}
+    engine.step([StepEntry(live["a"], tokens["a"][:30], ()), StepEntry(live["b"], tokens["b"][:20], ())])
+    free_before = engine.cache.free_pages()
+    last_block = engine.model.blocks[engine.spec.order[-1].layer]
+    healthy = last_block.forward
+
+    def failing(*args, **kwargs):
+        last_block.forward = healthy
+        raise RuntimeError("injected")
+
+    entries = [StepEntry(live["a"], tokens["a"][30:], tuple(range(10))), StepEntry(live["b"], tokens["b"][20:], tuple(range(7)))]
+    last_block.forward = failing
+    with pytest.raises(RuntimeError, match="injected"):
+        engine.step(entries)
+    assert engine.cache.free_pages() == free_before and live["a"].length == 30 and live["b"].length == 20
+    engine.cache.check()
+    got = engine.step(entries).cpu().numpy()
+    np.testing.assert_allclose(got[:10], expected["a"][30:], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(got[10:], expected["b"][20:], rtol=1e-4, atol=1e-5)
 
 
 # ---------------------------------------------------------------------------------------

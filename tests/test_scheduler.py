@@ -152,7 +152,7 @@ def test_skip_ahead_admission_and_its_100_ms_limit():
     scheduler.add("big", list(range(12)), SamplingParams(max_new_tokens=4, temperature=0.0))    # 4 pages: does not fit beside a
     scheduler.add("small", [1, 2], SamplingParams(max_new_tokens=1, temperature=0.0))            # 1 page
     scheduler.admit()
-    assert [r.request_id for r in scheduler.active] == ["a", "small"] and scheduler.head_skips == 1
+    assert [r.request_id for r in scheduler.active] == ["a", "small"] and scheduler.overtakes == 1
     scheduler2, _, clock2, _ = make(num_pages=6, plan=plan, admit_skip=4)
     scheduler2.add("a", list(range(8)), SamplingParams(max_new_tokens=4, temperature=0.0))
     scheduler2.add("big", list(range(12)), SamplingParams(max_new_tokens=4, temperature=0.0))
