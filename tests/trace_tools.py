@@ -65,11 +65,11 @@ def changing_portions(requests: dict[str, list[int]], sizes: Sequence[int] = (7,
     return steps
 
 
-def mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12) -> list[dict]:
+def mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12, max_portion: int = 24) -> list[dict]:
     """Up to ``max_live`` requests at a time: portions of some beside single tokens of others.
 
     Each request goes through its first ``len - decode_tail`` tokens in portions of random
-    size (2..24), then through the rest one token a step; a request is sometimes left out of
+    size (2..``max_portion``), then through the rest one token a step; a request is sometimes left out of
     a step; finished requests end and the next one starts, so their pages are used again.
     """
     rng = np.random.default_rng(seed)
@@ -89,7 +89,7 @@ def mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4, deco
             if remaining <= decode_tail:
                 size = 1
             else:
-                size = int(rng.integers(2, 25))
+                size = int(rng.integers(2, max_portion + 1))
                 size = min(size, remaining - decode_tail)
                 if size < 2:
                     size = remaining - decode_tail if remaining - decode_tail >= 1 else 1
