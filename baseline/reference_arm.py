@@ -88,7 +88,28 @@ class _Arm:
         return self.torch.randint(0, self.config.vocab_size, (count,), generator=self.generator).tolist()
 
     # -- the serving path: pages and graphs --------------------------------------------------
-    def paged_decode(self, batch: int, steps: int, warmup: int, graphs: bool) -> dict:
+    def timed_repeats(self, step, steps: int, warmup: int, repeats: int) -> list[float]:
+        """``warmup`` untimed calls of ``step``, then ``repeats`` times K calls between CUDA events; milliseconds of each repeat."""
+        torch = self.torch
+        for _ in range(warmup):
+            step()
+        spans = []
+        for _ in range(repeats):
+            begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin_event.record()
+            for _ in range(steps):
+                step()
+            end_event.record()
+            torch.cuda.synchronize()
+            spans.append(begin_event.elapsed_time(end_event))
+        return spans
+
+    @staticmethod
+    def middle(spans: list[float]) -> float:
+        return sorted(spans)[len(spans) // 2]
+
+    def paged_decode(self, batch: int, steps: int, warmup: int, graphs: bool, repeats: int = 1) -> dict:
         torch = self.torch
         from pylon.decode.runner import Decoder
         from pylon.decode.warmup import capture_decode_graphs
@@ -100,7 +121,7 @@ class _Arm:
         decoder = Decoder(self.model)
         decoder.page_pool = pool
         try:
-            start_length = self.context - (warmup + steps)
+            start_length = self.context - (warmup + repeats * steps)
             caches = [PagedKVCache(pool, self.context) for _ in range(batch)]
             for cache in caches:
                 prompt = self.tokens(start_length)
@@ -110,21 +131,18 @@ class _Arm:
             captured = ()
             if graphs:
                 captured = capture_decode_graphs(decoder, token_id=1, max_batch_size=batch, max_tokens=self.context)
-            token_ids = self.tokens(batch)
-            begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            for index in range(warmup + steps):
-                if index == warmup:
-                    torch.cuda.synchronize()
-                    begin_event.record()
-                logits = decoder.decode_caches(caches, token_ids)
-                token_ids = logits.argmax(dim=-1).cpu().tolist()
-            end_event.record()
-            torch.cuda.synchronize()
-            milliseconds = begin_event.elapsed_time(end_event)
+            state = {"tokens": self.tokens(batch)}
+
+            def step():
+                logits = decoder.decode_caches(caches, state["tokens"])
+                state["tokens"] = logits.argmax(dim=-1).cpu().tolist()
+
+            spans = self.timed_repeats(step, steps, warmup, repeats)
+            milliseconds = self.middle(spans)
             for cache in caches:
                 decoder.release_cache(cache)
             return {"ms_per_step": milliseconds / steps, "tokens_per_second": batch * steps / (milliseconds / 1e3),
-                    "graphs": batch in captured}
+                    "graphs": batch in captured, "per_repeat": [batch * steps / (ms / 1e3) for ms in spans]}
         finally:
             decoder.graphs = None
             decoder.release_page_pool()
@@ -200,36 +218,42 @@ class _Arm:
                 "d2h_bytes_per_step": batch * 8}
 
     # -- the dense cache: no pages, no graphs ------------------------------------------------
-    def dense_decode(self, batch: int, steps: int, warmup: int, host_timed: bool = False) -> dict:
+    def dense_decode(self, batch: int, steps: int, warmup: int, host_timed: bool = False, repeats: int = 1) -> dict:
         torch = self.torch
         from pylon.api.types import Sampling
         from pylon.decode.runner import Decoder
 
         decoder = Decoder(self.model)
-        start_length = self.context - (warmup + steps)
-        sampling = Sampling(temperature=0, top_p=1, max_new_tokens=warmup + steps)
+        new_tokens = warmup + repeats * steps
+        start_length = self.context - new_tokens
+        sampling = Sampling(temperature=0, top_p=1, max_new_tokens=new_tokens)
         caches = [decoder.prefill(self.tokens(start_length), sampling, max_total_tokens=self.context).cache for _ in range(batch)]
-        token_ids = self.tokens(batch)
-        begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        started = 0.0
-        for index in range(warmup + steps):
-            if index == warmup:
-                torch.cuda.synchronize()
-                begin_event.record()
-                started = time.perf_counter()
-            logits = decoder.decode_caches(caches, token_ids)
-            token_ids = logits.argmax(dim=-1).cpu().tolist()
-        end_event.record()
-        torch.cuda.synchronize()
-        seconds = time.perf_counter() - started
-        milliseconds = begin_event.elapsed_time(end_event)
+        state = {"tokens": self.tokens(batch)}
+
+        def step():
+            logits = decoder.decode_caches(caches, state["tokens"])
+            state["tokens"] = logits.argmax(dim=-1).cpu().tolist()
+
+        if host_timed:
+            for _ in range(warmup):
+                step()
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            for _ in range(steps):
+                step()
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - started
+        else:
+            spans = self.timed_repeats(step, steps, warmup, repeats)
+            milliseconds = self.middle(spans)
         for cache in caches:
             decoder.release_cache(cache)
         del caches
         torch.cuda.empty_cache()
         if host_timed:
             return {"value": batch * steps / seconds, "unit": "tokens/s", "h2d_bytes_per_step": batch * 16, "d2h_bytes_per_step": batch * 8}
-        return {"ms_per_step": milliseconds / steps, "tokens_per_second": batch * steps / (milliseconds / 1e3), "graphs": False}
+        return {"ms_per_step": milliseconds / steps, "tokens_per_second": batch * steps / (milliseconds / 1e3), "graphs": False,
+                "per_repeat": [batch * steps / (ms / 1e3) for ms in spans]}
 
     def dense_prefill(self, repeats: int = 5) -> float:
         torch = self.torch
@@ -283,13 +307,13 @@ def run(args, shared: dict) -> int:
     except Exception as error:
         return unavailable(f"raun6k/Pylon's model could not be built: {_short(error)}")
 
-    batch, steps, warmup = args.batch, args.steps, args.warmup
+    batch, steps, warmup, repeats = args.batch, args.steps, args.warmup, int(shared["config"].get("repeats", 1))
     sampler_class = shared["clock_sampler"]
     notes = {}
     path = "paged cache + CUDA graphs (the engine's serving path)"
     try:
         with sampler_class() as sampler:
-            decode = arm.paged_decode(batch, steps, warmup, graphs=True)
+            decode = arm.paged_decode(batch, steps, warmup, graphs=True, repeats=repeats)
         prefill_ms = arm.paged_prefill()
         paged = True
     except Exception as error:
@@ -313,7 +337,7 @@ def run(args, shared: dict) -> int:
         path = "dense per-request KVCache through Decoder (no pages, no graphs, no Engine): the paged path was refused"
         try:
             with sampler_class() as sampler:
-                decode = arm.dense_decode(batch, steps, warmup)
+                decode = arm.dense_decode(batch, steps, warmup, repeats=repeats)
             prefill_ms = arm.dense_prefill()
             e2e = arm.dense_decode(batch, steps, warmup, host_timed=True)
         except Exception as error:
@@ -350,6 +374,7 @@ def run(args, shared: dict) -> int:
         "prefill": {"value": round(arm.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": arm.prefill_tokens, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
         "points": points,
+        "spread": {"min": round(min(decode["per_repeat"]), 1), "max": round(max(decode["per_repeat"]), 1), "repeats": repeats},
     }
     if e2e is not None:
         record["e2e"] = {key: (round(value, 1) if isinstance(value, float) else value) for key, value in e2e.items()}

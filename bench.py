@@ -9,7 +9,14 @@ over exactly K steps of the step function; ``e2e`` is the same through the publi
 point (``Engine.submit`` / ``Engine.tick``: host token lists in, host token lists out, with
 the scheduler, the host-to-device copy of each step's inputs and the device-to-host read of
 its tokens inside the timed region).  ``prefill`` is one 2,048-token prompt in one step;
-``roofline`` relates the decode step to HBM bandwidth; ``points`` holds batch 1 and 64.
+``roofline`` relates the decode step to HBM bandwidth.  The K timed steps are repeated R times
+(``config.repeats``); ``value`` is the median repeat, ``spread`` its lowest and highest, and
+``clocks.sm_mhz_per_repeat`` the SM clock sampled during each.  ``points`` holds the other sizes
+and workloads: decoding at batch 1 and 64 at the same context; the reference's own decode-heavy
+workload (B requests, 128-token prompts, 512 new tokens: B x 511 tokens over the time of the 511
+decode steps) at B = 1, 8, 64 with its share of the HBM roofline; the output rate of the two
+serving workloads at the 8B and 14B shapes; and a full-depth float32 run at the 14B shape with
+its largest logit error against the plain implementation.
 """
 from __future__ import annotations
 
@@ -23,7 +30,9 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
-sys.path.insert(0, str(ROOT))
+for entry in (str(ROOT), str(ROOT / "tests")):   # tests/: the plain implementation, for the float32 check at the 14B shape
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
 
 QWEN3_4B = dict(
     vocab_size=151_936, hidden_size=2_560, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
@@ -68,15 +77,17 @@ class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device_index: int = 0) -> None:
+    def __init__(self, device_index: int = 0, interval_ms: int = 100) -> None:
         self.lines: list[str] = []
+        self.times: list[float] = []     # time.perf_counter() at which each line arrived
         self.process = None
         self.device_index = device_index
+        self.interval_ms = interval_ms
 
     def __enter__(self):
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", str(self.interval_ms)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             self.thread = threading.Thread(target=self._read, daemon=True)
@@ -88,6 +99,7 @@ class ClockSampler:
     def _read(self) -> None:
         for line in self.process.stdout:
             self.lines.append(line.strip())
+            self.times.append(time.perf_counter())
 
     def __exit__(self, *exc) -> None:
         if self.process is not None:
@@ -98,10 +110,14 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.process.kill()
 
-    def summary(self) -> dict:
+    def summary(self, begin: float | None = None, end: float | None = None) -> dict:
+        """Median SM clock, the highest clock the device offers and the throttle reasons seen, over all samples or over
+        those that arrived between two ``time.perf_counter()`` readings."""
         clocks, top, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line, arrived in zip(list(self.lines), list(self.times)):
+            if begin is not None and not begin <= arrived <= end:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -134,34 +150,125 @@ def fill_caches(engine, torch, batch: int, tokens_each: int, rng, chunk: int):
     return requests
 
 
-def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng) -> dict:
-    """Decode ``warmup + steps`` tokens for ``batch`` requests whose contexts end at CONTEXT;
-    the timed K steps are bracketed by CUDA events on the launching stream."""
+def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng, repeats: int = 1) -> dict:
+    """Decode ``warmup + repeats * steps`` tokens for ``batch`` requests whose contexts end at CONTEXT; each repeat's K
+    steps are bracketed by CUDA events on the launching stream.  The figures returned are those of the median repeat."""
     from pylon_b200.engine import StepEntry
 
-    start_length = CONTEXT - (warmup + steps)
+    start_length = CONTEXT - (warmup + repeats * steps)
     requests = fill_caches(engine, torch, batch, start_length, rng, PREFILL_TOKENS)
     tokens = rng.integers(0, engine.spec.vocab_size, size=batch).tolist()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches_before = 0
-    kv_tokens = 0
-    for index in range(warmup + steps):
-        if index == warmup:
-            torch.cuda.synchronize()
-            launches_before = ops.launches[0]
-            begin.record()
-        if index >= warmup:
-            kv_tokens += sum(request.length + 1 for request in requests)
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(repeats)]
+    windows, launches, kv_tokens = [], [], []
+
+    def step():
+        nonlocal tokens
         logits = engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])
         tokens = ops.sample(logits).cpu().tolist()
-    end.record()
-    torch.cuda.synchronize()
-    milliseconds = begin.elapsed_time(end)
-    launches = ops.launches[0] - launches_before
+
+    for _ in range(warmup):
+        step()
+    for begin, end in events:
+        torch.cuda.synchronize()
+        before, held = ops.launches[0], 0
+        started = time.perf_counter()
+        begin.record()
+        for _ in range(steps):
+            held += sum(request.length + 1 for request in requests)
+            step()
+        end.record()
+        torch.cuda.synchronize()
+        windows.append((started, time.perf_counter()))
+        launches.append(ops.launches[0] - before)
+        kv_tokens.append(held / steps)
     for request in requests:
         engine.close(request)
-    return {"ms_per_step": milliseconds / steps, "tokens_per_second": batch * steps / (milliseconds / 1e3),
-            "launches": launches, "kv_tokens_per_step": kv_tokens / steps}
+    milliseconds = [begin.elapsed_time(end) for begin, end in events]
+    middle = sorted(range(repeats), key=lambda index: milliseconds[index])[repeats // 2]
+    return {"ms_per_step": milliseconds[middle] / steps, "tokens_per_second": batch * steps / (milliseconds[middle] / 1e3),
+            "launches": launches[middle], "kv_tokens_per_step": kv_tokens[middle], "windows": windows,
+            "per_repeat": [batch * steps / (ms / 1e3) for ms in milliseconds]}
+
+
+def time_decode_heavy(engine, torch, ops, batch: int, rng, prompt_tokens: int = 128, new_tokens: int = 512) -> dict:
+    """raun6k/Pylon's decode-heavy workload at the step level (README.md:64-74: 128-token prompts, 512 new tokens):
+    ``batch`` requests are prefilled, the first token of each comes with the prompt, and the other 511 are decoded in
+    511 steps timed as one region with CUDA events: tokens a second = batch x 511 / that time."""
+    from pylon_b200.engine import StepEntry
+
+    vocab = engine.spec.vocab_size
+    requests = [engine.open(("heavy", batch, index), prompt_tokens + new_tokens) for index in range(batch)]
+    logits = None
+    for start in range(0, batch, 16):
+        group = requests[start : start + 16]
+        part = engine.step([StepEntry(request, rng.integers(0, vocab, size=prompt_tokens).tolist(), (prompt_tokens - 1,)) for request in group])
+        logits = part if logits is None else torch.cat((logits, part))
+    tokens = ops.sample(logits).cpu().tolist()
+    for _ in range(3):    # the first steps of a size capture its graph and warm up; they count as generated tokens all the same
+        tokens = ops.sample(engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])).cpu().tolist()
+    steps = new_tokens - 1 - 3
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    begin.record()
+    held = 0
+    for _ in range(steps):
+        held += sum(request.length + 1 for request in requests)
+        tokens = ops.sample(engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])).cpu().tolist()
+    end.record()
+    torch.cuda.synchronize()
+    seconds = begin.elapsed_time(end) / 1e3
+    for request in requests:
+        engine.close(request)
+    bytes_per_step = engine.model.weight_bytes() + held / steps * engine.cache.bytes_per_token()
+    return {"tokens_per_second": batch * steps / seconds, "gbs": bytes_per_step / (seconds / steps) / 1e9}
+
+
+def float32_14b_check(torch) -> dict:
+    """The Qwen3-14B shape at its full depth in true 32-bit: 16 requests of 64-token prompts generate 16 tokens each
+    through the engine (output tokens a second, prompts included in the time), and the logits of one 64-token request
+    at every position are compared with the plain implementation in float64, which draws the same weights tensor by
+    tensor (59 GB of float32 weights are on the device; the plain implementation holds one matrix at a time)."""
+    import numpy as np
+
+    import plain_qwen3 as plain
+    from pylon_b200.config import EngineConfig, Qwen3Config
+    from pylon_b200.engine import Engine, StepEntry
+    from pylon_b200.sampling import SamplingParams
+    from pylon_b200.weights.random_init import device_random_fetch
+
+    fields = QWEN3_14B
+    rng = np.random.default_rng(7)
+    requests, prompt_tokens, new_tokens = 16, 64, 16
+    config = EngineConfig(dtype="float32", page_size=PAGE_SIZE, max_cache_tokens=(requests + 1) * PAGE_SIZE, max_context=PAGE_SIZE,
+                          max_batch_size=requests, max_queue_size=requests, prefill_chunk_size=PREFILL_TOKENS)
+    engine = Engine(None, config, device="cuda:0", model_config=Qwen3Config(**fields), random_seed=0)
+    prompts = [rng.integers(0, fields["vocab_size"], size=prompt_tokens).tolist() for _ in range(requests)]
+    engine.generate(prompts[:1], SamplingParams(max_new_tokens=2, temperature=0.0, ignore_eos=True))   # warm up
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    results = engine.generate(prompts, SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    assert all(len(result.output_ids) == new_tokens and result.error is None for result in results)
+    request = engine.open("check", prompt_tokens)
+    logits = engine.step([StepEntry(request, prompts[0], tuple(range(prompt_tokens)))]).double()
+    engine.close(request)
+
+    fetch = device_random_fetch(engine.model.tensor_decls(), 0, engine.device, torch.float32)
+
+    class DrawnOnDemand(dict):
+        def __missing__(self, name):
+            return fetch(name).double()
+
+    cfg = dict(Qwen3Config(**fields).to_dict())
+    with torch.no_grad():
+        expected = plain.forward(cfg, DrawnOnDemand({"model.embed_tokens.weight": fetch("model.embed_tokens.weight").double()}), prompts[0])
+    error = float((logits - expected).abs().max())
+    agree = float((logits.argmax(-1) == expected.argmax(-1)).double().mean())
+    del engine
+    torch.cuda.empty_cache()
+    return {"tokens_per_second": requests * new_tokens / seconds, "max_abs_logit_error": error, "argmax_agreement": agree,
+            "logit_spread": float(expected.std())}
 
 
 def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
@@ -331,6 +438,9 @@ def prefill_flops(cfg: dict, tokens: int) -> float:
 METRIC = "decode tokens/s, Qwen3-4B shape, batch 8, context 4096"
 
 
+REPEATS = 5
+
+
 def headline_config(layers: int, batch: int, cuda_graphs: bool, peak_source: str) -> dict:
     fields = QWEN3_4B
     return {
@@ -338,7 +448,7 @@ def headline_config(layers: int, batch: int, cuda_graphs: bool, peak_source: str
         "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
         "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
         "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-        "parallelism": "single GPU", "cuda_graphs": cuda_graphs, "l2": "inputs larger than L2 (8 GB of weights per step)",
+        "parallelism": "single GPU", "cuda_graphs": cuda_graphs, "repeats": REPEATS, "l2": "inputs larger than L2 (8 GB of weights per step)",
         "peaks": peak_source, "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
     }
 
@@ -415,15 +525,19 @@ def main() -> int:
     peak = peaks()
 
     prefill = time_prefill(engine, torch, 5, rng)
-    with ClockSampler() as sampler:
-        decode = time_decode(engine, torch, ops, args.batch, args.steps, args.warmup, rng)
-    clocks = sampler.summary()
+    with ClockSampler(interval_ms=25) as sampler:
+        decode = time_decode(engine, torch, ops, args.batch, args.steps, args.warmup, rng, repeats=REPEATS)
+    clocks = sampler.summary(decode["windows"][0][0], decode["windows"][-1][1])
+    clocks["sm_mhz_per_repeat"] = [sampler.summary(begin, end)["sm_mhz"] for begin, end in decode["windows"]]
     e2e = time_e2e(engine, torch, args.batch, args.steps, args.warmup, rng)
     points = {}
     if not args.skip_points:
         for batch in (1, 64):
             points[f"decode_b{batch}"] = round(time_decode(engine, torch, ops, batch, max(16, args.steps // 2), args.warmup, rng)["tokens_per_second"], 1)
-
+        for batch in (1, 8, 64):
+            heavy = time_decode_heavy(engine, torch, ops, batch, rng)
+            points[f"decode_heavy_b{batch}"] = round(heavy["tokens_per_second"], 1)
+            points[f"decode_heavy_b{batch}_hbm_frac"] = round(heavy["gbs"] / peak["hbm_gbs"], 4)
     weight_bytes = engine.model.weight_bytes()
     kv_bytes = decode["kv_tokens_per_step"] * engine.cache.bytes_per_token()
     achieved = (weight_bytes + kv_bytes) / (decode["ms_per_step"] / 1e3) / 1e9
@@ -450,7 +564,23 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
+        "spread": {"min": round(min(decode["per_repeat"]), 1), "max": round(max(decode["per_repeat"]), 1), "repeats": REPEATS},
     }
+    if not args.skip_points:
+        # the other shapes need the memory: the 4B engine goes first
+        del engine
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name in ("mixed8b", "sampled14b"):
+            points[f"{name}_output_tokens_per_second"] = run_serving_workload(name, torch)["value"]
+            gc.collect()
+            torch.cuda.empty_cache()
+        check = float32_14b_check(torch)
+        points["float32_14b_tokens_per_second"] = round(check["tokens_per_second"], 1)
+        points["float32_14b_max_abs_logit_error"] = float(f"{check['max_abs_logit_error']:.3g}")
+        points["float32_14b_argmax_agreement"] = round(check["argmax_agreement"], 4)
     print(json.dumps(record))
     return 0
 

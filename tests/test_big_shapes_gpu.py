@@ -1,4 +1,4 @@
-"""The engine at the widths, head counts and vocabulary of Qwen3-4B and Qwen3-14B (a group of
+"""The engine at the widths, head counts and vocabulary of Qwen3-4B, Qwen3-8B and Qwen3-14B (a group of
 five query heads per KV head), with two layers so that the test stays short: float32 and
 bfloat16 logits under several cuttings against the plain implementation run in float64 on the
 GPU.  These sizes reach kernels the tiny models never do: head size 128, the tensor-core
@@ -17,6 +17,8 @@ pytestmark = pytest.mark.gpu
 SHAPES = {
     "4B": dict(vocab_size=151_936, hidden_size=2_560, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                intermediate_size=9_728, max_position_embeddings=4_096, rope_theta=5_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=True),
+    "8B": dict(vocab_size=151_936, hidden_size=4_096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=12_288, max_position_embeddings=4_096, rope_theta=1_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False),
     "14B": dict(vocab_size=151_936, hidden_size=5_120, num_hidden_layers=2, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
                 intermediate_size=17_408, max_position_embeddings=4_096, rope_theta=1_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False),
 }
