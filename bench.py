@@ -397,6 +397,8 @@ def run_serving_workload(name: str, torch) -> dict:
     # The decode graph of every batch size is captured before the first request, as raun6k/Pylon does when it starts
     # (src/pylon/engine.py:823-836); otherwise each size's first step pays for its capture (about 20 ms).
     captured = engine.capture_decode_graphs()
+    # ... and the graphs of the ticks that bring a prompt portion beside 0 to 63 decoding requests
+    engine.capture_padded_graphs([(ones, 1, min(PREFILL_TOKENS, max(lengths))) for ones in (0, 1, 2, 4, 8, 16, 32, 64)[: 1 + requests.bit_length()]])
     torch.cuda.synchronize()
     started = time.perf_counter()
     for prompt, sampling in zip(prompts, params):

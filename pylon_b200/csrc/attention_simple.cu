@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
   const int kv_head = h / (nq / nkv);
   const int pos = positions[t];
   const int row = token_row[t];
+  if (row < 0) return;   // a padding token of a step padded to a captured size: it belongs to no request, its output is never read
   const int* table = block_table + (size_t)row * table_width;
   const T* qrow = q + (size_t)t * q_token_stride + (size_t)h * d;
   for (int e = tid; e < d; e += SIMPLE_THREADS) qs[e] = to_float<T>(qrow[e]) * scale;

@@ -197,6 +197,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
   T* page_dst = nullptr;
   if (head >= nq) {
     const int row = token_row[t];
+    if (row < 0) return;   // a padding token of a step padded to a captured size: it belongs to no request
     const int page = block_table[(size_t)row * table_width + pos / page_size];
     if (page < 0 || page >= num_pages) {   // never for a prepared step: nothing is written, and the host is told
       if (lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
@@ -369,10 +370,10 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(
   size_t page_offset = 0;
   bool page_ok = true;
   if (head_begin + HPW > nq) {   // a key or value head among them
-    const int row = token_row[t];
-    const int page = block_table[(size_t)row * table_width + pos / page_size];
+    const int row = token_row[t];   // negative: a padding token of a step padded to a captured size, which belongs to no request
+    const int page = row < 0 ? -1 : block_table[(size_t)row * table_width + pos / page_size];
     page_ok = page >= 0 && page < num_pages;   // always for a prepared step: else nothing is written, and the host is told
-    if (!page_ok && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
+    if (!page_ok && row >= 0 && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
     page_offset = ((size_t)(page_ok ? page : 0) * nkv * page_size + pos % page_size) * d + lane * CHUNK;
   }
   float c[CHUNK], s[CHUNK];
@@ -463,10 +464,10 @@ __global__ void __launch_bounds__(128, 5) qk_norm_rope_kv_write_wide_kernel(
   size_t page_offset = 0;
   bool page_ok = true;
   if (head_begin + PER_WARP > nq) {   // a key or value head among them
-    const int row = token_row[t];
-    const int page = block_table[(size_t)row * table_width + pos / page_size];
+    const int row = token_row[t];   // negative: a padding token of a step padded to a captured size, which belongs to no request
+    const int page = row < 0 ? -1 : block_table[(size_t)row * table_width + pos / page_size];
     page_ok = page >= 0 && page < num_pages;   // always for a prepared step: else nothing is written, and the host is told
-    if (!page_ok && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
+    if (!page_ok && row >= 0 && lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
     page_offset = ((size_t)(page_ok ? page : 0) * nkv * page_size + pos % page_size) * D;
   }
   float c[8], s[8];

@@ -171,6 +171,43 @@ class Engine:
             torch.cuda.synchronize(self.device)
         return sorted(set(graphs.captured) | set(graphs.captured_alike))
 
+    def capture_padded_graphs(self, sizes: Sequence[tuple[int, int, int]]) -> list[tuple[int, int, int]]:
+        """Captures now, instead of at their first use, the graphs of steps that bring prompt portions: each size is
+        (rows of one token, portion rows, portion tokens), rounded up to the sizes steps are padded to.  Returns the sizes
+        that have a graph.  Needs ``cuda_graphs`` and a model whose parts take padded steps."""
+        from pylon_b200.engine.graphs import bucket_rows, bucket_tokens
+
+        graphs = self.step_function.graphs
+        if graphs is None:
+            raise RuntimeError("cuda_graphs is off")
+        if not graphs.pad_steps:
+            return []
+        graphs.capture_at_once = True
+        try:
+            with torch.cuda.device(self.device):
+                for ones, portions, tokens in sizes:
+                    key = (bucket_rows(ones), bucket_rows(portions), bucket_tokens(tokens))
+                    if key in graphs.captured_padded or key in graphs.failed or key[1] < 1:
+                        continue
+                    # as few real rows as give this size, so that the example step fits beside nothing else
+                    real_ones = key[0] // 2 + 1 if key[0] >= 2 else key[0]
+                    real_portions = key[1] // 2 + 1 if key[1] >= 2 else key[1]
+                    each = max(2, min(key[2] // real_portions, self.max_context))
+                    counts = [each] * real_portions
+                    counts[0] = max(2, min(self.max_context, key[2] - each * (real_portions - 1)))
+                    if real_ones + real_portions > self.cache.free_slots() or bucket_tokens(sum(counts)) != key[2]:
+                        continue
+                    requests = [self.cache.open(("capture", key, index), count) for index, count in enumerate([1] * real_ones + counts)]
+                    try:
+                        self.step_function([StepEntry(request, [0] * request.capacity, (request.capacity - 1,)) for request in requests])
+                    finally:
+                        for request in requests:
+                            self.cache.close(request)
+                torch.cuda.synchronize(self.device)
+        finally:
+            graphs.capture_at_once = False
+        return sorted(graphs.captured_padded)
+
     # -- generation --------------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, request_id: Optional[object] = None) -> object:
         """Queues one request (raun6k/Pylon's ``Engine.enqueue``, src/pylon/engine.py:241-253);

@@ -73,12 +73,13 @@ class StepFunction:
         self.graphs = None
 
     def enable_graphs(self) -> None:
-        """Decode-only steps (one token per request, logits wanted for each) are replayed from
-        CUDA graphs from now on; the logits tensor such a step returns is reused by the next
-        graph step of the same batch size."""
-        from pylon_b200.engine.graphs import DecodeGraphs
+        """Steps of the shapes a scheduler makes are replayed from CUDA graphs from now on: decode-only steps (one token
+        per request, logits wanted for each) from a graph of their exact batch size, steps that bring prompt portions from a
+        graph of the next larger captured size, padded.  The logits tensor such a step returns is reused by the next step
+        that replays the same graph."""
+        from pylon_b200.engine.graphs import StepGraphs
 
-        self.graphs = DecodeGraphs(self)
+        self.graphs = StepGraphs(self)
 
     # -- host side ---------------------------------------------------------------------
     def fill(self, entries: Sequence[StepEntry], layout: StepLayout, buffer: np.ndarray) -> tuple[int, int]:
@@ -109,6 +110,54 @@ class StepFunction:
             base = off[f"block_table_{g}"]
             buffer[base : base + table.size] = table.reshape(-1)
         return max_q, max_kv
+
+    def fill_padded(self, ones: Sequence[StepEntry], portions: Sequence[StepEntry], order: Sequence[StepEntry], layout: StepLayout,
+                    buffer: np.ndarray, one_rows: int) -> None:
+        """The arrays of a step padded to a captured size (see ``StepView.padded``): rows ``[0, one_rows)`` are for the
+        entries that bring one token (``ones``; the rows beyond them have no tokens), rows ``[one_rows, layout.rows)`` for
+        the others (``portions``; likewise); the tokens of all of them lie side by side and padding tokens follow.  Logits
+        are asked for in the order of ``order`` (the caller's entries), at the last token of each entry that wants any."""
+        off = layout.offsets
+        for name in ("token_ids", "positions"):
+            buffer[off[name] : off[name] + layout.tokens] = 0
+        buffer[off["token_row"] : off["token_row"] + layout.tokens] = -1
+        for name in ("kv_len", "slots"):
+            buffer[off[name] : off[name] + layout.rows] = 0
+        buffer[off["logit_rows"] : off["logit_rows"] + max(1, layout.logits)] = 0
+        last_token: dict[int, int] = {}
+        cursor = 0
+        starts = np.zeros(layout.rows + 1, dtype=np.int32)
+        placed: list[Optional[StepEntry]] = [None] * layout.rows
+        for row, entry in list(enumerate(ones)) + [(one_rows + index, entry) for index, entry in enumerate(portions)]:
+            placed[row] = entry
+        for row in range(layout.rows):
+            starts[row] = cursor
+            entry = placed[row]
+            if entry is None:
+                continue
+            count, start = len(entry.tokens), entry.request.length
+            buffer[off["token_ids"] + cursor : off["token_ids"] + cursor + count] = entry.tokens
+            buffer[off["positions"] + cursor : off["positions"] + cursor + count] = np.arange(start, start + count, dtype=np.int32)
+            buffer[off["token_row"] + cursor : off["token_row"] + cursor + count] = row
+            buffer[off["kv_len"] + row] = start + count
+            buffer[off["slots"] + row] = entry.request.slot
+            cursor += count
+            last_token[id(entry)] = cursor - 1
+        starts[layout.rows] = cursor
+        buffer[off["q_start"] : off["q_start"] + layout.rows + 1] = starts
+        wanted = 0
+        for entry in order:
+            if entry.want:
+                buffer[off["logit_rows"] + wanted] = last_token[id(entry)]
+                wanted += 1
+        for g, width in enumerate(layout.table_widths):
+            table = np.full((layout.rows, width), -1, dtype=np.int32)
+            for row, entry in enumerate(placed):
+                if entry is not None:
+                    pages = entry.request.tables[g]
+                    table[row, : len(pages)] = pages
+            base = off[f"block_table_{g}"]
+            buffer[base : base + table.size] = table.reshape(-1)
 
     @staticmethod
     def rows_alike(entries: Sequence[StepEntry]) -> bool:
@@ -169,7 +218,7 @@ class StepFunction:
         try:
             saved_state = self.cache.save_state([request for request, _ in batch])   # None for models without state
             logits = None
-            if self.graphs is not None and self.graphs.applies(entries):
+            if self.graphs is not None:
                 logits = self.graphs.run(entries)
             if logits is None:
                 logits = self._run_eager(entries)

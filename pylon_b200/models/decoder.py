@@ -74,6 +74,10 @@ class DecoderModel:
             total += self.blocks[run.layer].weight_bytes()
         return total
 
+    def takes_padding(self) -> bool:
+        """Whether every layer that runs is right for steps padded to the size of a captured graph."""
+        return all(self.blocks[run.layer].takes_padding for run in self.spec.order)
+
     # -- cache ---------------------------------------------------------------------------
     def cache_needs(self) -> list[Optional[CacheNeed]]:
         """Per run of the order: what its mixer keeps between steps (``None`` where the run

@@ -22,6 +22,8 @@ from pylon_b200.parts.spec import PartSpec
 
 @MIXERS.register("gqa_attention")
 class GroupedQueryAttention(Mixer):
+    takes_padding = True   # the kernels skip tokens without a row and rows without tokens
+
     def __init__(
         self,
         width: int,

@@ -118,6 +118,12 @@ class StepView:
     rows_alike: the requests of the step hold about equally many tokens (within an eighth of the
     longest), so that work dealt out evenly by row is dealt out evenly; a hint, never needed for
     a right result.
+    padded: the step was padded to the size of a captured CUDA graph.  It may then hold rows
+    without tokens (``q_start[r + 1] == q_start[r]``, ``kv_len[r] == 0``, no pages) and, after
+    the last row's tokens, padding tokens that belong to no row: ``token_row[t] == -1``, position
+    0.  Whatever a part computes for a padding token is never read; it must keep nothing of it
+    (no cache write, no state update).  Only models whose parts all say ``takes_padding`` get
+    such steps.
     """
 
     token_ids: torch.Tensor
@@ -136,6 +142,7 @@ class StepView:
     device: torch.device
     row_tokens: Optional[tuple] = None
     rows_alike: bool = False
+    padded: bool = False
 
 
 # ---------------------------------------------------------------------------------------
@@ -175,6 +182,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if ``forward`` is right for a padded step (see :class:`StepView`): rows without tokens, tokens without a
+    # row.  A mixer that indexes its cache or state by ``token_row`` has to look at this; so the default is False, and
+    # a model with such a mixer is never padded.
+    takes_padding = False
+
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
@@ -184,6 +196,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # A feed-forward works token by token, so padding tokens are usually no concern; one that looks across tokens (a
+    # router that balances its load over the batch, say) sets this to False.
+    takes_padding = True
+
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
         """Returns the delta for the residual stream (see :class:`ResidualStream`)."""
         raise NotImplementedError
@@ -192,6 +208,10 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
     feed_forward: FeedForward
+
+    @property
+    def takes_padding(self) -> bool:
+        return bool(self.mixer.takes_padding and self.feed_forward.takes_padding)
 
     def forward(self, stream: "ResidualStream", step: StepView, cache: LayerCache) -> None:
         raise NotImplementedError

@@ -86,6 +86,48 @@ def test_decode_steps_replayed_from_cuda_graphs(name, cutting, dtype, tiny_folde
     assert (graphs.captured or graphs.captured_alike) and not graphs.failed
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB", "tinyC"])
+def test_steps_with_portions_replayed_from_padded_graphs(name, dtype, tiny_folders, expected):
+    """Steps as a scheduler makes them (logits wanted at the last token of an entry, or nowhere) that bring prompt
+    portions are padded to a captured size and replayed from its graph: rows without tokens, tokens without a row.  The
+    logits must be the plain implementation's, and the same sizes must come from the same graph again."""
+    from pylon_b200.engine import StepEntry
+
+    requests = make_requests(name)
+    steps = trace_tools.mixed(requests, seed=7, max_portion=40)
+    engine = make_engine(tiny_folders[name], name, dtype, steps, cuda_graphs=True)
+    graphs = engine.step_function.graphs
+    at_once = name != "tinyC"
+    graphs.capture_at_once = at_once    # a size is captured when it comes up (else: when it comes back), so that more steps are replays
+    live, cursor = {}, {rid: 0 for rid in requests}
+    for number, step in enumerate(steps):
+        entries, places = [], []
+        for item in step["entries"]:
+            rid, count = item["id"], len(item["tokens"])
+            if rid not in live:
+                live[rid] = engine.open(rid, engine.max_context)
+            wants = number % 3 != 0 or count == 1     # every third step, portions ask for nothing
+            entries.append(StepEntry(live[rid], item["tokens"], (count - 1,) if wants else ()))
+            if wants:
+                places.append((rid, cursor[rid] + count - 1))
+            cursor[rid] += count
+        logits = engine.step(entries)
+        assert (logits is None) == (not places)
+        if places:
+            got = logits.float().cpu().numpy()
+            assert got.shape[0] == len(places)
+            for row, (rid, position) in enumerate(places):
+                np.testing.assert_allclose(got[row], expected[name][rid][position], err_msg=f"step {number} {rid} position {position}", **TOLERANCE[dtype])
+        for rid in step["end"]:
+            engine.close(live.pop(rid))
+    engine.cache.check()
+    assert graphs.replays["padded"] > (10 if at_once else 3) and graphs.replays["decode"] > 0 and not graphs.failed
+    assert len(graphs.captured_padded) < graphs.replays["padded"]    # sizes came back and were replayed, not captured again
+    if not at_once:
+        assert all(count >= 2 for key, count in graphs.seen_padded.items() if key in graphs.captured_padded)
+
+
 @pytest.mark.parametrize("name", ["tinyA", "tinyB"])
 def test_cuttings_agree_with_each_other_in_float32(name, tiny_folders):
     """Beyond agreeing with the oracle: in 32-bit the cuttings agree with each other far

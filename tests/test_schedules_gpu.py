@@ -266,6 +266,9 @@ def test_a_run_the_scheduler_cuts(dtype, graphs, tmp_path_factory):
                                          prefill_chunk_size=48, cuda_graphs=graphs))
     results = engine.generate(prompts, SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True))
     assert engine.scheduler.ticks > 40
+    if graphs:   # the ticks that brought prompt portions were padded to captured sizes and replayed
+        replays = engine.step_function.graphs.replays
+        assert replays["padded"] > 10 and replays["decode"] > 0 and not engine.step_function.graphs.failed
     spread = None
     for prompt, result in zip(prompts, results):
         assert result.error is None and len(result.output_ids) == new_tokens and result.prompt_tokens == len(prompt)
