@@ -328,7 +328,7 @@ def time_prefill(engine, torch, repeats: int, rng) -> dict:
     return {"ms": best}
 
 
-def profile_steps(engine, torch, ops, kind: str, batch: int, rng) -> None:
+def profile_steps(engine, torch, ops, kind: str, batch: int, rng, prompt_tokens: int = PREFILL_TOKENS) -> None:
     """Warm up, then run two steps of ``kind`` inside the profiler's range (eagerly, so that a
     profiler sees every kernel as its own launch)."""
     from pylon_b200.engine import StepEntry
@@ -346,9 +346,9 @@ def profile_steps(engine, torch, ops, kind: str, batch: int, rng) -> None:
         counter = [0]
 
         def step():
-            request = engine.open(("profile", counter[0]), PREFILL_TOKENS)
+            request = engine.open(("profile", counter[0]), prompt_tokens)
             counter[0] += 1
-            engine.step([StepEntry(request, rng.integers(0, vocab, size=PREFILL_TOKENS).tolist(), (PREFILL_TOKENS - 1,))])
+            engine.step([StepEntry(request, rng.integers(0, vocab, size=prompt_tokens).tolist(), (prompt_tokens - 1,))])
             torch.cuda.synchronize()
             engine.close(request)
     for _ in range(3):
@@ -359,7 +359,7 @@ def profile_steps(engine, torch, ops, kind: str, batch: int, rng) -> None:
         step()
     torch.cuda.synchronize()
     torch.cuda.cudart().cudaProfilerStop()
-    print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {CONTEXT}")
+    print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {CONTEXT}, prompt of {prompt_tokens} tokens")
 
 
 def run_serving_workload(name: str, torch) -> dict:
@@ -486,6 +486,7 @@ def main() -> int:
                         help="decode4b: the headline measurement (default); the others are the serving workloads of the 8B and 14B shapes")
     parser.add_argument("--profile", choices=["decode", "prefill"],
                         help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    parser.add_argument("--profile-tokens", type=int, default=PREFILL_TOKENS, help="with --profile prefill: tokens of the prompt")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -522,7 +523,7 @@ def main() -> int:
         )
     engine = Engine(None, engine_config, device="cuda:0", model_config=model_config, random_seed=0)
     if args.profile:
-        profile_steps(engine, torch, ops, args.profile, args.batch, rng)
+        profile_steps(engine, torch, ops, args.profile, args.batch, rng, args.profile_tokens)
         return 0
     peak = peaks()
 
