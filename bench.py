@@ -328,14 +328,14 @@ def time_prefill(engine, torch, repeats: int, rng) -> dict:
     return {"ms": best}
 
 
-def profile_steps(engine, torch, ops, kind: str, batch: int, rng, prompt_tokens: int = PREFILL_TOKENS) -> None:
+def profile_steps(engine, torch, ops, kind: str, batch: int, rng, prompt_tokens: int = PREFILL_TOKENS, context: int = CONTEXT) -> None:
     """Warm up, then run two steps of ``kind`` inside the profiler's range (eagerly, so that a
     profiler sees every kernel as its own launch)."""
     from pylon_b200.engine import StepEntry
 
     vocab = engine.spec.vocab_size
     if kind == "decode":
-        requests = fill_caches(engine, torch, batch, CONTEXT - 8, rng, PREFILL_TOKENS)
+        requests = fill_caches(engine, torch, batch, context - 8, rng, PREFILL_TOKENS)
         tokens = [1] * batch
 
         def step():
@@ -359,7 +359,7 @@ def profile_steps(engine, torch, ops, kind: str, batch: int, rng, prompt_tokens:
         step()
     torch.cuda.synchronize()
     torch.cuda.cudart().cudaProfilerStop()
-    print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {CONTEXT}, prompt of {prompt_tokens} tokens")
+    print(f"profiled 2 {kind} steps: {engine.spec.order.__len__()} layers, batch {batch}, context {context}, prompt of {prompt_tokens} tokens")
 
 
 def run_serving_workload(name: str, torch) -> dict:
@@ -487,6 +487,7 @@ def main() -> int:
     parser.add_argument("--profile", choices=["decode", "prefill"],
                         help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     parser.add_argument("--profile-tokens", type=int, default=PREFILL_TOKENS, help="with --profile prefill: tokens of the prompt")
+    parser.add_argument("--profile-context", type=int, default=CONTEXT, help="with --profile decode: tokens each request holds")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -523,7 +524,7 @@ def main() -> int:
         )
     engine = Engine(None, engine_config, device="cuda:0", model_config=model_config, random_seed=0)
     if args.profile:
-        profile_steps(engine, torch, ops, args.profile, args.batch, rng, args.profile_tokens)
+        profile_steps(engine, torch, ops, args.profile, args.batch, rng, args.profile_tokens, args.profile_context)
         return 0
     peak = peaks()
 

@@ -1006,6 +1006,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     have = have_following;
   }
   if (!CLUSTER) {
+    if (!waited) grid_dependency_wait();   // a block without a segment: no grid ends before the grid ahead of it has
     publish_and_combine();
     return;
   }

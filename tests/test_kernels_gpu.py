@@ -492,6 +492,39 @@ def test_decode_attention_in_clusters(rows, nkv, group, d, page, window, lengths
     assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0
 
 
+@pytest.mark.parametrize("rows, nkv, group, d, page, lengths", [
+    (64, 8, 4, 128, 256, "equal"),      # 512 pairs of 6 tiles over 444 blocks: nearly every block shares a pair with its neighbour
+    (64, 8, 4, 128, 256, "ragged"),
+    (70, 8, 2, 64, 64, "equal"),
+    (48, 4, 4, 64, 16, "ragged"),       # pages of 16 keys: the gathering form
+    (64, 8, 4, 128, 256, "one_long"),   # one long row among short ones
+    (200, 2, 4, 128, 64, "equal"),
+])
+def test_decode_attention_of_many_short_rows(rows, nkv, group, d, page, lengths):
+    """More (row, KV head) pairs than blocks, each a few tiles long (the decode steps of many requests with short
+    contexts): runs of a few tiles that nearly all end inside a pair, so that nearly every pair is combined from two
+    blocks' partial results; twice in a row, since a call must leave the counters as it found them."""
+    from pylon_b200.kernels import ops
+
+    nq = nkv * group
+    if lengths == "equal":
+        kv_lens = [384 - (i % 2) for i in range(rows)]
+    elif lengths == "ragged":
+        kv_lens = [1 + (97 * i) % 500 for i in range(rows)]
+    else:
+        kv_lens = [5_000] + [100 + (53 * i) % 300 for i in range(rows - 1)]
+    q_lens = [2 if (i % 5 == 2 and kv_lens[i] >= 2 and 2 * group <= 16) else 1 for i in range(rows)]
+    cache = Paged(kv_lens, q_lens, nkv, d, page, torch.bfloat16, seed=rows)
+    fused = torch.randn(cache.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(torch.bfloat16)
+    expected = attention_reference(fused[:, : nq * d].reshape(cache.tokens, nq, d), cache, nq, nkv, d, None, 1.0 / math.sqrt(d))
+    for repeat in range(2):   # the second call finds the counters as the first left them
+        out = ops.paged_attention(fused, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table,
+                                  nq, max(q_lens), max(kv_lens))
+        torch.testing.assert_close(out.double(), expected, rtol=2e-2, atol=2e-2)
+    ops.raise_on_kernel_errors(torch.device(DEVICE))
+    assert int(ops._zeroed_counters(torch.device(DEVICE), "attention", rows * nkv).abs().sum().item()) == 0
+
+
 @pytest.mark.parametrize("mode", ["float32", "bfloat16_mma", "bfloat16_mma_splits"])
 def test_attention_finds_one_far_key_among_hundreds(mode):
     """Random keys would hide a wrong page: here one key far back dominates the softmax,
