@@ -97,6 +97,8 @@ class Qwen3Config:
             raise ConfigError("rope_scaling is not supported")
         if data.get("use_sliding_window", False):
             raise ConfigError("use_sliding_window=true is not supported")
+        if data.get("sliding_window") is not None:   # refused as raun6k/Pylon refuses it (src/pylon/model/config.py:48), whatever use_sliding_window says
+            raise ConfigError(f"sliding_window={data.get('sliding_window')!r} is not supported (Qwen3 dense attends to every earlier token)")
         heads = _positive_int(data, "num_attention_heads")
         hidden = _positive_int(data, "hidden_size")
         if "head_dim" in data and data["head_dim"] is not None:

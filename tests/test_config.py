@@ -37,6 +37,7 @@ def test_head_dim_and_kv_heads_defaults():
     ({"rope_scaling": {"type": "yarn"}}, "rope_scaling"),
     ({"use_sliding_window": True}, "sliding_window"),
     ({"model_type": "llama"}, "model_type"),
+    ({"sliding_window": 4096}, "sliding_window"),
     ({"num_key_value_heads": 4}, "multiple"),
     ({"head_dim": 15}, "even"),
     ({"vocab_size": 0}, "vocab_size"),
