@@ -239,8 +239,9 @@ class Engine:
         return logits
 
     def _checked_sample(self, logits, params, randoms) -> list[int]:
+        ops.queue_error_word_read(self.device)           # behind the step's kernels; arrives with the tokens
         tokens = self.sampler(logits, params, randoms)   # reads the tokens back: the step is done
-        ops.raise_on_kernel_errors(self.device)
+        ops.raise_on_kernel_errors(self.device, queued=True)
         return tokens
 
     def default_stop_ids(self) -> tuple[int, ...]:

@@ -106,17 +106,36 @@ def cache_write_error_word(device: torch.device) -> torch.Tensor:
     return _error_words(device)[3:4]
 
 
-def raise_on_kernel_errors(device: torch.device) -> None:
+_error_word_copies: dict[int, torch.Tensor] = {}   # pinned host copies, filled by queue_error_word_read
+
+
+def queue_error_word_read(device: torch.device) -> None:
+    """Enqueues a copy of the error words into pinned host memory behind the work queued so far, without waiting.  A
+    caller that is about to wait for the stream anyway (to read a step's tokens back) queues this first and looks at
+    the words with ``raise_on_kernel_errors(device, queued=True)`` afterwards: one trip to the device instead of two."""
+    key = _device_index(device)
+    if key not in _error_word_storage:
+        return
+    if key not in _error_word_copies:
+        _error_word_copies[key] = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+    _error_word_copies[key].copy_(_error_word_storage[key], non_blocking=True)
+
+
+def raise_on_kernel_errors(device: torch.device, queued: bool = False) -> None:
     """Reads the error words of ``device`` (a 16-byte copy that waits for the work queued so
-    far) and raises if, since the last call, a kernel gave up one of its bounded waits or met a
-    block table that names a page outside the pool.  The words are cleared, so the next call
-    reports only what happens from now on; and the counters by which the blocks of a decode
-    attention find the last of them are put back to zero, since a block that gave up never
-    took part in the count of the rows it shared, and the next launch must find zeros."""
+    far; with ``queued`` the copy :func:`queue_error_word_read` enqueued, which the caller has
+    waited for since) and raises if, since the last call, a kernel gave up one of its bounded
+    waits or met a block table that names a page outside the pool.  The words are cleared, so
+    the next call reports only what happens from now on; and the counters by which the blocks
+    of a decode attention find the last of them are put back to zero, since a block that gave
+    up never took part in the count of the rows it shared, and the next launch must find zeros."""
     key = _device_index(device)
     if key not in _error_word_storage:
         return   # no kernel that can set them has run
-    words = _error_word_storage[key].cpu().tolist()
+    if queued and key in _error_word_copies:
+        words = _error_word_copies[key].tolist()
+    else:
+        words = _error_word_storage[key].cpu().tolist()
     if any(words):
         _error_word_storage[key].zero_()
         for (index, _purpose), buffer in _counter_buffers.items():

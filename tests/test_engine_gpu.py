@@ -208,8 +208,8 @@ def test_a_decode_step_replays_the_graph_that_fits_its_lengths(tiny_folders):
 def test_a_void_step_fails_its_requests_and_the_engine_goes_on(tiny_folders):
     """A kernel that gives up a bounded wait leaves its error word set and its step's result void.  The engine looks at
     the words before it accepts a step's tokens: the requests of that step fail with the kernel error and give back what
-    they held; requests that come afterwards run as if nothing had happened.  (The word is set from the host, while a step
-    is being sampled: no kernel is made to give up.)"""
+    they held; requests that come afterwards run as if nothing had happened.  (The word is set from the host, right after a
+    step's kernels are queued: no kernel is made to give up.)"""
     from pylon_b200.kernels import ops
     from pylon_b200.sampling import SamplingParams
 
@@ -218,17 +218,24 @@ def test_a_void_step_fails_its_requests_and_the_engine_goes_on(tiny_folders):
     prompts = prompts_for(name)[:2]
     engine = engine_for(tiny_folders[name], name, "float32")
     greedy = SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True)
-    healthy_sampler, calls = engine.sampler, []
+    healthy_step, calls = engine.step_function, []
 
-    class Sampler:
-        def __call__(self, logits, params, randoms):
-            calls.append(len(params))
-            if len(calls) == 2:   # the second sampled step is the void one
+    class Step:
+        """The engine's step function, after whose second sampled step the attention's error word and counters look as
+        a kernel that gave up would have left them."""
+
+        def __call__(self, entries):
+            logits = healthy_step(entries)
+            calls.append(len(entries))
+            if len(calls) == 2:
                 ops.attention_error_word(engine.device).fill_(1)
                 ops._zeroed_counters(engine.device, "attention", 8)[:8] = 3
-            return healthy_sampler(logits, params, randoms)
+            return logits
 
-    engine.sampler = Sampler()
+        def __getattr__(self, name):
+            return getattr(healthy_step, name)
+
+    engine.step_function = Step()
     for prompt in prompts:
         engine.submit(prompt, greedy)
     results = []
@@ -239,7 +246,7 @@ def test_a_void_step_fails_its_requests_and_the_engine_goes_on(tiny_folders):
     engine.cache.check()
     assert engine.cache.free_pages() == [g.pool.num_pages for g in engine.cache.groups] and engine.cache.free_slots() == 4
     assert int(ops._zeroed_counters(engine.device, "attention", 8).abs().sum().item()) == 0
-    engine.sampler = healthy_sampler
+    engine.step_function = healthy_step
     again = engine.generate(prompts, greedy)
     assert [r.output_ids for r in again] == [plain.generate_greedy(cfg, weights, prompt, 5) for prompt in prompts]
 
