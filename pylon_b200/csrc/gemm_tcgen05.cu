@@ -14,7 +14,11 @@
 //               matrix's edge; a lane storing its own row left half-written sectors and cost a
 //               fifth of the time); with SWIGLU the columns hold gate and up values in
 //               alternating groups of 8 and silu(gate) * up is stored, half as wide
-// so the epilogue of one tile overlaps the products of the next.  All waits on mbarriers are
+// so the epilogue of one tile overlaps the products of the next.  Tiles wider than 256 columns (288: nine of them
+// cover the 2,560 columns of an output or down projection, so that 2,048 rows are 144 tiles, one round over 148 SMs,
+// where 160 tiles of 256 columns are a full round and a nearly empty one) take two products per step of k (the tensor
+// core's N ends at 256) and have one accumulator buffer, since two would not fit in tensor memory: their epilogue
+// does not overlap the next tile.  All waits on mbarriers are
 // bounded: a wait that runs out sets an error word for the host and the block winds down
 // (frees its tensor memory and returns) instead of hanging.
 //
@@ -56,12 +60,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
-// Shared memory -> global through a tensor map; the rows and columns outside the matrix are not written.
+// Shared memory -> global through a tensor map; the rows and columns outside the matrix are not written.  The store
+// joins the thread's open bulk group: tma_store_commit() closes it.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
                ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
-  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
 // Until all but the newest `Pending` stores of this thread have read their shared memory.
 template <int Pending>
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(Pending) : "memory"); }
@@ -121,6 +126,10 @@ constexpr int TC_STAGING_BYTES = 4 * 2 * 32 * 128;   // four epilogue warps x tw
 template <int BN>
 struct TcShared {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+  static constexpr int PIECES = BN > 256 ? 2 : 1;            // products (and boxes of B) per step of k: the tensor core's N and a TMA box end at 256
+  static constexpr int PIECE_ROWS = BN / PIECES;
+  static constexpr int ACCUMULATORS = 2 * BN <= 512 ? 2 : 1;  // buffers in tensor memory (512 columns)
+  static_assert(PIECE_ROWS % 16 == 0 && PIECE_ROWS <= 256 && (PIECE_ROWS * 128) % 1024 == 0, "a piece of B must be a valid N and start on a swizzle group");
   static constexpr int FIT = (227 * 1024 - 1024 /* alignment slack */ - 256 /* barriers */ - TC_STAGING_BYTES) / (A_BYTES + B_BYTES);
   static constexpr int STAGES = FIT > 6 ? 6 : FIT;
   static constexpr size_t BYTES = (size_t)STAGES * (A_BYTES + B_BYTES) + TC_STAGING_BYTES + 1024 + 256;
@@ -166,7 +175,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  constexpr int TMEM_COLUMNS = 2 * BN <= 256 ? 256 : 512;   // both accumulator buffers; allocations are powers of two
+  constexpr int ACCUMULATORS = S::ACCUMULATORS;
+  constexpr int TMEM_COLUMNS = ACCUMULATORS * BN <= 256 ? 256 : 512;   // the accumulator buffers; allocations are powers of two
   if (warp == 1) {   // the whole warp allocates
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLUMNS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
@@ -190,19 +200,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
           if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); alive = false; break; }
           mbar_expect_tx(&full[stage], S::A_BYTES + S::B_BYTES);
           tma_load_2d(a_tiles + (size_t)stage * S::A_BYTES, &map_a, &full[stage], kb * TC_BK, m0);
-          tma_load_2d(b_tiles + (size_t)stage * S::B_BYTES, &map_b, &full[stage], kb * TC_BK, n0);
+#pragma unroll
+          for (int piece = 0; piece < S::PIECES; ++piece)
+            tma_load_2d(b_tiles + (size_t)stage * S::B_BYTES + (size_t)piece * S::PIECE_ROWS * 128, &map_b, &full[stage], kb * TC_BK, n0 + piece * S::PIECE_ROWS);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
+      constexpr uint32_t idesc = tc_instr_desc(TC_BM, S::PIECE_ROWS);
       uint32_t stage = 0, phase = 0;
       uint32_t round = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++round) {
-        const uint32_t buffer = round & 1, buffer_phase = (round >> 1) & 1;
+        const uint32_t buffer = round % ACCUMULATORS, buffer_phase = (round / ACCUMULATORS) & 1;
         if (!mbar_wait(&acc_empty[buffer], buffer_phase ^ 1)) { atomicExch(error, 2); break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buffer * BN;
@@ -213,7 +225,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
           const uint64_t b_desc = tc_smem_desc(b_tiles + (size_t)stage * S::B_BYTES);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k)   // 16 k-values = 32 bytes further along the swizzled row: +2 in 16-byte units
-            tc_mma(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int piece = 0; piece < S::PIECES; ++piece)   // a piece of B lies PIECE_ROWS rows of 128 bytes further on, its columns of the accumulator likewise
+              tc_mma(tmem_d + piece * S::PIECE_ROWS, a_desc + 2 * k, b_desc + 2 * k + (uint64_t)((piece * S::PIECE_ROWS * 128) >> 4), idesc, (kb | k) != 0 ? 1u : 0u);
           tc_commit(&empty[stage]);   // the stage is free once these products have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -229,7 +243,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
     uint32_t round = 0, staged = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
-      const uint32_t buffer = round & 1, buffer_phase = (round >> 1) & 1;
+      const uint32_t buffer = round % ACCUMULATORS, buffer_phase = (round / ACCUMULATORS) & 1;
       if (!mbar_wait(&acc_full[buffer], buffer_phase)) { atomicExch(error, 3); break; }
       tc_fence_after();
       const int row0 = m0 + quarter * 32;
@@ -268,7 +282,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
         fence_async_shared();   // the writes above, before the TMA engine reads them
         __syncwarp();
         const int out_column = (n0 + c0) / (SWIGLU ? 2 : 1);
-        if (lane == 0 && row0 < M && out_column < out_columns) tma_store_2d(&map_c, stage_rows, out_column, row0);
+        if (lane == 0) {
+          if (row0 < M && out_column < out_columns) tma_store_2d(&map_c, stage_rows, out_column, row0);
+          // A group for every turn of this loop, empty where the rows lie outside the matrix and nothing is stored: the wait
+          // at the loop's head counts groups ("all but the newest have read their buffer"), and a turn without one would let
+          // the turn after it write the buffer that the last real store is still reading.  (Seen with a last row tile
+          // whose lower quarters lie outside the matrix: the tile a block had stored just before it came out wrong in places.)
+          tma_store_commit();
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -341,7 +362,7 @@ static int forced_columns = 0;
 
 }  // namespace pylon
 
-// For measurements: every later product uses tiles of 128 x columns (256, 192, 160 or 128); 0 returns to the choice by size.
+// For measurements: every later product uses tiles of 128 x columns (288, 256, 192, 160 or 128); 0 returns to the choice by size.
 extern "C" int pylon_gemm_tcgen05_force_tile(int columns) {
   pylon::forced_columns = columns;
   return 0;
@@ -365,15 +386,17 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
   const long long tiles_m = (M + TC_BM - 1) / TC_BM;
   int bn = 128;
   long long best = -1;
-  for (int candidate : {256, 192, 160, 128}) {
+  for (int candidate : {288, 256, 192, 160, 128}) {
     if (forced_columns && candidate != forced_columns) continue;
-    if (swiglu && candidate == 160) continue;   // 160 accumulator columns do not divide into stores of 32 output columns
+    if (swiglu && (candidate == 160 || candidate == 288)) continue;   // their accumulator columns do not divide into stores of 32 output columns
     const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
-    const long long cost = ((tiles + sm_count - 1) / sm_count) * (candidate + 16);   // + a per-tile overhead
+    const long long rounds = (tiles + sm_count - 1) / sm_count;
+    long long cost = rounds * (candidate + 16);   // + a per-tile overhead
+    if (candidate > 256) cost += (rounds - 1) * 32;   // one accumulator buffer: the epilogue of a tile holds up the next
     if (best < 0 || cost < best) { best = cost; bn = candidate; }
   }
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, N, K, ldw, bn))
+  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, N, K, ldw, bn > 256 ? bn / 2 : bn))
     PYLON_REFUSE("gemm_tcgen05: the tensor maps could not be made");
   __nv_bfloat16* out = (__nv_bfloat16*)y;
 #define PYLON_TC_CASE(BN_)                                                                                          \
@@ -383,6 +406,7 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
   }
   PYLON_TC_CASE(256) PYLON_TC_CASE(192)
 #undef PYLON_TC_CASE
+  if (bn == 288) return launch_tcgen05<288, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (bn == 160) return launch_tcgen05<160, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);

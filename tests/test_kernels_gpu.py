@@ -162,7 +162,7 @@ def test_tcgen05_gemm(m, n, k):
     assert int(ops.tcgen05_error_word(x.device).item()) == 0
 
 
-@pytest.mark.parametrize("columns", [256, 192, 160, 128])
+@pytest.mark.parametrize("columns", [288, 256, 192, 160, 128])
 def test_tcgen05_gemm_every_tile_width(columns):
     """Each tile width on its own (the choice by size would never take some of them here),
     with edges inside a tile in both directions, plain and with the SwiGLU epilogue, and
@@ -171,7 +171,8 @@ def test_tcgen05_gemm_every_tile_width(columns):
 
     ops.tcgen05_force_tile(columns)
     try:
-        for m, n, k in [(128, 256, 64), (300, 328, 224), (130, 72, 64), (700, 1224, 512)]:
+        # the last: more tiles than SMs at every width, so that blocks take a second tile (with 288 columns: into the one accumulator)
+        for m, n, k in [(128, 256, 64), (300, 328, 224), (130, 72, 64), (700, 1224, 512), (2100, 2560, 320)]:
             x = torch.randn(m, k + 8, device=DEVICE).to(torch.bfloat16)[:, :k]
             w = (torch.randn(n, k + 16, device=DEVICE) * 0.05).to(torch.bfloat16)[:, 8:8 + k]
             torch.testing.assert_close(ops.linear_tcgen05(x, w).double(), x.double() @ w.double().T, rtol=2e-2, atol=2e-2)
@@ -185,6 +186,29 @@ def test_tcgen05_gemm_every_tile_width(columns):
         assert int(ops.tcgen05_error_word(torch.device(DEVICE)).item()) == 0
     finally:
         ops.tcgen05_force_tile(0)
+
+
+@pytest.mark.parametrize("columns", [128, 256, 288])
+def test_tcgen05_gemm_tile_before_a_partly_empty_row_tile(columns):
+    """A last row tile whose lower quarters lie outside the matrix stores nothing for them; the tile a block wrote just
+    before it must still come out whole (its last store may still be reading its buffer when the block moves on).  Few
+    steps of k and several tiles a block make the window wide; two inputs take turns, so that what an earlier call left
+    in shared or tensor memory is never the right answer."""
+    from pylon_b200.kernels import ops
+
+    m, n, k = 4000, 2560, 128
+    xs = [torch.randn(m, k, device=DEVICE).to(torch.bfloat16) for _ in range(2)]
+    ws = [(torch.randn(n, k, device=DEVICE) * 0.05).to(torch.bfloat16) for _ in range(2)]
+    wants = [x.float() @ w.float().T for x, w in zip(xs, ws)]
+    ops.tcgen05_force_tile(columns)
+    try:
+        for turn in range(40):
+            got = ops.linear_tcgen05(xs[turn % 2], ws[turn % 2])
+            wrong = (got.float() - wants[turn % 2]).abs() > 0.1
+            assert not bool(wrong.any()), f"turn {turn}: {int(wrong.sum())} values off, rows {sorted(set((torch.nonzero(wrong)[:, 0] // 32).tolist()))[:8]} (groups of 32)"
+    finally:
+        ops.tcgen05_force_tile(0)
+    assert int(ops.tcgen05_error_word(torch.device(DEVICE)).item()) == 0
 
 
 @pytest.mark.parametrize("m, inter, k", [(128, 128, 64), (2048, 9728, 2560), (130, 104, 96), (500, 224, 96)])
