@@ -86,16 +86,16 @@ def test_decode_steps_replayed_from_cuda_graphs(name, cutting, dtype, tiny_folde
     assert (graphs.captured or graphs.captured_alike) and not graphs.failed
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype, seed", [("float32", 7), ("bfloat16", 7), ("bfloat16", 8), ("bfloat16", 9)])
 @pytest.mark.parametrize("name", ["tinyA", "tinyB", "tinyC"])
-def test_steps_with_portions_replayed_from_padded_graphs(name, dtype, tiny_folders, expected):
+def test_steps_with_portions_replayed_from_padded_graphs(name, dtype, seed, tiny_folders, expected):
     """Steps as a scheduler makes them (logits wanted at the last token of an entry, or nowhere) that bring prompt
     portions are padded to a captured size and replayed from its graph: rows without tokens, tokens without a row.  The
     logits must be the plain implementation's, and the same sizes must come from the same graph again."""
     from pylon_b200.engine import StepEntry
 
     requests = make_requests(name)
-    steps = trace_tools.mixed(requests, seed=7, max_portion=40)
+    steps = trace_tools.mixed(requests, seed=seed, max_portion=40 if seed == 7 else 90)
     engine = make_engine(tiny_folders[name], name, dtype, steps, cuda_graphs=True)
     graphs = engine.step_function.graphs
     at_once = name != "tinyC"
@@ -122,8 +122,10 @@ def test_steps_with_portions_replayed_from_padded_graphs(name, dtype, tiny_folde
         for rid in step["end"]:
             engine.close(live.pop(rid))
     engine.cache.check()
-    assert graphs.replays["padded"] > (10 if at_once else 3) and graphs.replays["decode"] > 0 and not graphs.failed
-    assert len(graphs.captured_padded) < graphs.replays["padded"]    # sizes came back and were replayed, not captured again
+    assert graphs.replays["padded"] > ((10 if at_once else 3) if seed == 7 else 0) and not graphs.failed
+    if seed == 7:
+        assert graphs.replays["decode"] > 0
+        assert len(graphs.captured_padded) < graphs.replays["padded"]    # sizes came back and were replayed, not captured again
     if not at_once:
         assert all(count >= 2 for key, count in graphs.seen_padded.items() if key in graphs.captured_padded)
 
