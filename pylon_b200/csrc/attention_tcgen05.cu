@@ -9,19 +9,23 @@
 //   warps 0..3  softmax: thread i owns row i, which is lane i of tensor memory.  It reads its
 //               64 scores with tcgen05.ld, scales and masks them, keeps the running maximum
 //               and sum in float32 (no shuffles: a row is one thread), writes the weights as
-//               bfloat16 into shared memory in the layout the tensor core reads (128-byte
-//               swizzle), and at the end divides the output row by its sum and stores it.
+//               bfloat16 back into tensor memory over the scores it has read (tcgen05.st, two
+//               weights to a column), and at the end divides the output row by its sum and
+//               stores it.
 //   warp 4      TMA producer: keys and values of a tile as 64 x 64 boxes into a two-stage ring
 //   warp 5      MMA issuer: S = Q K^T (tcgen05.mma, M 128, N 64, accumulator in tensor memory,
 //               two score buffers so that the scores of tile t + 1 are computed while tile t
-//               goes through the softmax), then O += P V (M 128, N = head size; V is read
-//               straight from its [key][value] tile as the MN-major operand)
+//               goes through the softmax), then O += P V (M 128, N = head size; the weights are
+//               the A operand, read from tensor memory; V is read straight from its [key][value]
+//               tile as the MN-major operand).  The weights never touch shared memory, which the
+//               operand reads of the N = 64 products keep busy as it is, and no softmax thread
+//               waits for the weights' buffer to come free: 504 against 529 us at 8,192 tokens.
 // The output accumulator stays in tensor memory.  When a row's maximum grows, the row is
 // rescaled there (tcgen05.ld, multiply, tcgen05.st) - but only when it grew by more than 2^8:
 // up to that, the old maximum stays the reference point, which changes nothing in exact
 // arithmetic and keeps every weight below 256.
 //
-// Two blocks fit on an SM (shared memory 112 KB, tensor memory 256 columns each), so one
+// Two blocks fit on an SM (shared memory 96 KB, tensor memory 256 columns each), so one
 // block's softmax overlaps the other's products.  All waits on mbarriers are bounded: a wait
 // that runs out sets an error word for the host and every role winds down (tensor memory is
 // freed) instead of hanging.  No TMA load here uses cluster multicast.
@@ -46,10 +50,9 @@ static_assert(D == 64 || D == 128, "the tcgen05 attention is built for head size
 constexpr int FA_BM = 128, FA_BN = 64, FA_STAGES = 2, FA_THREADS = 192;
 constexpr int FA_SMALL_ROWS = 16;                  // rows with at most this many packed query rows belong to the decode kernel
 constexpr int FA_Q_BYTES = FA_BM * D * 2;          // D / 64 panels of [128 rows][64 values]
-constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;      // [128 rows][64 keys]
 constexpr int FA_TILE_BYTES = FA_BN * D * 2;       // keys or values of one tile: D / 64 boxes of [64 keys][64 values]
 constexpr int FA_STAGE_BYTES = 2 * FA_TILE_BYTES;
-constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_P_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers: 13 x 8 bytes and the tensor-memory address */;
+constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers: 14 x 8 bytes and the tensor-memory address */;
 // At least 80 KB: never more than two blocks on an SM, so that their 2 x 256 columns of tensor memory always fit and no
 // block waits in tcgen05.alloc for another to finish.
 constexpr size_t FA_SMEM = FA_SMEM_USED > 80 * 1024 ? FA_SMEM_USED : 80 * 1024;
@@ -135,6 +138,21 @@ __device__ __forceinline__ void fa_tmem_store_32(unsigned taddr, const unsigned 
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
+// The product with the A operand in tensor memory (the weights) and B through a shared-memory descriptor.
+__device__ __forceinline__ void fa_mma_a_tmem(unsigned tmem_d, unsigned tmem_a, uint64_t b_desc, unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane; the caller waits for the stores.
+__device__ __forceinline__ void fa_tmem_store_16(unsigned taddr, const unsigned* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void fa_tmem_wait_stores() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -170,16 +188,19 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
                                                                            const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_tile = smem;
-  unsigned char* p_tile = q_tile + FA_Q_BYTES;
-  unsigned char* stages = p_tile + FA_P_BYTES;
+  unsigned char* stages = q_tile + FA_Q_BYTES;
   uint64_t* k_full = reinterpret_cast<uint64_t*>(stages + FA_STAGES * FA_STAGE_BYTES);   // [2] the keys of a tile have landed
   uint64_t* k_empty = k_full + 2;      // [2] ... and are read (their scores are computed)
   uint64_t* v_full = k_empty + 2;      // [2] the same for the values
   uint64_t* v_empty = v_full + 2;      // [2]
   uint64_t* s_full = v_empty + 2;      // [2] scores of a tile are in tensor memory
-  uint64_t* p_full = s_full + 2;       // weights of a tile are in shared memory (and the scores read)
-  uint64_t* pv_done = p_full + 1;      // the weighted sum of a tile is added: the weights' buffer is free
-  uint64_t* q_full = pv_done + 1;      // the query tile is in shared memory
+  uint64_t* p_full = s_full + 2;       // weights of a tile are in tensor memory, over its scores (and the output rescaled)
+  // [2] the weighted sum of tile t is added to the output: barrier t % 2.  A softmax thread waits for it only when it has
+  // to (a row to rescale; the end), and a wait by parity can tell a phase only from its neighbours: with one barrier a
+  // thread that skipped two tiles' waits would take the phase before last for the one it asks for.  With two, the phase
+  // before (tile t - 2) is always complete when tile t's scores are: the products run in the order they were issued.
+  uint64_t* pv_done = p_full + 1;
+  uint64_t* q_full = pv_done + 2;      // the query tile is in shared memory
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_full + 1);
 
   const int row = p.first_row + blockIdx.y, kv_head = blockIdx.x;
@@ -215,7 +236,8 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       fa_mbar_init(&s_full[s], 1);
     }
     fa_mbar_init(p_full, 128);
-    fa_mbar_init(pv_done, 1);
+    fa_mbar_init(&pv_done[0], 1);
+    fa_mbar_init(&pv_done[1], 1);
     fa_mbar_init(q_full, 128);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -281,12 +303,11 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         const unsigned char* v_tile = stages + (t & 1) * FA_STAGE_BYTES + FA_TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < FA_BN / 16; ++kk) {   // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) down V
-          const uint64_t a = fa_desc(p_tile, 16, 1024) + 2 * kk;
           const uint64_t b = fa_desc(v_tile + kk * 2048, FA_BN * 128, 1024);
-          fa_mma(tmem_base + FA_O_COLUMN, a, b, idesc_o, (t | kk) != 0 ? 1u : 0u);
+          fa_mma_a_tmem(tmem_base + FA_O_COLUMN, tmem_base + (t & 1) * FA_S_COLUMNS + kk * 8, b, idesc_o, (t | kk) != 0 ? 1u : 0u);
         }
         fa_commit(&v_empty[t & 1]);
-        fa_commit(pv_done);
+        fa_commit(&pv_done[t & 1]);
       };
       if (alive) {
         alive = fa_mbar_wait(&k_full[0], 0);
@@ -376,25 +397,23 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         packed[j / 2] = fa_pack(w0, w1);
       }
       sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
-      // The weights' buffer and the output are free once the tile before this one is added up.
-      if (t > 0) {
-        if (!fa_mbar_wait(pv_done, (t - 1) & 1)) { atomicExch(p.error, 3); alive = false; break; }
+      // The weights go into tensor memory over this tile's scores, two to a column (this lane's scores are in registers
+      // and nothing else reads these columns before the weighted sum).  The output may be rescaled once the tile before
+      // this one is added up: only then is that product waited for.
+      if (t > 0 && __any_sync(0xffffffffu, move)) {   // tcgen05.ld/st are warp-wide: rows that stay multiply by one
+        if (!fa_mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) { atomicExch(p.error, 3); alive = false; break; }
         fa_fence_after();
-        if (__any_sync(0xffffffffu, move)) {   // tcgen05.ld/st are warp-wide: rows that stay multiply by one
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            unsigned raw[32];
-            fa_tmem_load_32(lane_base + FA_O_COLUMN + c * 32, raw);
+        for (int c = 0; c < D / 32; ++c) {
+          unsigned raw[32];
+          fa_tmem_load_32(lane_base + FA_O_COLUMN + c * 32, raw);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) * alpha);
-            fa_tmem_store_32(lane_base + FA_O_COLUMN + c * 32, raw);
-          }
+          for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) * alpha);
+          fa_tmem_store_32(lane_base + FA_O_COLUMN + c * 32, raw);
         }
       }
-#pragma unroll
-      for (int c = 0; c < FA_BN / 8; ++c)
-        *reinterpret_cast<uint4*>(p_tile + r * 128 + ((c ^ (r & 7)) << 4)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      fa_tmem_store_16(lane_base + (t & 1) * FA_S_COLUMNS, packed);
+      fa_tmem_store_16(lane_base + (t & 1) * FA_S_COLUMNS + 16, packed + 16);
       if (key0 + FA_BN > kv_len) {
         // Keys past the row's length are masked, but their values (whatever the page held) still meet a weight of zero in
         // the product: make them zero, once they have landed.
@@ -406,12 +425,13 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
           if (key >= first_unused)
             *reinterpret_cast<uint4*>(v_tile + (unit / 8) * (FA_BN * 128) + key * 128 + (((unit % 8) ^ (key & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
         }
+        fa_fence_async_shared();   // the zeroed values, before the tensor core reads them
       }
-      fa_fence_async_shared();   // the weights (and zeroed values), before the tensor core reads them
+      fa_tmem_wait_stores();
       fa_fence_before();
       fa_mbar_arrive(p_full);
     }
-    if (alive && !fa_mbar_wait(pv_done, (num_tiles - 1) & 1)) { atomicExch(p.error, 3); alive = false; }
+    if (alive && !fa_mbar_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) { atomicExch(p.error, 3); alive = false; }
     if (alive) {
       fa_fence_after();
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
