@@ -150,6 +150,42 @@ def fill_caches(engine, torch, batch: int, tokens_each: int, rng, chunk: int):
     return requests
 
 
+class DecodeLoop:
+    """Decoding as the engine's scheduler does it when it runs ahead: a step takes its tokens on the device from what the
+    sampling kernel chose in the step before, it is queued behind that step, and only then are that step's tokens read
+    back to the host.  Every step's tokens do come back, one step late; ``tokens`` are the latest that have."""
+
+    def __init__(self, engine, requests, tokens: list[int]) -> None:
+        from pylon_b200.sampling.sampler import Sampler
+
+        self.engine, self.requests, self.tokens = engine, requests, tokens
+        self.sampler = Sampler(engine.device)
+        self.flying = None
+        self.greedy = None
+
+    def step(self) -> None:
+        from pylon_b200.engine import StepEntry
+        from pylon_b200.sampling import SamplingParams
+
+        if self.greedy is None:
+            self.greedy = [SamplingParams(temperature=0.0)] * len(self.requests)
+        if self.flying is None or not self.engine.config.run_ahead:
+            entries = [StepEntry(request, [token], (0,)) for request, token in zip(self.requests, self.tokens)]
+        else:
+            entries = [StepEntry(request, [0], (0,), (self.flying.device, row)) for row, request in enumerate(self.requests)]
+        launched = self.sampler.launch(self.engine.step(entries), self.greedy, [None] * len(self.requests))
+        if self.flying is not None:
+            self.tokens = self.flying.result()
+        self.flying = launched
+        if not self.engine.config.run_ahead:
+            self.finish()
+
+    def finish(self) -> list[int]:
+        if self.flying is not None:
+            self.tokens, self.flying = self.flying.result(), None
+        return self.tokens
+
+
 def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng, repeats: int = 1) -> dict:
     """Decode ``warmup + repeats * steps`` tokens for ``batch`` requests whose contexts end at CONTEXT; each repeat's K
     steps are bracketed by CUDA events on the launching stream.  The figures returned are those of the median repeat."""
@@ -160,22 +196,19 @@ def time_decode(engine, torch, ops, batch: int, steps: int, warmup: int, rng, re
     tokens = rng.integers(0, engine.spec.vocab_size, size=batch).tolist()
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(repeats)]
     windows, launches, kv_tokens = [], [], []
-
-    def step():
-        nonlocal tokens
-        logits = engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])
-        tokens = ops.sample(logits).cpu().tolist()
-
+    loop = DecodeLoop(engine, requests, tokens)
     for _ in range(warmup):
-        step()
+        loop.step()
     for begin, end in events:
+        loop.finish()
         torch.cuda.synchronize()
         before, held = ops.launches[0], 0
         started = time.perf_counter()
         begin.record()
         for _ in range(steps):
             held += sum(request.length + 1 for request in requests)
-            step()
+            loop.step()
+        loop.finish()   # the last step's tokens are back on the host inside the timed region
         end.record()
         torch.cuda.synchronize()
         windows.append((started, time.perf_counter()))
@@ -203,9 +236,10 @@ def time_decode_heavy(engine, torch, ops, batch: int, rng, prompt_tokens: int = 
         group = requests[start : start + 16]
         part = engine.step([StepEntry(request, rng.integers(0, vocab, size=prompt_tokens).tolist(), (prompt_tokens - 1,)) for request in group])
         logits = part if logits is None else torch.cat((logits, part))
-    tokens = ops.sample(logits).cpu().tolist()
+    loop = DecodeLoop(engine, requests, ops.sample(logits).cpu().tolist())
     for _ in range(3):    # the first steps of a size capture its graph and warm up; they count as generated tokens all the same
-        tokens = ops.sample(engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])).cpu().tolist()
+        loop.step()
+    loop.finish()
     steps = new_tokens - 1 - 3
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -213,7 +247,8 @@ def time_decode_heavy(engine, torch, ops, batch: int, rng, prompt_tokens: int = 
     held = 0
     for _ in range(steps):
         held += sum(request.length + 1 for request in requests)
-        tokens = ops.sample(engine.step([StepEntry(request, [token], (0,)) for request, token in zip(requests, tokens)])).cpu().tolist()
+        loop.step()
+    loop.finish()
     end.record()
     torch.cuda.synchronize()
     seconds = begin.elapsed_time(end) / 1e3
@@ -286,7 +321,7 @@ def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
     for _ in range(batch):
         engine.submit(rng.integers(0, vocab, size=prompt_length).tolist(), params)
     scheduler = engine.scheduler
-    while any(r.pending_token is None for r in scheduler.active) or scheduler.waiting or len(scheduler.active) < batch:
+    while any(r.prefilling for r in scheduler.active) or scheduler.waiting or len(scheduler.active) < batch:
         engine.tick()
     for _ in range(warmup):
         engine.tick()
@@ -443,14 +478,14 @@ METRIC = "decode tokens/s, Qwen3-4B shape, batch 8, context 4096"
 REPEATS = 5
 
 
-def headline_config(layers: int, batch: int, cuda_graphs: bool, peak_source: str) -> dict:
+def headline_config(layers: int, batch: int, cuda_graphs: bool, peak_source: str, run_ahead: bool = True) -> dict:
     fields = QWEN3_4B
     return {
         "model": "Qwen3-4B shape", "layers": layers, "layers_of_model": fields["num_hidden_layers"],
         "hidden": fields["hidden_size"], "q_heads": fields["num_attention_heads"], "kv_heads": fields["num_key_value_heads"],
         "head_dim": fields["head_dim"], "intermediate": fields["intermediate_size"], "vocab": fields["vocab_size"],
         "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
-        "parallelism": "single GPU", "cuda_graphs": cuda_graphs, "repeats": REPEATS, "l2": "inputs larger than L2 (8 GB of weights per step)",
+        "parallelism": "single GPU", "cuda_graphs": cuda_graphs, "run_ahead": run_ahead, "repeats": REPEATS, "l2": "inputs larger than L2 (8 GB of weights per step)",
         "peaks": peak_source, "baseline": "Pylon README decode_heavy c=8 on L4 (HTTP end to end)",
     }
 
@@ -559,7 +594,7 @@ def main() -> int:
         "vs_baseline": round(decode["tokens_per_second"] / BASELINE_TOKENS_PER_SECOND, 2),
         "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids, caches filled by real prefill",
-        "config": headline_config(args.layers, args.batch, engine_config.cuda_graphs, peak["source"]),
+        "config": headline_config(args.layers, args.batch, engine_config.cuda_graphs, peak["source"], engine_config.run_ahead),
         "clocks": clocks,
         "e2e": {k: (round(v, 1) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": decode["launches"],

@@ -36,6 +36,7 @@ _ENVIRONMENT: dict[str, tuple[str, Callable[[str], object]]] = {
     "max_gpu_utilization": ("PYLON_MAX_GPU_UTILIZATION", float),
     "cuda_graphs": ("PYLON_CUDA_GRAPHS", _read_switch),
     "admit_skip": ("PYLON_ADMIT_SKIP", int),
+    "run_ahead": ("PYLON_B200_RUN_AHEAD", _read_switch),
 }
 
 
@@ -54,6 +55,7 @@ class EngineConfig:
     max_cache_tokens: Optional[int] = None   # size of the page pool in tokens; None: from free memory
     max_context: Optional[int] = None  # longest request (prompt + new tokens); None: min(model limit, pool)
     seed: int = 0
+    run_ahead: bool = True             # a tick queues its step before it waits for the tokens of the step before (see engine/scheduler.py)
 
     def __post_init__(self) -> None:
         if self.dtype not in _DTYPES:

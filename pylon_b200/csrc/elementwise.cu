@@ -26,6 +26,18 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
 }
 
 // -----------------------------------------------------------------------------------------
+// tokens that the host does not know yet: ids[t] = sampled[source[t]] where source[t] >= 0
+// (the token the sampling kernel chose for that row of the step before, still on the device)
+// -----------------------------------------------------------------------------------------
+__global__ void take_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ sampled,
+                                   int sampled_rows, int num_tokens) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= num_tokens) return;
+  const int from = source[t];
+  if (from >= 0 && from < sampled_rows) ids[t] = sampled[from];
+}
+
+// -----------------------------------------------------------------------------------------
 // residual add + RMSNorm
 //   x = residual[row] (+ delta[row]);  if write_residual: residual[row] = x
 //   out[r] = x / sqrt(mean(x^2) + eps) * weight          (out row r, compact)
@@ -624,6 +636,13 @@ extern "C" int pylon_logit_transform(float* logits, long long n, float scale, fl
   const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
   logit_transform_kernel<<<blocks, threads, 0, stream>>>(logits, (size_t)n, scale, cap);
   PYLON_CHECK_LAUNCH("logit_transform");
+}
+
+extern "C" int pylon_take_tokens(int* ids, const int* source, const int* sampled, int sampled_rows, int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (sampled_rows <= 0) PYLON_REFUSE("take_tokens: %d sampled rows", sampled_rows);
+  take_tokens_kernel<<<(num_tokens + 255) / 256, 256, 0, stream>>>(ids, source, sampled, sampled_rows, num_tokens);
+  PYLON_CHECK_LAUNCH("take_tokens");
 }
 
 extern "C" int pylon_embed_gather(const int* ids, const void* table, float* out, int num_tokens, int width,

@@ -95,9 +95,10 @@ class Engine:
             self.step_function.enable_graphs()
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(
-            self.cache, self._checked_step, self._checked_sample,
+            self.cache, self._checked_step, _CheckedSampler(self.sampler),
             max_batch_size=self.config.max_batch_size, prefill_chunk_size=self.config.prefill_chunk_size,
             max_queue_size=self.config.max_queue_size, admit_skip=self.config.admit_skip, seed=self.config.seed,
+            run_ahead=self.config.run_ahead,
         )
         self._next_id = 0
 
@@ -229,20 +230,14 @@ class Engine:
     def _tick(self) -> list[GenerationResult]:
         return self.scheduler.tick()
 
-    # What the scheduler calls.  A kernel that gave up one of its bounded waits leaves a void result and an error word;
-    # the words are looked at (a 16-byte read) where the device has just been waited for anyway, and inside the
-    # scheduler's own error handling, so that the requests of a void step fail instead of going on with its tokens.
+    # What the scheduler calls (with _CheckedSampler below).  A kernel that gave up one of its bounded waits leaves a void
+    # result and an error word; the words are looked at (a 16-byte read) where the device is waited for anyway, and inside
+    # the scheduler's own error handling, so that the requests of a void step fail instead of going on with its tokens.
     def _checked_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         logits = self.step_function(entries)
         if logits is None:   # nothing will be sampled from this step: look now
             ops.raise_on_kernel_errors(self.device)
         return logits
-
-    def _checked_sample(self, logits, params, randoms) -> list[int]:
-        ops.queue_error_word_read(self.device)           # behind the step's kernels; arrives with the tokens
-        tokens = self.sampler(logits, params, randoms)   # reads the tokens back: the step is done
-        ops.raise_on_kernel_errors(self.device, queued=True)
-        return tokens
 
     def default_stop_ids(self) -> tuple[int, ...]:
         return tuple(self.spec.eos_token_ids)
@@ -291,6 +286,21 @@ class Engine:
         needed = len(prompt) + params.max_new_tokens
         if needed > self.max_context:
             raise ValueError(f"prompt plus max_new_tokens is {needed} tokens; this engine was set up for requests of up to {self.max_context}")
+
+
+class _CheckedSampler:
+    """The sampler as the scheduler uses it: a copy of the kernels' error words is queued behind the step and travels with
+    its tokens; whoever waits for the tokens (at once, or a step later when the scheduler runs ahead) gets the error
+    instead, if the step's result is void."""
+
+    def __init__(self, sampler: Sampler) -> None:
+        self.sampler = sampler
+
+    def launch(self, logits, params, randoms):
+        return self.sampler.launch(logits, params, randoms, check_errors=True)
+
+    def __call__(self, logits, params, randoms) -> list[int]:
+        return self.launch(logits, params, randoms).result()
 
 
 def generate(

@@ -133,10 +133,11 @@ class StepGraphs:
                 gc.enable()
         return CapturedStep(graph, layout, static_buffer, logits, launches)
 
-    def _replay(self, captured: CapturedStep, host: torch.Tensor, kind: str) -> Optional[torch.Tensor]:
+    def _replay(self, captured: CapturedStep, host: torch.Tensor, kind: str, sampled: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         from pylon_b200.kernels import ops
 
         captured.static_buffer.copy_(host, non_blocking=True)
+        self.step_function.take_sampled(captured.static_buffer, captured.layout, sampled)   # tokens the host does not know yet
         captured.graph.replay()
         ops.launches[0] += captured.launches
         self.replays[kind] += 1
@@ -177,7 +178,7 @@ class StepGraphs:
             # the capture itself launched nothing; fall through to the first replay
         host = torch.empty(captured.layout.total, dtype=torch.int32, pin_memory=True)
         self.step_function.fill(entries, captured.layout, host.numpy())
-        return self._replay(captured, host, "decode")
+        return self._replay(captured, host, "decode", self.step_function.sampled_source(entries))
 
     # -- steps with prompt portions: padded to a captured size ------------------------------------
     def padded_size(self, entries: Sequence[StepEntry]) -> tuple[tuple[int, int, int], list[StepEntry], list[StepEntry]]:
@@ -217,7 +218,7 @@ class StepGraphs:
             self.captured_padded[key] = captured
         host = torch.empty(captured.layout.total, dtype=torch.int32, pin_memory=True)
         function.fill_padded(ones, portions, entries, captured.layout, host.numpy(), one_rows)
-        logits = self._replay(captured, host, "padded")
+        logits = self._replay(captured, host, "padded", self.step_function.sampled_source(entries))
         return logits[:wanted] if wanted else None
 
 

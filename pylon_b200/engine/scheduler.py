@@ -21,6 +21,12 @@ Policies follow raun6k/Pylon:
 * tokens (src/pylon/engine.py:598-618): a stop id ends the request (``"eos"``, the stop
   token is not returned); ``max_new_tokens`` outputs end it (``"length"``); the first
   token comes from the step that brings the prompt's last portion.
+* running ahead (this engine's own; the reference waits for every step's tokens before it builds the next,
+  src/pylon/engine.py:454-471): with ``run_ahead`` a tick queues its step behind the one before and only then waits
+  for that one's tokens, so the device never waits for the host.  A decoding request's token for the new step is taken on
+  the device from what the sampling kernel chose in the step before.  The host is one step behind: a request that met a
+  stop id has been given one more step already, whose token is dropped; ``max_new_tokens`` is known beforehand and never
+  overrun.  What a request generates is the same either way.
 * pages: reservations make running out impossible for admitted requests; waiting requests
   wait.  If a step fails all the same (out of pages or any other error), the requests of
   that step fail with the error and give back what they held, the others go on.  (The
@@ -77,8 +83,10 @@ class Request:
     # while active
     cache: Optional[RequestCache] = None
     reservation: list[int] = field(default_factory=list)
-    prompt_offset: int = 0
-    pending_token: Optional[int] = None
+    prompt_offset: int = 0              # prompt tokens handed to steps so far
+    pending_token: Optional[int] = None     # the last token chosen, known here and not yet fed to a step
+    in_flight: Optional[tuple[object, int]] = None   # (sampled tokens of a step not read back yet, row): the same, still on the device
+    launched: int = 0                   # tokens being chosen by steps whose results are not read back yet
     output_ids: list[int] = field(default_factory=list)
     prompt_progress_at: float = 0.0     # when the prompt last got a portion (or was queued)
     admitted_at: float = 0.0
@@ -97,7 +105,36 @@ class Request:
 
     @property
     def prefilling(self) -> bool:
-        return self.pending_token is None and self.prompt_offset < len(self.prompt)
+        return self.pending_token is None and self.in_flight is None and self.prompt_offset < len(self.prompt)
+
+    @property
+    def decoding(self) -> bool:
+        """Has a last token (here or on the device) and room for one more."""
+        return (self.pending_token is not None or self.in_flight is not None) and len(self.output_ids) + self.launched < self.sampling.max_new_tokens
+
+
+class _Known:
+    """Tokens that are there already, in the form of a sampler's ``launch`` result."""
+
+    device = None
+
+    def __init__(self, tokens: Sequence[int]) -> None:
+        self._tokens = list(tokens)
+
+    def result(self) -> list[int]:
+        return self._tokens
+
+
+@dataclass
+class _Launched:
+    """A step that is queued and whose tokens are not accepted yet."""
+
+    selected: list[Request]
+    chunks: list[list[int]]
+    prompt_rows: list[bool]          # by selected request: it brought a portion of its prompt
+    ready: list[Request]             # the requests a token is chosen for, in the order of the tokens
+    tokens: object                   # result() gives them; .device holds them before that
+    started: float
 
 
 class Scheduler:
@@ -114,6 +151,7 @@ class Scheduler:
         free_page_floor: bool = True,
         clock: Callable[[], float] = time.perf_counter,
         seed: int = 0,
+        run_ahead: bool = False,
     ) -> None:
         if max_batch_size < 1 or max_batch_size > cache.max_requests:
             raise ValueError(f"max_batch_size must be between 1 and the cache's {cache.max_requests} request slots")
@@ -123,9 +161,14 @@ class Scheduler:
             raise ValueError("max_queue_size must be at least 1")
         if admit_skip < 0:
             raise ValueError("admit_skip must be an integer of at least 0")
+        if run_ahead and not hasattr(sample, "launch"):
+            raise ValueError("run_ahead needs a sampler with launch(): one that hands out its tokens on the device before the host has them")
         self.cache = cache
         self.run_step = run_step
         self.sample = sample
+        self.run_ahead = run_ahead
+        self._flying: Optional[_Launched] = None    # the step whose tokens are not read back yet
+        self._collected_at = 0.0
         self.max_batch_size = max_batch_size
         self.prefill_chunk_size = prefill_chunk_size
         self.max_queue_size = max_queue_size
@@ -178,7 +221,7 @@ class Scheduler:
         return False
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.active)
+        return bool(self.waiting or self.active or self._flying is not None)
 
     # -- admission -----------------------------------------------------------------------
     def _reserved(self) -> list[int]:
@@ -191,7 +234,7 @@ class Scheduler:
     def _fits(self, request: Request) -> bool:
         reserved = self._reserved()
         needed = self.cache.lifetime_pages(request.capacity, self.prefill_chunk_size)
-        decoding = sum(1 for active in self.active if active.pending_token is not None)
+        decoding = sum(1 for active in self.active if active.pending_token is not None or active.in_flight is not None)
         for g, group in enumerate(self.cache.groups):
             left = group.pool.num_pages - reserved[g] - needed[g]
             if left < 0 or (self.free_page_floor and left < decoding):
@@ -262,65 +305,112 @@ class Scheduler:
 
     def build_step(self) -> tuple[list[Request], list[list[int]]]:
         now = self.clock()
-        decoding = [r for r in self.active if r.pending_token is not None]
+        decoding = [r for r in self.active if r.decoding]
         stalled_since = [r.prompt_progress_at for r in self.active if r.prefilling]
         # every slot decodes: prompts wait, so that the step stays a graph replay, until the oldest runs out of patience
         hold_off = len(decoding) == self.max_batch_size and stalled_since and now - min(stalled_since) < FULL_BATCH_PATIENCE
         portions = [] if hold_off else self._cut_portions(now)
         selected = decoding + [request for request, _ in portions]
-        chunks = [[r.pending_token] for r in decoding] + [tokens for _, tokens in portions]
+        chunks = [[r.pending_token if r.in_flight is None else 0] for r in decoding] + [tokens for _, tokens in portions]   # 0: taken on the device
         return selected, chunks
 
     # -- one tick --------------------------------------------------------------------------
     def tick(self) -> list[GenerationResult]:
-        """Admit, run one step, accept its tokens.  Returns the requests that finished."""
+        """Admit, queue one step, accept tokens: this step's, or with ``run_ahead`` those of the step before.  Returns the
+        requests that finished."""
         self.ticks += 1
         done_before = len(self.finished)
         self.admit()
+        launched = None
         if self.active:
             selected, chunks = self.build_step()
             if selected:
-                self._execute(selected, chunks)
+                launched = self._launch(selected, chunks)
+        if self._flying is not None:   # the step before: the new one is queued behind it, now its tokens are waited for
+            flying, self._flying = self._flying, None
+            self._collect(flying)
+        if launched is not None:
+            if self.run_ahead:
+                self._flying = launched
+            else:
+                self._collect(launched)
         self.admit()
         return self.finished[done_before:]
 
     def run(self) -> list[GenerationResult]:
-        """Ticks until nothing is waiting or active; returns everything that finished."""
+        """Ticks until nothing is waiting, active or in flight; returns everything that finished."""
         start = len(self.finished)
         while self.has_work():
             before = (len(self.waiting), len(self.active), len(self.finished))
             self.tick()
-            if not self.active and self.waiting and before == (len(self.waiting), 0, len(self.finished)):
+            if not self.active and self._flying is None and self.waiting and before == (len(self.waiting), 0, len(self.finished)):
                 raise RuntimeError("a waiting request can never be admitted")   # guarded by add(); defensive
         return self.finished[start:]
 
-    def _execute(self, selected: list[Request], chunks: list[list[int]]) -> None:
-        entries, ready = [], []
+    def _fail_step(self, selected: Sequence[Request], error: BaseException) -> None:
+        """The step's requests fail; the others go on."""
+        logger.error("model_batch_failed requests=%s error=%r", [request.request_id for request in selected], error)
+        for request in selected:
+            if request in self.active:
+                self._finish(request, "error", error)
+
+    def _launch(self, selected: list[Request], chunks: list[list[int]]) -> Optional["_Launched"]:
+        """Queues the step and the choice of its tokens; waits for nothing."""
+        entries, ready, prompt_rows = [], [], []
         for request, chunk in zip(selected, chunks):
-            samples = request.pending_token is not None or request.prompt_offset + len(chunk) >= len(request.prompt)
-            entries.append(StepEntry(request.cache, chunk, (len(chunk) - 1,) if samples else ()))
+            decodes = not request.prefilling
+            samples = decodes or request.prompt_offset + len(chunk) >= len(request.prompt)
+            source = None if request.in_flight is None else (request.in_flight[0].device, request.in_flight[1])
+            entries.append(StepEntry(request.cache, chunk, (len(chunk) - 1,) if samples else (), source))
+            prompt_rows.append(not decodes)
             if samples:
                 ready.append(request)
         self.last_step = [(request.request_id, len(chunk)) for request, chunk in zip(selected, chunks)]
         started = self.clock()
         try:
             logits = self.run_step(entries)
-            tokens = self.sample(logits, [r.sampling for r in ready], [r.random for r in ready]) if ready else []
-        except Exception as error:   # the step's requests fail; the others go on
-            logger.exception("model_batch_failed requests=%s", [request.request_id for request in selected])
-            for request in selected:
-                self._finish(request, "error", error)
+            if not ready:
+                tokens = _Known([])
+            elif hasattr(self.sample, "launch"):
+                tokens = self.sample.launch(logits, [r.sampling for r in ready], [r.random for r in ready])
+            else:
+                tokens = _Known(self.sample(logits, [r.sampling for r in ready], [r.random for r in ready]))
+        except Exception as error:
+            self._fail_step(selected, error)
+            return None
+        for request, chunk, prompt_row in zip(selected, chunks, prompt_rows):
+            if prompt_row:
+                request.prompt_offset += len(chunk)
+        for row, request in enumerate(ready):
+            request.pending_token = None
+            request.in_flight = (tokens, row)
+            request.launched += 1
+        return _Launched(selected, chunks, prompt_rows, ready, tokens, started)
+
+    def _collect(self, step: "_Launched") -> None:
+        """Waits for a queued step's tokens and accepts them."""
+        try:
+            tokens = step.tokens.result()
+        except Exception as error:
+            self._fail_step(step.selected, error)
             return
         now = self.clock()
-        elapsed = now - started
-        for request, chunk in zip(selected, chunks):
-            if request.pending_token is None:
-                request.prompt_offset += len(chunk)
+        elapsed = now - max(step.started, self._collected_at)
+        self._collected_at = now
+        for request, chunk, prompt_row in zip(step.selected, step.chunks, step.prompt_rows):
+            if request not in self.active:
+                continue   # finished (a stop id in the step before, an error, an abort) while this step was in flight
+            if prompt_row:
                 request.prompt_progress_at = now
                 request.prefill_seconds += elapsed
             else:
                 request.inter_token_seconds.append(elapsed)
-        for request, token in zip(ready, tokens):
+        for request, token in zip(step.ready, tokens):
+            if request not in self.active:
+                continue   # likewise: the token is dropped
+            request.launched -= 1
+            if request.in_flight is not None and request.in_flight[0] is step.tokens:
+                request.in_flight = None   # no later step has taken it on the device: it is fed from here
             self._accept(request, int(token), now)
 
     def _accept(self, request: Request, token: int, now: float) -> None:
@@ -334,7 +424,8 @@ class Scheduler:
         if len(request.output_ids) >= request.sampling.max_new_tokens:
             self._finish(request, "length")
             return
-        request.pending_token = token
+        if request.in_flight is None:
+            request.pending_token = token
 
     # -- ending ----------------------------------------------------------------------------
     def _release(self, request: Request) -> None:

@@ -31,6 +31,10 @@ class StepEntry:
     request: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    # (int32 tokens on the device, row): the entry's one token is that one - what the sampling kernel chose for the request
+    # in the step before, not read back yet - and ``tokens`` holds any valid id in its place.  All such entries of a step
+    # name the same tensor.
+    source: Optional[tuple[torch.Tensor, int]] = None
 
 
 def _aligned(count: int) -> int:
@@ -51,7 +55,7 @@ class StepLayout:
     def __post_init__(self) -> None:
         cursor = 0
         sections = [
-            ("token_ids", self.tokens), ("positions", self.tokens), ("token_row", self.tokens),
+            ("token_ids", self.tokens), ("positions", self.tokens), ("token_row", self.tokens), ("token_source", self.tokens),
             ("q_start", self.rows + 1), ("kv_len", self.rows), ("slots", self.rows), ("logit_rows", max(1, self.logits)),
         ] + [(f"block_table_{g}", self.rows * width) for g, width in enumerate(self.table_widths)]
         for name, size in sections:
@@ -96,6 +100,7 @@ class StepFunction:
             buffer[off["token_ids"] + cursor : off["token_ids"] + cursor + count] = entry.tokens
             buffer[off["positions"] + cursor : off["positions"] + cursor + count] = np.arange(start, start + count, dtype=np.int32)
             buffer[off["token_row"] + cursor : off["token_row"] + cursor + count] = row
+            buffer[off["token_source"] + cursor : off["token_source"] + cursor + count] = -1 if entry.source is None else entry.source[1]
             for index in entry.want:
                 buffer[off["logit_rows"] + wanted] = cursor + index
                 wanted += 1
@@ -121,6 +126,7 @@ class StepFunction:
         for name in ("token_ids", "positions"):
             buffer[off[name] : off[name] + layout.tokens] = 0
         buffer[off["token_row"] : off["token_row"] + layout.tokens] = -1
+        buffer[off["token_source"] : off["token_source"] + layout.tokens] = -1
         for name in ("kv_len", "slots"):
             buffer[off[name] : off[name] + layout.rows] = 0
         buffer[off["logit_rows"] : off["logit_rows"] + max(1, layout.logits)] = 0
@@ -139,6 +145,8 @@ class StepFunction:
             buffer[off["token_ids"] + cursor : off["token_ids"] + cursor + count] = entry.tokens
             buffer[off["positions"] + cursor : off["positions"] + cursor + count] = np.arange(start, start + count, dtype=np.int32)
             buffer[off["token_row"] + cursor : off["token_row"] + cursor + count] = row
+            if entry.source is not None:
+                buffer[off["token_source"] + cursor] = entry.source[1]
             buffer[off["kv_len"] + row] = start + count
             buffer[off["slots"] + row] = entry.request.slot
             cursor += count
@@ -166,13 +174,37 @@ class StepFunction:
         lengths = [entry.request.length + len(entry.tokens) for entry in entries]
         return max(lengths) * len(lengths) * 8 <= sum(lengths) * 9
 
+    @staticmethod
+    def sampled_source(entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """The tensor of sampled tokens that entries of the step take their token from, or ``None``."""
+        for entry in entries:
+            if entry.source is not None:
+                return entry.source[0]
+        return None
+
+    def take_sampled(self, device_buffer: torch.Tensor, layout: StepLayout, sampled: Optional[torch.Tensor]) -> None:
+        """After the step's arrays are on the device: the tokens that come from ``sampled`` are put in their places."""
+        if sampled is None:
+            return
+        from pylon_b200.kernels import ops
+
+        off = layout.offsets
+        ops.take_tokens(device_buffer[off["token_ids"] : off["token_ids"] + layout.tokens],
+                        device_buffer[off["token_source"] : off["token_source"] + layout.tokens], sampled)
+
     def validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise ValueError("a step needs at least one entry")
+        sampled = self.sampled_source(entries)
         for entry in entries:
             count = len(entry.tokens)
             if count < 1:
                 raise ValueError(f"request {entry.request.request_id!r} brings no tokens")
+            if entry.source is not None:
+                tensor, row = entry.source
+                if count != 1 or tensor is not sampled or not 0 <= int(row) < tensor.shape[0]:
+                    raise ValueError(f"request {entry.request.request_id!r}: a token taken from the device is one token, a row of the one tensor "
+                                     "of sampled tokens that the step names")
             for token in entry.tokens:
                 if not 0 <= int(token) < self.vocab_size:
                     raise ValueError(f"token id {token} is outside the vocabulary [0, {self.vocab_size})")
@@ -245,6 +277,7 @@ class StepFunction:
         host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
         max_q, max_kv = self.fill(entries, layout, host.numpy())
         device_buffer = host.to(self.device, non_blocking=True)
+        self.take_sampled(device_buffer, layout, self.sampled_source(entries))
         step, tables = self.view(device_buffer, layout, max_q, max_kv)
         step.row_tokens = tuple(len(entry.tokens) for entry in entries)
         step.rows_alike = self.rows_alike(entries)

@@ -121,9 +121,22 @@ def queue_error_word_read(device: torch.device) -> None:
     _error_word_copies[key].copy_(_error_word_storage[key], non_blocking=True)
 
 
-def raise_on_kernel_errors(device: torch.device, queued: bool = False) -> None:
+def queue_error_word_copy(device: torch.device) -> Optional[torch.Tensor]:
+    """Like :func:`queue_error_word_read`, into a pinned buffer of the caller's own (returned; ``None`` if no kernel that
+    can set the words has run): for callers that have more than one step in flight and look at each step's words when
+    they come to it, with ``raise_on_kernel_errors(device, words=...)``."""
+    key = _device_index(device)
+    if key not in _error_word_storage:
+        return None
+    words = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+    words.copy_(_error_word_storage[key], non_blocking=True)
+    return words
+
+
+def raise_on_kernel_errors(device: torch.device, queued: bool = False, words: Optional[torch.Tensor] = None) -> None:
     """Reads the error words of ``device`` (a 16-byte copy that waits for the work queued so
-    far; with ``queued`` the copy :func:`queue_error_word_read` enqueued, which the caller has
+    far; with ``queued`` the copy :func:`queue_error_word_read` enqueued, with ``words`` the one
+    :func:`queue_error_word_copy` returned, which the caller has
     waited for since) and raises if, since the last call, a kernel gave up one of its bounded
     waits or met a block table that names a page outside the pool.  The words are cleared, so
     the next call reports only what happens from now on; and the counters by which the blocks
@@ -132,7 +145,9 @@ def raise_on_kernel_errors(device: torch.device, queued: bool = False) -> None:
     key = _device_index(device)
     if key not in _error_word_storage:
         return   # no kernel that can set them has run
-    if queued and key in _error_word_copies:
+    if words is not None:
+        words = words.tolist()
+    elif queued and key in _error_word_copies:
         words = _error_word_copies[key].tolist()
     else:
         words = _error_word_storage[key].cpu().tolist()
@@ -150,6 +165,7 @@ def raise_on_kernel_errors(device: torch.device, queued: bool = False) -> None:
 _SIGNATURES = {
     "elementwise.cu": {
         "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "pylon_take_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "pylon_logit_transform": [c_void_p, c_longlong, c_float, c_float, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "pylon_residual_add": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
@@ -245,6 +261,18 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
     library = _library("elementwise.cu")
     _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), _stream()))
     return out
+
+
+def take_tokens(ids: torch.Tensor, source: torch.Tensor, sampled: torch.Tensor) -> torch.Tensor:
+    """In place on int32 ``ids [T]``: ``ids[t] = sampled[source[t]]`` wherever ``source[t] >= 0``.  How a step gets tokens
+    that the sampling kernel chose in the step before and the host has not read yet."""
+    _need_cuda(ids, source, sampled)
+    for name, tensor in (("ids", ids), ("source", source), ("sampled", sampled)):
+        _need(tensor.dtype == torch.int32 and tensor.dim() == 1 and tensor.is_contiguous(), f"take_tokens: {name} must be contiguous int32")
+    _need(source.shape[0] >= ids.shape[0], "take_tokens: a source for every token")
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_take_tokens(_ptr(ids), _ptr(source), _ptr(sampled), sampled.shape[0], ids.shape[0], _stream()))
+    return ids
 
 
 def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:

@@ -27,17 +27,45 @@ class RequestRandom:
         return float(self._generator.random(dtype=np.float32))
 
 
+class SampledTokens:
+    """The tokens of one sampling launch: on the device at once (``device``, int32 ``[rows]``, for a next step that
+    takes its tokens from there), on the host when :meth:`result` has waited for them."""
+
+    def __init__(self, device_tokens: torch.Tensor, check_errors: bool) -> None:
+        self.device = device_tokens
+        self.rows = device_tokens.shape[0]
+        self._check_errors = check_errors
+        self._error_words = ops.queue_error_word_copy(device_tokens.device) if check_errors else None   # behind the step's kernels
+        self._host = torch.empty((self.rows,), dtype=torch.int32, pin_memory=True)
+        self._host.copy_(device_tokens, non_blocking=True)
+        self._arrived = torch.cuda.Event()
+        self._arrived.record()
+        self._tokens: Optional[list[int]] = None
+
+    def result(self) -> list[int]:
+        """Waits for the launch (and the step before it) and returns the tokens; raises if a kernel of the step reported
+        that its result is void."""
+        if self._tokens is None:
+            self._arrived.synchronize()
+            if self._error_words is not None:
+                ops.raise_on_kernel_errors(self.device.device, words=self._error_words)
+            self._tokens = self._host.tolist()
+        return self._tokens
+
+
 class Sampler:
     def __init__(self, device: torch.device) -> None:
         self.device = torch.device(device)
 
-    def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[Optional[RequestRandom]]) -> list[int]:
-        """``logits``: float32 ``[rows, vocab]`` on the device; returns one token id per row."""
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[Optional[RequestRandom]],
+               check_errors: bool = False) -> SampledTokens:
+        """``logits``: float32 ``[rows, vocab]`` on the device.  Starts the choice of one token per row and their copy to
+        the host, and returns without waiting.  ``check_errors``: the kernels' error words travel with the tokens."""
         rows = logits.shape[0]
         if rows != len(params) or rows != len(randoms):
             raise ValueError("one set of sampling options and one random stream per row of logits")
         if all(p.greedy for p in params):
-            return ops.sample(logits).cpu().tolist()
+            return SampledTokens(ops.sample(logits), check_errors)
         host = torch.empty((3, rows), dtype=torch.float32, pin_memory=True)
         values = host.numpy()
         for row, (p, random) in enumerate(zip(params, randoms)):
@@ -45,4 +73,8 @@ class Sampler:
             values[1, row] = p.top_p
             values[2, row] = 0.0 if p.greedy or random is None else random.next_uniform()
         device_values = host.to(self.device, non_blocking=True)
-        return ops.sample(logits, device_values[0], device_values[1], device_values[2]).cpu().tolist()
+        return SampledTokens(ops.sample(logits, device_values[0], device_values[1], device_values[2]), check_errors)
+
+    def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[Optional[RequestRandom]]) -> list[int]:
+        """The same, waited for: one token id per row."""
+        return self.launch(logits, params, randoms).result()

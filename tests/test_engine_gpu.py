@@ -94,6 +94,46 @@ def test_one_call_generate_and_stop_ids(tiny_folders):
         engine_module.generate(tiny_folders[name], [[1] * 300], SamplingParams(max_new_tokens=10), config)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["tinyA", "tinyB"])
+def test_running_ahead_generates_the_same_tokens(name, graphs, tiny_folders, dtype="float32"):
+    """With ``run_ahead`` (the default) a tick queues its step before the host has the tokens of the step before, and the
+    decoding requests' tokens are taken on the device; without it every step waits for its tokens.  Greedy requests with a
+    stop id that comes up, and seeded draws, under a small prefill budget: the same outputs either way, and the steps
+    did take tokens from the device.  (In float32, where logits do not depend on what else is in a step: the two ways
+    batch differently, since the host learns of an ending one tick later.  bfloat16 with tokens taken on the device is
+    checked against the plain logits by the test above, which runs ahead by default.)"""
+    from pylon_b200.sampling import SamplingParams
+
+    prompts = prompts_for(name) * 2
+    free_run = engine_for(tiny_folders[name], name, dtype, run_ahead=False).generate(prompts[:1], SamplingParams(max_new_tokens=8, temperature=0.0, ignore_eos=True))
+    stop = free_run[0].output_ids[4]
+    params = [SamplingParams(max_new_tokens=9, temperature=0.0, stop_ids=(stop,)) if index % 2 == 0 else
+              SamplingParams(max_new_tokens=5 + index, temperature=0.8, top_p=0.9, seed=40 + index, ignore_eos=True) for index in range(len(prompts))]
+    outcomes = {}
+    for run_ahead in (False, True):
+        engine = engine_for(tiny_folders[name], name, dtype, run_ahead=run_ahead, cuda_graphs=graphs, prefill_chunk_size=11, max_batch_size=3)
+        healthy_step, taken = engine.step_function, []
+
+        class Step:
+            def __call__(self, entries):
+                taken.append(sum(1 for entry in entries if entry.source is not None))
+                return healthy_step(entries)
+
+            def __getattr__(self, attribute):
+                return getattr(healthy_step, attribute)
+
+        engine.step_function = Step()
+        results = engine.generate(prompts, params)
+        outcomes[run_ahead] = [(r.output_ids, r.finish_reason) for r in results]
+        assert (sum(taken) > 20) == run_ahead
+        engine.cache.check()
+        assert engine.cache.free_pages() == [g.pool.num_pages for g in engine.cache.groups]
+    assert outcomes[True] == outcomes[False]
+    cut = free_run[0].output_ids.index(stop)
+    assert outcomes[True][0] == (free_run[0].output_ids[:cut], "eos")
+
+
 def test_temperature_sampling_does_not_depend_on_batching(tiny_folders):
     """Seeded requests draw the same tokens alone, together, and under a small prefill budget
     (float32, so the logits themselves agree bit for bit)."""

@@ -253,3 +253,128 @@ def test_rows_alike_is_a_matter_of_the_longest_against_the_mean():
     assert not StepFunction.rows_alike(entries((700, 1), (1000, 1)))        # 1001 against a mean of 851
     assert not StepFunction.rows_alike(entries((4000, 1), (10, 1), (10, 1)))
     assert StepFunction.rows_alike(entries((2000, 48), (2047, 1)))           # what a request brings counts as held
+
+
+# -- running ahead: a tick queues its step before it waits for the tokens of the step before --------------------------
+class FakeDeviceTokens:
+    """Stands for the tensor of sampled tokens on the device: the step function may look into it, the scheduler may not."""
+
+    def __init__(self, tokens):
+        self.tokens = list(tokens)
+        self.shape = (len(self.tokens),)
+
+
+class LaunchingSampler:
+    """A sampler with ``launch``: the tokens are 'on the device' at once and reach the host when ``result`` is called.
+    Keeps the order of launches and results in ``events``."""
+
+    def __init__(self, plan, events):
+        self.choose = planned_sampler(plan)
+        self.events = events
+
+    def launch(self, logits, params, randoms):
+        sampler, tokens = self, self.choose(logits, params, randoms)
+        number = sum(1 for event in self.events if event[0] == "launch")
+        self.events.append(("launch", number))
+
+        class Handle:
+            device = FakeDeviceTokens(tokens)
+
+            def result(self):
+                sampler.events.append(("result", number))
+                return tokens
+
+        return Handle()
+
+    def __call__(self, logits, params, randoms):
+        return self.launch(logits, params, randoms).result()
+
+
+class FakeStepWithSources(FakeStep):
+    """Takes the tokens that entries name on the 'device' from there, as the real step function's kernel does."""
+
+    def __call__(self, entries):
+        for entry in entries:
+            if entry.source is not None:
+                tensor, row = entry.source
+                assert len(entry.tokens) == 1
+                entry.tokens = [tensor.tokens[row]]
+        return super().__call__(entries)
+
+
+def make_ahead(plan, run_ahead, num_pages=64, page_size=4, slots=4, **options):
+    cache = CacheManager([CacheNeed(kv=KVNeed(1, 4))], [None], page_size=page_size, num_pages=num_pages, max_requests=slots)
+    events = []
+    step = FakeStepWithSources(cache)
+    options.setdefault("max_batch_size", slots)
+    options.setdefault("free_page_floor", False)
+    scheduler = Scheduler(cache, step, LaunchingSampler(plan, events), clock=FakeClock(), run_ahead=run_ahead, **options)
+    return scheduler, step, events, cache
+
+
+def test_running_ahead_queues_the_next_step_before_it_reads_the_tokens_of_the_last():
+    scheduler, step, events, cache = make_ahead({"a": [50, 51, 52, 53]}, run_ahead=True, prefill_chunk_size=4)
+    scheduler.add("a", list(range(6)), SamplingParams(max_new_tokens=4, temperature=0.0))
+    results = scheduler.run()
+    assert results[0].output_ids == [50, 51, 52, 53] and results[0].finish_reason == "length"
+    # the prompt's two portions, then three decoded tokens, each taken on the device; max_new_tokens is never overrun
+    assert [call[0][1] for call in step.calls] == [[0, 1, 2, 3], [4, 5], [50], [51], [52]]
+    # every result is read after the launch of the step behind it
+    assert events == [("launch", 0), ("launch", 1), ("result", 0), ("launch", 2), ("result", 1), ("launch", 3), ("result", 2), ("result", 3)]
+    assert cache.free_pages() == [64] and cache.free_slots() == 4
+
+
+def test_running_ahead_drops_the_token_of_the_step_behind_a_stop_id():
+    scheduler, step, events, cache = make_ahead({"a": [5, 6, 99, 7, 8], "b": [1, 2, 3, 4, 5, 6]}, run_ahead=True)
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=8, temperature=0.0), stop_ids=[99])
+    scheduler.add("b", [4, 5], SamplingParams(max_new_tokens=6, temperature=0.0))
+    results = {result.request_id: result for result in scheduler.run()}
+    assert results["a"].output_ids == [5, 6] and results["a"].finish_reason == "eos"
+    assert results["b"].output_ids == [1, 2, 3, 4, 5, 6] and results["b"].finish_reason == "length"
+    # a was given one step with its stop id as input (queued before the host had seen it), and none after that
+    fed_to_a = [tokens for call in step.calls for rid, tokens, _ in call if rid == "a"]
+    assert fed_to_a == [[1, 2, 3], [5], [6], [99]]
+    assert cache.free_pages() == [64] and cache.free_slots() == 4
+
+
+def test_a_scheduler_that_runs_ahead_needs_a_sampler_that_launches():
+    cache = CacheManager([CacheNeed(kv=KVNeed(1, 4))], [None], page_size=4, num_pages=8, max_requests=2)
+    with pytest.raises(ValueError, match="launch"):
+        Scheduler(cache, FakeStep(cache), planned_sampler({}), max_batch_size=2, run_ahead=True)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_running_ahead_generates_what_waiting_generates(seed):
+    """Random requests (prompt lengths, limits, stop ids that do and do not come up, arrival ticks) through a tight pool,
+    with and without running ahead: the same output for every request, every page and slot given back, and at most one
+    step more per request."""
+    import random
+
+    rng = random.Random(seed)
+    requests = []
+    for index in range(14):
+        prompt = [rng.randrange(100) for _ in range(rng.randrange(1, 19))]
+        limit = rng.randrange(1, 12)
+        plan = [rng.randrange(100, 120) for _ in range(limit + 2)]
+        requests.append((f"r{index}", prompt, limit, plan, [rng.choice(plan)] if rng.random() < 0.5 else [], rng.randrange(0, 12)))
+    outcomes = {}
+    for run_ahead in (False, True):
+        scheduler, step, events, cache = make_ahead({rid: plan for rid, _, _, plan, _, _ in requests}, run_ahead, num_pages=24, slots=3,
+                                                    prefill_chunk_size=7, max_queue_size=14)
+        waiting = sorted(requests, key=lambda request: request[5])
+        results = {}
+        tick = 0
+        while waiting or scheduler.has_work():
+            while waiting and waiting[0][5] <= tick:
+                rid, prompt, limit, _, stops, _ = waiting.pop(0)
+                scheduler.add(rid, prompt, SamplingParams(max_new_tokens=limit, temperature=0.0), stop_ids=stops)
+            for result in scheduler.tick():
+                results[result.request_id] = (result.output_ids, result.finish_reason)
+            cache.check()
+            tick += 1
+            assert tick < 2_000
+        assert cache.free_pages() == [24] and cache.free_slots() == 3
+        outcomes[run_ahead] = (results, len(step.calls))
+    assert outcomes[True][0] == outcomes[False][0]
+    # the host learns of an ending one tick late, so a slot may stand empty for a tick each time a request ends
+    assert outcomes[True][1] <= outcomes[False][1] + len(requests)
