@@ -50,6 +50,7 @@ struct AttentionParams {
   const int* block_table;
   int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens, num_rows;
   int small_rows_elsewhere;   // rows of at most SMALL_ROWS packed query rows are left to the decode kernel
+  int incoming_rows;          // the cluster form's buffers for partial results hold this many packed query rows
   unsigned* counters;         // [rows * nkv], zero between launches: the last block of a decoded (row, KV head) combines its segments
   int* error;                 // set non-zero when a bounded wait for a TMA copy ran out (the output is then void)
   float scale_log2;     // softmax scale * log2(e)
@@ -383,6 +384,11 @@ constexpr int DEC_STAGES = 2;   // two stages leave room for three blocks per SM
 // an SM at all, and clusters that have to be placed whole on one GPC no longer find room at once: 3.88 ms a step instead of
 // 3.25 at batch 12, 2.75 instead of 2.49 at batch 4 (2.11 instead of 2.14 at batch 1).
 constexpr int DEC_CLUSTER_STAGES = 2;
+// With so few pairs that every block of their 16-block clusters has an SM to itself (one request of eight KV heads), the
+// ring holds three tiles, so that more of a block's old tiles are asked for before the kernel waits for the one ahead of
+// it: 1,975 against 1,990 us a step at one request.  (Four stages, all of a block's tiles at a context of 4,096, take so
+// much shared memory that the output projection's blocks cannot move in beside them and ask for their weights early: 2,215 us.)
+constexpr int DEC_LONE_STAGES = 3;
 
 // Two ways to bring a 64-key tile into shared memory.  With a head size that is a multiple of
 // 64 and pages that are multiples of 64 keys, TMA copies the tile (one elected thread, boxes of
@@ -440,6 +446,9 @@ __device__ __forceinline__ float cluster_load(unsigned address) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(value) : "r"(address) : "memory");
   return value;
 }
+__device__ __forceinline__ void cluster_store(unsigned address, float value) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(address), "f"(value) : "memory");
+}
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
@@ -489,19 +498,24 @@ __device__ __forceinline__ int run_of(int tile, int total, int used) { return (i
 //
 // CLUSTER > 0 (TMA form, launches with so few (row, KV head) pairs that CLUSTER blocks for each are all resident): the
 // blocks of a thread-block cluster share one pair, each walks an equal share of its tiles, and the partial results are
-// combined through distributed shared memory: every block reads all blocks' results for its slice of the head's values.
-// No scratch, fence, counter or second trip to L2; with one request the combination of 16 partial results per head
-// was most of the kernel's time.
-template <bool TMA, int CLUSTER = 0>
-__global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
+// combined through distributed shared memory: every block sends each other block the slice of its result that the
+// other one adds up (stores into that block's shared memory, which nobody waits for), and after one cluster barrier each
+// block adds up what it was sent and leaves.  No scratch, fence, counter or second trip to L2; with one request the
+// combination of 16 partial results per head was most of the kernel's time.  (Fetching the slices from the other
+// blocks instead took a second barrier, so that nobody left while it was being read: 3,000 to 4,000 cycles for the
+// loads and that barrier, measured at one request.)
+template <bool TMA, int CLUSTER = 0, int CLUSTER_STAGES = DEC_CLUSTER_STAGES>
+__global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ? 3 : 1) paged_attention_decode_kernel(const AttentionParams p, const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v) {
-  constexpr int STAGES = CLUSTER ? DEC_CLUSTER_STAGES : DEC_STAGES;
+  constexpr int STAGES = CLUSTER ? CLUSTER_STAGES : DEC_STAGES;
   using Tiles = DecodeTiles<TMA, STAGES>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* smem_base = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023) : smem_raw;
   __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_base);                 // [STAGES][2][64 keys]
   __nv_bfloat16* q_tile = stages + STAGES * Tiles::STAGE;                          // [16][LD]
   uint64_t* tile_full = reinterpret_cast<uint64_t*>(q_tile + SMALL_ROWS * LD);         // [STAGES], TMA form
+  // cluster form: what the other blocks send - [CLUSTER][slice] partial results, then [CLUSTER][SMALL_ROWS] log-sum-exps
+  float* incoming = reinterpret_cast<float*>(tile_full + 8);
   __shared__ int plan[4];   // tiles of the launch; the row this block starts in; tiles before that row; blocks with a run
   __shared__ int pending[DEC_PENDING][6];   // segments to publish: pair, first block, segments, q0, packed rows, KV head
   __shared__ bool pending_last[DEC_PENDING];
@@ -728,6 +742,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
 
   Segment current, following;
   bool have = next_segment(current);
+  const bool had_tiles = have;   // cluster form: this block has a share of the pair's tiles
   bool waited = false;       // for the kernel before this one (programmatic dependent launch)
   bool prefetched = false;   // the segment's query and first tile were asked for while the one before it was merged
   while (have) {
@@ -971,11 +986,17 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
           for (int w = 0; w < 4; ++w) mine[i] += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
         }
       }
-      __syncthreads();
+      // Element e of the pair's result belongs to the block that adds up slice e / slice_length.
+      const int slice_length = (packed_rows * D + CLUSTER - 1) / (CLUSTER ? CLUSTER : 1), slice_stride = (p.incoming_rows * D + CLUSTER - 1) / (CLUSTER ? CLUSTER : 1);
 #pragma unroll
       for (int i = 0; i < SMALL_ROWS * D / ATT_THREADS; ++i) {
         const int e = threadIdx.x + i * ATT_THREADS;
-        if (e < packed_rows * D) reinterpret_cast<float*>(stages)[e] = mine[i];
+        if (e < packed_rows * D) cluster_store(cluster_address(incoming + cluster_rank * slice_stride + e % slice_length, e / slice_length), mine[i]);
+      }
+      for (int x = threadIdx.x; x < CLUSTER * SMALL_ROWS; x += ATT_THREADS) {
+        const int r = x % SMALL_ROWS;
+        if (r < packed_rows)
+          cluster_store(cluster_address(incoming + (CLUSTER ? CLUSTER : 1) * slice_stride + cluster_rank * SMALL_ROWS + r, x / SMALL_ROWS), row_lse[r]);
       }
     }
     for (int e = threadIdx.x; !CLUSTER && e < packed_rows * D; e += ATT_THREADS) {
@@ -1011,30 +1032,33 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
     return;
   }
 
-  // The cluster's blocks combine their results: each block a share of the (packed row, value) elements, from all blocks'
-  // shared memory.
+  // The cluster's blocks combine their results: each block the slice of the (packed row, value) elements that the others
+  // sent it.
   constexpr int SIZE = CLUSTER ? CLUSTER : 1;
-  if (!cluster_share_taken || current.tile_end <= current.tile_begin) {   // no tiles for this block: nothing visible in its share
-    if (threadIdx.x < SMALL_ROWS) row_lse[threadIdx.x] = -INFINITY;
-  }
-  if (!waited) {   // only a block without tiles comes here without having waited
-    grid_dependency_wait();
-    allow_dependents();
-  }
-  __syncthreads();
-  cluster_barrier();
   {
     const int cluster_row = cluster_pair / p.nkv;
     const int q0 = p.q_start[cluster_row];
     const int packed_rows = (p.q_start[cluster_row + 1] - q0) * G;
     const int kv_head = cluster_pair % p.nkv;
-    for (int e = cluster_rank * ATT_THREADS + threadIdx.x; e < packed_rows * D; e += SIZE * ATT_THREADS) {   // dealt out by the hundred
-      const int r = e / D, col = e % D;
+    const int slice_length = (packed_rows * D + SIZE - 1) / SIZE, slice_stride = (p.incoming_rows * D + SIZE - 1) / SIZE;
+    float* incoming_lse = incoming + SIZE * slice_stride;
+    if (!had_tiles) {
+      // no tiles for this block: nothing visible in its share, and nothing sent but that
+      for (int x = threadIdx.x; x < SIZE * SMALL_ROWS; x += ATT_THREADS)
+        if (x % SMALL_ROWS < packed_rows) cluster_store(cluster_address(incoming_lse + cluster_rank * SMALL_ROWS + x % SMALL_ROWS, x / SMALL_ROWS), -INFINITY);
+    }
+    if (!waited) {   // only a block without tiles comes here without having waited
+      grid_dependency_wait();
+      allow_dependents();
+    }
+    cluster_barrier();   // what every block sent is there
+    for (int x = threadIdx.x; x < slice_length && cluster_rank * slice_length + x < packed_rows * D; x += ATT_THREADS) {
+      const int e = cluster_rank * slice_length + x, r = e / D, col = e % D;
       float lse[SIZE], part[SIZE];
 #pragma unroll
       for (int c = 0; c < SIZE; ++c) {
-        lse[c] = cluster_load(cluster_address(&row_lse[r], c));
-        part[c] = cluster_load(cluster_address(reinterpret_cast<float*>(stages) + r * D + col, c));
+        lse[c] = incoming_lse[c * SMALL_ROWS + r];
+        part[c] = incoming[c * slice_stride + x];
       }
       float top = -INFINITY;
 #pragma unroll
@@ -1042,7 +1066,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       float sum = 0.f, total = 0.f;
 #pragma unroll
       for (int c = 0; c < SIZE; ++c) {
-        if (lse[c] == -INFINITY) continue;   // a block without visible keys: whatever lies in its buffer does not count
+        if (lse[c] == -INFINITY) continue;   // a block without visible keys: whatever lies in its place does not count
         const float weight = fast_exp2(lse[c] - top);
         sum += weight * part[c];
         total += weight;
@@ -1052,7 +1076,6 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 ? 3 : 1) paged_attention
       p.out[(token * p.nq + head) * D + col] = __float2bfloat16_rn(total > 0.f ? sum / total : 0.f);
     }
   }
-  cluster_barrier();   // nobody leaves while its shared memory is being read
 }
 
 // out[token, head] = sum_s w_s partial[s] / sum_s w_s with w_s = 2^(lse_s - max lse).  One
@@ -1156,7 +1179,14 @@ static bool page_pool_map(CUtensorMap* map, const void* pages, long long rows) {
 }
 
 constexpr size_t DEC_SMEM_TMA = DecodeTiles<TMA_HEAD>::SMEM, DEC_SMEM_GATHER = DecodeTiles<false>::SMEM;
-constexpr size_t DEC_SMEM_CLUSTER = DecodeTiles<TMA_HEAD, DEC_CLUSTER_STAGES>::SMEM;
+// The cluster form: its stages and query tile, then what the other blocks of the cluster send (partial results of
+// `rows` packed query rows in all, and every block's log-sum-exps).
+constexpr size_t DEC_SMEM_CLUSTER_BASE = DecodeTiles<TMA_HEAD, DEC_CLUSTER_STAGES>::SMEM;
+constexpr size_t DEC_SMEM_LONE_BASE = DecodeTiles<TMA_HEAD, DEC_LONE_STAGES>::SMEM;
+constexpr size_t dec_smem_cluster(int rows, int cluster, bool lone = false) {
+  return (lone ? DEC_SMEM_LONE_BASE : DEC_SMEM_CLUSTER_BASE) + ((size_t)rows * D + cluster + (size_t)cluster * SMALL_ROWS) * sizeof(float);
+}
+constexpr size_t DEC_SMEM_CLUSTER = dec_smem_cluster(SMALL_ROWS, 16);   // the most
 static bool clusters_of_16() {
   static const bool allowed = [] {
     if (!TMA_HEAD) return false;
@@ -1276,6 +1306,11 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
       err = cudaFuncSetAttribute(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_CLUSTER);
     PYLON_CLUSTER_CASE(16) PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
+    if (err == cudaSuccess && TMA_HEAD && dec_smem_cluster(SMALL_ROWS, 16, true) <= 227 * 1024 && clusters_of_16()) {
+      auto lone = paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? 16 : 0, DEC_LONE_STAGES>;
+      err = cudaFuncSetAttribute(lone, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (err == cudaSuccess) err = cudaFuncSetAttribute(lone, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem_cluster(SMALL_ROWS, 16, true));
+    }
     if (err != cudaSuccess) PYLON_REFUSE("paged_attention_mma: %s", cudaGetErrorString(err));
     configured = true;
   }
@@ -1302,6 +1337,7 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.num_rows = num_rows;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.small_rows_elsewhere = maybe_small ? 1 : 0;
+  p.incoming_rows = (int)(packed_max < SMALL_ROWS ? packed_max : SMALL_ROWS);
   if (run_tiled) {
     // 128-row blocks when the rows are long enough to fill them and the accumulators fit.
     const bool wide = WIDE_TILES && packed_max >= 256;
@@ -1331,8 +1367,13 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
         if (pairs * size > decode_blocks) size = 0;
       }
 #define PYLON_CLUSTER_CASE(N)                                                                                                   \
-      if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), DEC_SMEM_CLUSTER, \
+      if (size == N) launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? N : 0>, dim3((unsigned)(pairs * N)), dim3(ATT_THREADS), dec_smem_cluster(p.incoming_rows, N), \
                                               stream, N, p, map_k, map_v);
+      if (size == 16 && pairs * 16 <= decode_sm_count() && dec_smem_cluster(SMALL_ROWS, 16, true) <= 227 * 1024) {   // every block an SM to itself
+        launch_dependent_cluster(paged_attention_decode_kernel<TMA_HEAD, TMA_HEAD ? 16 : 0, DEC_LONE_STAGES>, dim3((unsigned)(pairs * 16)), dim3(ATT_THREADS),
+                                 dec_smem_cluster(p.incoming_rows, 16, true), stream, 16, p, map_k, map_v);
+        size = -1;
+      }
       PYLON_CLUSTER_CASE(16) PYLON_CLUSTER_CASE(8) PYLON_CLUSTER_CASE(6) PYLON_CLUSTER_CASE(4) PYLON_CLUSTER_CASE(3) PYLON_CLUSTER_CASE(2)
 #undef PYLON_CLUSTER_CASE
       if (size == 0)
