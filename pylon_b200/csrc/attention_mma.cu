@@ -453,6 +453,11 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
+// The decode kernel's warps merge their results through a buffer whose rows lie 4 D bytes apart, a multiple of all 32
+// banks: column c of row r sits at c ^ merge_swizzle(r), so that the four rows a half-warp stores at once fall into
+// different banks (head sizes that are multiples of 32; others keep their columns).
+__device__ __forceinline__ int merge_swizzle(int r) { return D % 32 == 0 ? (r & 3) << 3 : 0; }
+
 // Tiles of 64 keys that a row of decoded tokens (at most SMALL_ROWS packed query rows) walks
 // per KV head, and the first of them; 0 for every other row.
 __device__ __forceinline__ int decode_row_tiles(const AttentionParams& p, int row, int* first_tile) {
@@ -935,7 +940,8 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
 
     // Merge the four warps: each leaves its (max, sum, unnormalised output) in shared memory.
     __nv_bfloat16* idle_stage = stages + ((consumed + STAGES - 1) % STAGES) * Tiles::STAGE;   // the stage read last
-    float* merge_o = reinterpret_cast<float*>(idle_stage);             // [4][16][D]: exactly one stage of the TMA form
+    // [4][16][D]: exactly one stage of the TMA form; columns swizzled by row (merge_swizzle)
+    float* merge_o = reinterpret_cast<float*>(idle_stage);
     __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -950,7 +956,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
       }
       float* dst = merge_o + ((size_t)warp * SMALL_ROWS + r) * D;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * tq) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(dst + ((i * 8 + 2 * tq) ^ merge_swizzle(r))) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     __syncthreads();
     // Per row, once: the warps' weights 2^(max_w - max) over the total, and the log-sum-exp.
@@ -983,7 +989,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
         mine[i] = 0.f;
         if (e < packed_rows * D) {
 #pragma unroll
-          for (int w = 0; w < 4; ++w) mine[i] += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
+          for (int w = 0; w < 4; ++w) mine[i] += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + (col ^ merge_swizzle(r))];
         }
       }
       // Element e of the pair's result belongs to the block that adds up slice e / slice_length.
@@ -1003,7 +1009,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
       const int r = e / D, col = e % D;
       float value = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) value += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + col];
+      for (int w = 0; w < 4; ++w) value += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + (col ^ merge_swizzle(r))];
       if (segments == 1) {
         const size_t token = (size_t)q0 + r / G;
         const int head = kv_head * G + r % G;
