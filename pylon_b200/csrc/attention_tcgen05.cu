@@ -52,7 +52,7 @@ constexpr int FA_SMALL_ROWS = 16;                  // rows with at most this man
 constexpr int FA_Q_BYTES = FA_BM * D * 2;          // D / 64 panels of [128 rows][64 values]
 constexpr int FA_TILE_BYTES = FA_BN * D * 2;       // keys or values of one tile: D / 64 boxes of [64 keys][64 values]
 constexpr int FA_STAGE_BYTES = 2 * FA_TILE_BYTES;
-constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers: 14 x 8 bytes and the tensor-memory address */;
+constexpr size_t FA_SMEM_USED = (size_t)FA_Q_BYTES + FA_STAGES * FA_STAGE_BYTES + 128 /* barriers: 15 x 8 bytes and the tensor-memory address */;
 // At least 80 KB: never more than two blocks on an SM, so that their 2 x 256 columns of tensor memory always fit and no
 // block waits in tcgen05.alloc for another to finish.
 constexpr size_t FA_SMEM = FA_SMEM_USED > 80 * 1024 ? FA_SMEM_USED : 80 * 1024;
@@ -194,12 +194,17 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   uint64_t* v_full = k_empty + 2;      // [2] the same for the values
   uint64_t* v_empty = v_full + 2;      // [2]
   uint64_t* s_full = v_empty + 2;      // [2] scores of a tile are in tensor memory
-  uint64_t* p_full = s_full + 2;       // weights of a tile are in tensor memory, over its scores (and the output rescaled)
+  // [2] weights of tile t are in tensor memory, over its scores (and the output rescaled): barrier t % 2.  The softmax
+  // threads wait for nothing between two tiles but the scores, so they may be done with tile t + 1 while the issuer still
+  // waits for the values of tile t: with one barrier its wait by parity for tile t would then look at the phase of tile
+  // t + 2 and never end.  (Until the weights went into tensor memory the softmax threads waited for the weighted sum of
+  // tile t before they wrote the weights of tile t + 1, and could not get that far ahead.)
+  uint64_t* p_full = s_full + 2;
   // [2] the weighted sum of tile t is added to the output: barrier t % 2.  A softmax thread waits for it only when it has
   // to (a row to rescale; the end), and a wait by parity can tell a phase only from its neighbours: with one barrier a
   // thread that skipped two tiles' waits would take the phase before last for the one it asks for.  With two, the phase
   // before (tile t - 2) is always complete when tile t's scores are: the products run in the order they were issued.
-  uint64_t* pv_done = p_full + 1;
+  uint64_t* pv_done = p_full + 2;
   uint64_t* q_full = pv_done + 2;      // the query tile is in shared memory
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_full + 1);
 
@@ -235,7 +240,8 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       fa_mbar_init(&k_full[s], 1); fa_mbar_init(&k_empty[s], 1); fa_mbar_init(&v_full[s], 1); fa_mbar_init(&v_empty[s], 1);
       fa_mbar_init(&s_full[s], 1);
     }
-    fa_mbar_init(p_full, 128);
+    fa_mbar_init(&p_full[0], 128);
+    fa_mbar_init(&p_full[1], 128);
     fa_mbar_init(&pv_done[0], 1);
     fa_mbar_init(&pv_done[1], 1);
     fa_mbar_init(q_full, 128);
@@ -320,7 +326,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         const unsigned next_parity = ((t + 1) >> 1) & 1, parity = (t >> 1) & 1;
         for (unsigned tries = 0; (scores_due || sum_due) && alive; ++tries) {
           if (scores_due && fa_mbar_test(&k_full[(t + 1) & 1], next_parity)) { scores(t + 1); scores_due = false; }
-          if (sum_due && fa_mbar_test(p_full, t & 1) && fa_mbar_test(&v_full[t & 1], parity)) { weighted_sum(t); sum_due = false; }
+          if (sum_due && fa_mbar_test(&p_full[t & 1], parity) && fa_mbar_test(&v_full[t & 1], parity)) { weighted_sum(t); sum_due = false; }
           if (tries == FA_WAIT_LIMIT) { atomicExch(p.error, 2); alive = false; }
         }
       }
@@ -429,7 +435,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       }
       fa_tmem_wait_stores();
       fa_fence_before();
-      fa_mbar_arrive(p_full);
+      fa_mbar_arrive(&p_full[t & 1]);
     }
     if (alive && !fa_mbar_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) { atomicExch(p.error, 3); alive = false; }
     if (alive) {

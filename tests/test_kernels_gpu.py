@@ -495,6 +495,19 @@ def test_tcgen05_attention_gives_the_same_bits_every_time(d, nq, nkv):
     first = run().clone()
     for turn in range(30):
         assert torch.equal(run(), first), f"call {turn + 1} differs from the first"
+    # One portion that ends inside a page, as a prompt of 411 tokens leaves it, many times over: its last tile's values land
+    # late now and then, and an issuer that then mistook the softmax threads' next arrival for the one it waited for never
+    # came back (a bounded wait ran out: the error word).
+    lone = Paged([411], [411], nkv, d, 256, torch.bfloat16, seed=6)
+    lone_q = torch.randn(lone.tokens, (nq + 2 * nkv) * d, device=DEVICE).to(torch.bfloat16)
+    run_lone = lambda: ops.paged_attention(lone_q, lone.k_pages, lone.v_pages, lone.positions, lone.token_row, lone.q_start, lone.kv_len, lone.table,
+                                           nq, 448, 411, prefill_kernel="tcgen05", row_tokens=[411])
+    first_lone = run_lone().clone()
+    for turn in range(300):
+        out = run_lone()
+        if turn % 50 == 49:
+            assert torch.equal(out, first_lone), f"call {turn + 1} differs from the first"
+            assert int(ops.attention_error_word(torch.device(DEVICE)).item()) == 0, f"a wait ran out by call {turn + 1}"
     # against the plain statement, on the two longest rows (the reference is slow)
     longest = sorted(range(len(lengths)), key=lambda r: -lengths[r])[:2]
     for r in longest:
