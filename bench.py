@@ -502,7 +502,7 @@ def run_reference_arm(args) -> int:
         "context": CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS, "clock_sampler": ClockSampler, "peaks": peak,
         "prefill_flops": lambda tokens: prefill_flops(QWEN3_4B, tokens), "metric": METRIC,
         "baseline_tokens_per_second": BASELINE_TOKENS_PER_SECOND,
-        "config": headline_config(QWEN3_4B["num_hidden_layers"], args.batch, True, peak["source"]),
+        "config": headline_config(QWEN3_4B["num_hidden_layers"], args.batch, True, peak["source"], run_ahead=False),   # the reference waits for every step's tokens
     }
     return module.run(args, shared)
 
