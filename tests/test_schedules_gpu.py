@@ -281,3 +281,46 @@ def test_a_run_the_scheduler_cuts(dtype, graphs, tmp_path_factory):
     engine.cache.check()
     pool = engine.cache.groups[0].pool
     assert pool.free_count == pool.num_pages and pool.acquired_total > pool.num_pages
+
+
+def test_a_trace_of_mixed_steps_gives_the_same_bits_every_time(wide_model):
+    """A fixed trace of scheduler-shaped steps at Qwen3-4B widths (portions of up to 700 tokens beside decoded tokens of
+    up to eight requests, requests of 100 to 2,400 tokens, pages of 256, graphs on), three times over: the first pass warms
+    up and captures, the second and third must agree bit for bit at every step, with no error word set.  The kernels of a
+    step overlap one another (dependent launch) and wait for one another through barriers; a result that is read a moment
+    too early, or a wait that takes another phase for its own, shows here as a bit that differs from pass to pass or as a
+    wait that ran out, whatever the plain logits' tolerance would forgive."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine, StepEntry
+    from pylon_b200.kernels import ops
+
+    folder, _, _ = wide_model
+    rng = np.random.default_rng(12)
+    requests = {f"r{index}": rng.integers(0, WIDE_MODEL["vocab_size"], size=int(length)).tolist() for index, length in enumerate(rng.integers(100, 2_400, size=14))}
+    steps = trace_tools.mixed(requests, seed=12, max_live=8, decode_tail=16, max_portion=700)
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", page_size=256, max_cache_tokens=8 * 2_560, max_context=2_560, max_batch_size=8, cuda_graphs=True))
+    engine.step_function.graphs.capture_at_once = True
+
+    def one_pass():
+        live, outputs = {}, []
+        for step in steps:
+            entries = []
+            for item in step["entries"]:
+                if item["id"] not in live:
+                    live[item["id"]] = engine.open(item["id"], 2_560)
+                entries.append(StepEntry(live[item["id"]], item["tokens"], (len(item["tokens"]) - 1,)))
+            outputs.append(engine.step(entries).clone())
+            for name in step["end"]:
+                engine.close(live.pop(name))
+        torch.cuda.synchronize()
+        return outputs
+
+    one_pass()
+    second, third = one_pass(), one_pass()
+    assert all(bool(torch.isfinite(logits).all()) for logits in second)
+    differing = [index for index, (a, b) in enumerate(zip(second, third)) if not torch.equal(a, b)]
+    assert not differing, f"steps {differing[:8]} of {len(steps)} differ between two passes over the same trace"
+    assert ops._error_words(engine.device).tolist() == [0, 0, 0, 0]
+    graphs = engine.step_function.graphs
+    assert graphs.replays["padded"] > 50 and graphs.replays["decode"] > 20 and not graphs.failed
+    engine.cache.check()
