@@ -378,3 +378,57 @@ def test_running_ahead_generates_what_waiting_generates(seed):
     assert outcomes[True][0] == outcomes[False][0]
     # the host learns of an ending one tick late, so a slot may stand empty for a tick each time a request ends
     assert outcomes[True][1] <= outcomes[False][1] + len(requests)
+
+
+def test_running_ahead_a_step_that_fails_at_launch_fails_its_requests_only():
+    scheduler, step, events, cache = make_ahead({"a": [1, 2, 3, 4, 5, 6], "b": [7, 8, 9]}, run_ahead=True)
+    step.fail_on = 3     # the fourth call of the step function raises, with the third step still in flight
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=6, temperature=0.0))
+    for _ in range(3):
+        scheduler.tick()
+    scheduler.add("b", [4, 5], SamplingParams(max_new_tokens=3, temperature=0.0))   # joins at the failing step
+    results = {result.request_id: result for result in scheduler.run()}
+    assert results["a"].finish_reason == "error" and results["b"].finish_reason == "error"
+    assert results["a"].output_ids == [1, 2]      # what had been read back before the step failed; the token in flight is dropped
+    assert cache.free_pages() == [64] and cache.free_slots() == 4
+    cache.check()
+    scheduler.add("c", [1], SamplingParams(max_new_tokens=2, temperature=0.0))
+    scheduler.sample.choose = planned_sampler({"c": [11, 12]})
+    assert scheduler.run()[0].output_ids == [11, 12]
+
+
+def test_running_ahead_a_request_dropped_while_its_step_is_in_flight():
+    scheduler, step, events, cache = make_ahead({"a": [1, 2, 3, 4, 5, 6], "b": [7, 8, 9, 10]}, run_ahead=True)
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=6, temperature=0.0))
+    scheduler.add("b", [4, 5], SamplingParams(max_new_tokens=4, temperature=0.0))
+    scheduler.tick()
+    scheduler.tick()
+    assert scheduler.abort("a")           # a step with a row for it is queued; its token will be dropped
+    assert cache.free_slots() == 3
+    results = scheduler.run()
+    assert [(result.request_id, result.output_ids) for result in results] == [("b", [7, 8, 9, 10])]
+    assert cache.free_pages() == [64] and cache.free_slots() == 4
+    cache.check()
+
+
+def test_running_ahead_tokens_that_come_back_void_fail_the_requests_of_that_step():
+    scheduler, step, events, cache = make_ahead({"a": [1, 2, 3, 4, 5, 6, 7, 8], "b": [7, 8, 9]}, run_ahead=True)
+    launch = scheduler.sample.launch
+    count = [0]
+
+    def launch_with_one_void_result(logits, params, randoms):
+        handle = launch(logits, params, randoms)
+        count[0] += 1
+        if count[0] == 3:
+            def void():
+                raise RuntimeError("the results of that step are void")
+            handle.result = void
+        return handle
+
+    scheduler.sample.launch = launch_with_one_void_result
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=8, temperature=0.0))
+    results = scheduler.run()
+    assert results[0].finish_reason == "error" and results[0].output_ids == [1, 2]
+    assert cache.free_pages() == [64] and cache.free_slots() == 4
+    scheduler.add("b", [4], SamplingParams(max_new_tokens=3, temperature=0.0))
+    assert scheduler.run()[0].output_ids == [7, 8, 9]
