@@ -47,6 +47,10 @@ def build_parser() -> argparse.ArgumentParser:
     graphs = engine.add_mutually_exclusive_group()
     graphs.add_argument("--cuda-graphs", dest="cuda_graphs", action="store_true", default=None, help="PYLON_CUDA_GRAPHS: replay decode steps from CUDA graphs")
     graphs.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false")
+    ahead = engine.add_mutually_exclusive_group()
+    ahead.add_argument("--run-ahead", dest="run_ahead", action="store_true", default=None,
+                       help="PYLON_B200_RUN_AHEAD: queue the next step before waiting for the last one's tokens (the default)")
+    ahead.add_argument("--no-run-ahead", dest="run_ahead", action="store_false")
     engine.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default 256)")
     engine.add_argument("--max-cache-tokens", type=int, default=None, help="size of the cache pool in tokens (default: from free memory)")
     engine.add_argument("--max-context", type=int, default=None, help="longest request, prompt plus new tokens")
@@ -110,7 +114,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     config = EngineConfig.from_env(
         None, dtype=args.dtype, prefill_chunk_size=args.prefill_chunk_size, max_batch_size=args.max_batch_size,
         max_queue_size=args.max_queue_size, max_gpu_utilization=args.max_gpu_utilization, admit_skip=args.admit_skip,
-        cuda_graphs=args.cuda_graphs, page_size=args.page_size, max_cache_tokens=args.max_cache_tokens, max_context=args.max_context,
+        cuda_graphs=args.cuda_graphs, run_ahead=args.run_ahead, page_size=args.page_size, max_cache_tokens=args.max_cache_tokens, max_context=args.max_context,
         seed=args.sample_seed,
     )
     engine = Engine(model_dir, config)
