@@ -78,14 +78,19 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     group = n_heads // k.shape[0]
     k = k.repeat_interleave(group, dim=0)
     v = v.repeat_interleave(group, dim=0)
-    scores = q @ k.transpose(1, 2) / math.sqrt(dim)
-    i = torch.arange(tokens, device=q.device).unsqueeze(1)
-    j = torch.arange(tokens, device=q.device).unsqueeze(0)
-    visible = j <= i
-    if window is not None:
-        visible &= (i - j) < window
-    scores = scores.masked_fill(~visible, float("-inf"))
-    return torch.softmax(scores, dim=-1) @ v
+    out = torch.empty_like(q)
+    rows = tokens if tokens <= 8_192 else 2_048   # long sequences: the same rows, a slice at a time (the scores of all would not fit)
+    for begin in range(0, tokens, rows):
+        end = min(tokens, begin + rows)
+        scores = q[:, begin:end] @ k[:, :end].transpose(1, 2) / math.sqrt(dim)
+        i = torch.arange(begin, end, device=q.device).unsqueeze(1)
+        j = torch.arange(end, device=q.device).unsqueeze(0)
+        visible = j <= i
+        if window is not None:
+            visible &= (i - j) < window
+        scores = scores.masked_fill(~visible, float("-inf"))
+        out[:, begin:end] = torch.softmax(scores, dim=-1) @ v[:, :end]
+    return out
 
 
 def attention_part(x, w, prefix, cfg, cos, sin, window=None):

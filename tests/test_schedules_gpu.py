@@ -123,15 +123,15 @@ def test_pages_of_256_tokens_under_every_cutting(page_256_model, cutting, dtype)
 # (b) one long request
 # ---------------------------------------------------------------------------------------
 LONG_MODEL = dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-                  intermediate_size=512, max_position_embeddings=16_384, rope_theta=5_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
-LONG_PROMPT, LONG_TAIL, SHORT_PROMPT = 8_300, 32, 45
+                  intermediate_size=512, max_position_embeddings=40_960, rope_theta=5_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+LONG_PROMPTS, LONG_TAIL, SHORT_PROMPT = (8_300, 40_000), 32, 45   # 40,000: near the longest request Qwen3-4B takes (40,960)
 
 
-@pytest.fixture(scope="module")
-def long_model(tmp_path_factory):
+@pytest.fixture(scope="module", params=LONG_PROMPTS)
+def long_model(request, tmp_path_factory):
     folder, cfg, weights = make_model(tmp_path_factory, "long", LONG_MODEL, 32)
     rng = np.random.default_rng(42)
-    requests = {"long": rng.integers(0, 512, size=LONG_PROMPT + LONG_TAIL).tolist(), "short": rng.integers(0, 512, size=SHORT_PROMPT + LONG_TAIL // 2).tolist()}
+    requests = {"long": rng.integers(0, 512, size=request.param + LONG_TAIL).tolist(), "short": rng.integers(0, 512, size=SHORT_PROMPT + LONG_TAIL // 2).tolist()}
     expected = {rid: plain_logits(cfg, weights, tokens) for rid, tokens in requests.items()}
     del weights
     torch.cuda.empty_cache()
@@ -140,8 +140,8 @@ def long_model(tmp_path_factory):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_long_request_in_portions_of_2048_and_then_token_by_token(long_model, dtype):
-    """8,300 tokens in portions of 2,048 (the second and later portions attend to thousands of cached keys), then 32
-    tokens one by one over more than 128 key tiles: the first 16 beside a short request (rows of very different lengths:
+    """8,300 tokens (and 40,000) in portions of 2,048 (the second and later portions attend to thousands of cached keys),
+    then 32 tokens one by one over more than 128 key tiles: the first 16 beside a short request (rows of very different lengths:
     the decode attention's form of equal runs), the last 16 alone (its cluster form), from CUDA graphs in bfloat16.
     Positions beyond 8,000 with a rotary base of 5,000,000."""
     from pylon_b200.config import EngineConfig
@@ -149,6 +149,7 @@ def test_a_long_request_in_portions_of_2048_and_then_token_by_token(long_model, 
 
     folder, requests, expected = long_model
     long_tokens, short_tokens = requests["long"], requests["short"]
+    LONG_PROMPT = len(long_tokens) - LONG_TAIL
     steps = []
 
     def add(entries, end=()):
@@ -162,7 +163,7 @@ def test_a_long_request_in_portions_of_2048_and_then_token_by_token(long_model, 
         add([("long", [long_tokens[LONG_PROMPT + index]]), ("short", [short_tokens[SHORT_PROMPT + index]])], end=["short"] if index == half - 1 else ())
     for index in range(half, LONG_TAIL):
         add([("long", [long_tokens[LONG_PROMPT + index]])], end=["long"] if index == LONG_TAIL - 1 else ())
-    engine = Engine(folder, EngineConfig(dtype=dtype, page_size=256, max_cache_tokens=trace_tools.pool_tokens(steps, 256), max_context=8_448,
+    engine = Engine(folder, EngineConfig(dtype=dtype, page_size=256, max_cache_tokens=trace_tools.pool_tokens(steps, 256), max_context=-(-len(long_tokens) // 256) * 256,
                                          max_batch_size=2, cuda_graphs=dtype == "bfloat16"))
     got = trace_tools.run_in_process(engine, steps)
     for rid in requests:
