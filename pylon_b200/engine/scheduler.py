@@ -26,7 +26,8 @@ Policies follow raun6k/Pylon:
   for that one's tokens, so the device never waits for the host.  A decoding request's token for the new step is taken on
   the device from what the sampling kernel chose in the step before.  The host is one step behind: a request that met a
   stop id has been given one more step already, whose token is dropped; ``max_new_tokens`` is known beforehand and never
-  overrun.  What a request generates is the same either way.
+  overrun, and a request gives back its slot and pages when its last token by count is launched, not when it arrives.
+  What a request generates is the same either way.
 * pages: reservations make running out impossible for admitted requests; waiting requests
   wait.  If a step fails all the same (out of pages or any other error), the requests of
   that step fail with the error and give back what they held, the others go on.  (The
@@ -178,6 +179,7 @@ class Scheduler:
         self.seed = seed
         self.waiting: deque[Request] = deque()
         self.active: list[Request] = []
+        self.leaving: list[Request] = []    # running ahead: their last token is being chosen; slot and pages are given back already
         self.finished: list[GenerationResult] = []
         self.overtakes = 0    # admissions that passed the oldest waiting request
         self.ticks = 0
@@ -213,15 +215,16 @@ class Scheduler:
             if request.request_id == request_id:
                 self.waiting.remove(request)
                 return True
-        for request in self.active:
-            if request.request_id == request_id:
-                self._release(request)
-                self.active.remove(request)
-                return True
+        for holding in (self.active, self.leaving):
+            for request in holding:
+                if request.request_id == request_id:
+                    self._release(request)
+                    holding.remove(request)
+                    return True
         return False
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.active or self._flying is not None)
+        return bool(self.waiting or self.active or self.leaving or self._flying is not None)
 
     # -- admission -----------------------------------------------------------------------
     def _reserved(self) -> list[int]:
@@ -351,7 +354,7 @@ class Scheduler:
         """The step's requests fail; the others go on."""
         logger.error("model_batch_failed requests=%s error=%r", [request.request_id for request in selected], error)
         for request in selected:
-            if request in self.active:
+            if request in self.active or request in self.leaving:
                 self._finish(request, "error", error)
 
     def _launch(self, selected: list[Request], chunks: list[list[int]]) -> Optional["_Launched"]:
@@ -385,6 +388,13 @@ class Scheduler:
             request.pending_token = None
             request.in_flight = (tokens, row)
             request.launched += 1
+            if self.run_ahead and len(request.output_ids) + request.launched >= request.sampling.max_new_tokens:
+                # The token being chosen is the request's last whatever it is, and no later step will read its cache: slot
+                # and pages go back now, a tick before the token is here, so that a waiting request can have them (the
+                # device runs its steps in the order they were queued: whoever gets the pages writes them after this step).
+                self._release(request)
+                self.active.remove(request)
+                self.leaving.append(request)
         return _Launched(selected, chunks, prompt_rows, ready, tokens, started)
 
     def _collect(self, step: "_Launched") -> None:
@@ -398,7 +408,7 @@ class Scheduler:
         elapsed = now - max(step.started, self._collected_at)
         self._collected_at = now
         for request, chunk, prompt_row in zip(step.selected, step.chunks, step.prompt_rows):
-            if request not in self.active:
+            if request not in self.active and request not in self.leaving:
                 continue   # finished (a stop id in the step before, an error, an abort) while this step was in flight
             if prompt_row:
                 request.prompt_progress_at = now
@@ -406,7 +416,7 @@ class Scheduler:
             else:
                 request.inter_token_seconds.append(elapsed)
         for request, token in zip(step.ready, tokens):
-            if request not in self.active:
+            if request not in self.active and request not in self.leaving:
                 continue   # likewise: the token is dropped
             request.launched -= 1
             if request.in_flight is not None and request.in_flight[0] is step.tokens:
@@ -437,8 +447,9 @@ class Scheduler:
 
     def _finish(self, request: Request, reason: str, error: Optional[BaseException] = None) -> None:
         self._release(request)
-        if request in self.active:
-            self.active.remove(request)
+        for holding in (self.active, self.leaving):
+            if request in holding:
+                holding.remove(request)
         now = self.clock()
         self.finished.append(
             GenerationResult(

@@ -347,7 +347,7 @@ def test_a_scheduler_that_runs_ahead_needs_a_sampler_that_launches():
 def test_running_ahead_generates_what_waiting_generates(seed):
     """Random requests (prompt lengths, limits, stop ids that do and do not come up, arrival ticks) through a tight pool,
     with and without running ahead: the same output for every request, every page and slot given back, and at most one
-    step more per request."""
+    step more per request that met a stop id."""
     import random
 
     rng = random.Random(seed)
@@ -376,8 +376,10 @@ def test_running_ahead_generates_what_waiting_generates(seed):
         assert cache.free_pages() == [24] and cache.free_slots() == 3
         outcomes[run_ahead] = (results, len(step.calls))
     assert outcomes[True][0] == outcomes[False][0]
-    # the host learns of an ending one tick late, so a slot may stand empty for a tick each time a request ends
-    assert outcomes[True][1] <= outcomes[False][1] + len(requests)
+    # A request that ends by its length gives back slot and pages when its last token is launched, so nothing waits for
+    # it; the host learns of a stop id one tick late, so a slot may stand empty for a tick each time a request ends by one.
+    stopped = sum(1 for _, reason in outcomes[False][0].values() if reason == "eos")
+    assert outcomes[True][1] <= outcomes[False][1] + stopped + 1
 
 
 def test_running_ahead_a_step_that_fails_at_launch_fails_its_requests_only():
@@ -432,3 +434,24 @@ def test_running_ahead_tokens_that_come_back_void_fail_the_requests_of_that_step
     assert cache.free_pages() == [64] and cache.free_slots() == 4
     scheduler.add("b", [4], SamplingParams(max_new_tokens=3, temperature=0.0))
     assert scheduler.run()[0].output_ids == [7, 8, 9]
+
+
+def test_running_ahead_a_request_that_ends_by_length_makes_room_when_its_last_token_is_launched():
+    """One slot, two requests: the step that chooses the first one's last token gives its slot and pages back, so the
+    second's prompt goes into the very next step, while the first one's last token is still on its way to the host."""
+    scheduler, step, events, cache = make_ahead({"a": [1, 2, 3], "b": [7, 8]}, run_ahead=True, slots=1)
+    scheduler.add("a", [1, 2, 3], SamplingParams(max_new_tokens=3, temperature=0.0))
+    scheduler.add("b", [4, 5], SamplingParams(max_new_tokens=2, temperature=0.0))
+    results = {result.request_id: result for result in scheduler.run()}
+    assert results["a"].output_ids == [1, 2, 3] and results["b"].output_ids == [7, 8]
+    assert [[rid for rid, _, _ in call] for call in step.calls] == [["a"], ["a"], ["a"], ["b"], ["b"]]   # no step stands empty in between
+    assert events.index(("launch", 3)) < events.index(("result", 2))      # b's prompt is queued before a's last token is read
+    assert cache.free_pages() == [64] and cache.free_slots() == 1
+    # a request dropped while its last token is on its way
+    scheduler.sample.choose = planned_sampler({"c": [5, 6]})
+    scheduler.add("c", [9], SamplingParams(max_new_tokens=2, temperature=0.0))
+    scheduler.tick()
+    scheduler.tick()
+    assert [request.request_id for request in scheduler.leaving] == ["c"] and cache.free_slots() == 1
+    assert scheduler.abort("c") and not scheduler.leaving
+    assert scheduler.run() == [] and not scheduler.has_work()
