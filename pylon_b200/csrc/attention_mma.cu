@@ -656,6 +656,9 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
         if ((page < -1 || page >= p.num_pages) && p.error) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // a broken table; -1 is "no page"
         const int y = page_ok ? (page * p.nkv + s.kv_head) * p.page_size + key0 % p.page_size : p.num_pages * p.nkv * p.page_size;
         uint64_t* bar = &tile_full[issued % STAGES];
+        // The stage was read with ordinary loads (ldmatrix) until the barrier before this; TMA is another proxy, which
+        // that barrier alone does not order behind them.
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         att_mbar_expect_tx(bar, (unsigned)(Tiles::STAGE * sizeof(__nv_bfloat16)));
 #pragma unroll
         for (int box = 0; box < D / 64; ++box) {

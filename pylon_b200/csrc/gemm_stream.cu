@@ -110,6 +110,11 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
       unsigned stage = 0, phase = 1;   // the ring has gone round once
       for (int box = box_begin + ahead; box < box_end; ++box) {
         if (!st_mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); break; }
+        // The consumers read the stage with ordinary loads (ldmatrix); TMA, which writes it next, is another proxy, and
+        // the barrier alone does not order the two.  Without this fence the next box's first rows now and then landed
+        // under a warp's last reads: one weight row in some 1,500 calls off by a box's worth of its sum, for every token.
+        // (The same fence in every consumer warp, before it gives the stage back, cost 6 % of a decode step; here 1.7 %.)
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         unsigned char* dst = stages + (size_t)stage * STAGE_BYTES;
         st_mbar_expect_tx(&full[stage], STAGE_BYTES);
         st_tma_load(dst, &map_w, &full[stage], box * ST_BK, n0);

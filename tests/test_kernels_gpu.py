@@ -285,6 +285,26 @@ def test_stream_gemm_partial_sums(m, n, k):
         ops.linear_stream_partial(x, w, k_boxes + 1)
 
 
+def test_stream_gemm_gives_the_same_bits_every_time():
+    """The TMA-fed product, 17 rows against the QKV matrix of the 4B shape (its blocks go round their rings), the same call
+    8,000 times: every result bit for bit the first one's, which is the plain product.  Its consumers read a ring stage
+    with ordinary loads and TMA, another proxy, writes it next; without a proxy fence between the two the next box's first
+    rows landed under a warp's last reads about once in 1,500 calls: one weight row off by a box's worth of its sum."""
+    from pylon_b200.kernels import ops
+
+    torch.manual_seed(0)
+    w = (torch.randn(6_144, 2_560, device=DEVICE) * 0.02).to(torch.bfloat16)
+    x = torch.randn(17, 2_560, device=DEVICE).to(torch.bfloat16)
+    first = ops.linear_stream_partial(x, w).clone()
+    torch.testing.assert_close(first.sum(0).double(), x.double() @ w.double().T, rtol=1e-4, atol=1e-4)
+    differing = 0
+    for _ in range(80):
+        results = [ops.linear_stream_partial(x, w) for _ in range(100)]
+        differing += sum(1 for result in results if not torch.equal(result, first))
+    assert differing == 0, f"{differing} of 8,000 calls gave other bits than the first"
+    assert int(ops.stream_error_word(torch.device(DEVICE)).item()) == 0
+
+
 def test_kernel_error_words_are_reported_once():
     """A kernel whose bounded wait ran out sets a word on the device; the engine's check turns
     it into an exception and clears it.  (The word is set from the host here: no kernel is made
