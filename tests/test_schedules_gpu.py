@@ -325,3 +325,33 @@ def test_a_trace_of_mixed_steps_gives_the_same_bits_every_time(wide_model):
     graphs = engine.step_function.graphs
     assert graphs.replays["padded"] > 50 and graphs.replays["decode"] > 20 and not graphs.failed
     engine.cache.check()
+
+
+@pytest.mark.parametrize("tokens", [9, 17])
+def test_a_short_prompt_portion_gives_the_same_logits_every_time(wide_model, tokens):
+    """A prompt portion of a few tokens goes through the kernels of a decode step (the TMA-fed products with their partial
+    sums, the rotation that adds them up) and the tcgen05 attention: 200 times over, other steps in between, from graphs.
+    (This is where a missing proxy fence in the TMA-fed product showed: 54 different logits in 300 runs.)"""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine, StepEntry
+    from pylon_b200.kernels import ops
+
+    folder, _, _ = wide_model
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, WIDE_MODEL["vocab_size"], size=tokens).tolist()
+    others = [rng.integers(0, WIDE_MODEL["vocab_size"], size=size).tolist() for size in (600, 33, 1)]
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", page_size=256, max_cache_tokens=4 * 1_024, max_context=1_024, max_batch_size=4, cuda_graphs=True))
+    engine.step_function.graphs.capture_at_once = True
+    seen = {}
+    for turn in range(200):
+        request = engine.open(("short", turn), 1_024)
+        logits = engine.step([StepEntry(request, ids, (tokens - 1,))])
+        key = logits.cpu().numpy().tobytes()
+        seen[key] = seen.get(key, 0) + 1
+        engine.close(request)
+        if turn % 3 == 0:
+            other = engine.open(("other", turn), 1_024)
+            engine.step([StepEntry(other, others[turn // 3 % 3], (len(others[turn // 3 % 3]) - 1,))])
+            engine.close(other)
+    assert len(seen) == 1, f"{len(seen)} different results: {sorted(seen.values(), reverse=True)[:6]}"
+    assert ops._error_words(engine.device).tolist() == [0, 0, 0, 0]
