@@ -1,0 +1,102 @@
+"""Every hot kernel many times over on the same inputs: the same bits every time.
+
+A kernel whose blocks, warps or proxies (ordinary loads and stores, TMA, the tensor core) hand data to one another
+through barriers gives a result that depends on timing when one of them reads a moment too early or writes a moment too
+soon.  Such a result is still close to the right one - a tolerance forgives it - and comes out differently from run to
+run, which nothing forgives.  (Found this way: the TMA-fed product's missing proxy fence, about one call in 1,500.)"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from test_kernels_gpu import DEVICE, Paged
+
+pytestmark = pytest.mark.gpu
+
+
+def same_bits(function, calls: int, batch: int = 50) -> int:
+    """How many of ``calls`` calls of ``function`` give other bits than the first."""
+    first = function().clone()
+    differing = 0
+    for _ in range(calls // batch):
+        results = [function() for _ in range(batch)]     # queued back to back: the kernels of one call overlap the next
+        differing += sum(1 for result in results if not torch.equal(result, first))
+    return differing
+
+
+@pytest.fixture(scope="module")
+def weights():
+    from pylon_b200.kernels import ops
+
+    torch.manual_seed(0)
+    make = lambda rows, columns: (torch.randn(rows, columns, device=DEVICE) * 0.02).to(torch.bfloat16)
+    return {"qkv": make(6_144, 2_560), "gate_up": ops.interleave_gate_up(make(9_728, 2_560), make(9_728, 2_560)), "down": make(2_560, 9_728),
+            "head": make(32_000, 2_560)}
+
+
+@pytest.mark.parametrize("rows", [1, 8, 24])
+def test_tma_fed_products(weights, rows):
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(rows, 2_560, device=DEVICE).to(torch.bfloat16)
+    wide = torch.randn(rows, 9_728, device=DEVICE).to(torch.bfloat16)
+    assert same_bits(lambda: ops.linear_stream(x, weights["gate_up"], swiglu=True), 1_500) == 0      # 40 boxes a block: the ring goes round
+    assert same_bits(lambda: ops.linear_stream_partial(wide, weights["down"]), 1_500) == 0
+    assert same_bits(lambda: ops.linear_stream_partial(x, weights["qkv"]), 1_500) == 0
+    assert same_bits(lambda: ops.linear_stream(x, weights["qkv"]), 1_000) == 0
+    assert int(ops.stream_error_word(torch.device(DEVICE)).item()) == 0
+
+
+@pytest.mark.parametrize("rows", [333, 2_048])
+def test_tcgen05_products(weights, rows):
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(rows, 2_560, device=DEVICE).to(torch.bfloat16)
+    assert same_bits(lambda: ops.linear_tcgen05(x, weights["qkv"]), 400) == 0
+    assert same_bits(lambda: ops.linear_tcgen05(x, weights["gate_up"], swiglu=True), 300) == 0
+    assert int(ops.tcgen05_error_word(torch.device(DEVICE)).item()) == 0
+
+
+def test_skinny_product(weights):
+    from pylon_b200.kernels import ops
+
+    x = torch.randn(3, 2_560, device=DEVICE).to(torch.bfloat16)
+    assert same_bits(lambda: ops.linear_skinny(x, weights["head"], out_dtype=torch.float32), 1_000) == 0
+
+
+def test_attention_kernels():
+    from pylon_b200.kernels import ops
+
+    nq, nkv, d = 32, 8, 128
+    device = torch.device(DEVICE)
+    # a prompt of 2,048 tokens on the tcgen05 kernel
+    cache = Paged([2_048], [2_048], nkv, d, 256, torch.bfloat16, seed=3)
+    q = torch.randn(2_048, nq * d, device=DEVICE).to(torch.bfloat16)
+    prompt = lambda: ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.positions, cache.token_row, cache.q_start, cache.kv_len, cache.table,
+                                         nq, 2_048, 2_048, prefill_kernel="tcgen05", row_tokens=[2_048])
+    assert same_bits(prompt, 300) == 0
+    # later portions beside a decoded row
+    mixed_cache = Paged([3_000, 40, 700], [1_000, 40, 1], nkv, d, 256, torch.bfloat16, seed=4)
+    mixed_q = torch.randn(mixed_cache.tokens, nq * d, device=DEVICE).to(torch.bfloat16)
+    mixed = lambda: ops.paged_attention(mixed_q, mixed_cache.k_pages, mixed_cache.v_pages, mixed_cache.positions, mixed_cache.token_row, mixed_cache.q_start,
+                                        mixed_cache.kv_len, mixed_cache.table, nq, 1_000, 3_000, row_tokens=[1_000, 40, 1])
+    assert same_bits(mixed, 300) == 0
+    # decoded rows: equally long (clusters) and not (runs)
+    for lengths, alike in (([4_096] * 8, True), ([700, 3_000, 1_500, 90] * 4, False), ([4_000], True)):
+        decode_cache = Paged(lengths, [1] * len(lengths), nkv, d, 256, torch.bfloat16, seed=5)
+        decode_q = torch.randn(len(lengths), nq * d, device=DEVICE).to(torch.bfloat16)
+        decode = lambda: ops.paged_attention(decode_q, decode_cache.k_pages, decode_cache.v_pages, decode_cache.positions, decode_cache.token_row,
+                                             decode_cache.q_start, decode_cache.kv_len, decode_cache.table, nq, 1, max(lengths), rows_alike=alike)
+        assert same_bits(decode, 1_500) == 0, (lengths[:4], alike)
+    assert int(ops.attention_error_word(device).item()) == 0
+
+
+def test_norm_and_sampling():
+    from pylon_b200.kernels import ops
+
+    residual = torch.randn(2_048, 2_560, device=DEVICE)
+    delta = torch.randn(2_048, 2_560, device=DEVICE).to(torch.bfloat16)
+    weight = torch.ones(2_560, device=DEVICE)
+    assert same_bits(lambda: ops.add_rmsnorm(residual.clone(), delta, weight, 1e-6, torch.bfloat16), 300) == 0
+    logits = torch.randn(8, 151_936, device=DEVICE)
+    assert same_bits(lambda: ops.sample(logits), 500) == 0
