@@ -449,6 +449,10 @@ __device__ __forceinline__ float cluster_load(unsigned address) {
 __device__ __forceinline__ void cluster_store(unsigned address, float value) {
   asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(address), "f"(value) : "memory");
 }
+// The two halves of a cluster barrier: a block arrives when it starts and waits before it first writes into another
+// block's shared memory, by which time every block of the cluster has started too.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
@@ -544,6 +548,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
       grid_dependency_wait();   // a grid must not end before the grid ahead of it has: the next kernel's wait sees only this one
       return;
     }
+    cluster_arrive();   // "this block has started"; waited for before the first store into another block's shared memory
   }
   if (!CLUSTER && warp == 0) {
     int unused;
@@ -995,6 +1000,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
           for (int w = 0; w < 4; ++w) mine[i] += merge_max[w * SMALL_ROWS + r] * merge_o[((size_t)w * SMALL_ROWS + r) * D + (col ^ merge_swizzle(r))];
         }
       }
+      cluster_wait();   // every block of the cluster has started
       // Element e of the pair's result belongs to the block that adds up slice e / slice_length.
       const int slice_length = (packed_rows * D + CLUSTER - 1) / (CLUSTER ? CLUSTER : 1), slice_stride = (p.incoming_rows * D + CLUSTER - 1) / (CLUSTER ? CLUSTER : 1);
 #pragma unroll
@@ -1053,6 +1059,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
     float* incoming_lse = incoming + SIZE * slice_stride;
     if (!had_tiles) {
       // no tiles for this block: nothing visible in its share, and nothing sent but that
+      cluster_wait();   // every block of the cluster has started
       for (int x = threadIdx.x; x < SIZE * SMALL_ROWS; x += ATT_THREADS)
         if (x % SMALL_ROWS < packed_rows) cluster_store(cluster_address(incoming_lse + cluster_rank * SMALL_ROWS + x % SMALL_ROWS, x / SMALL_ROWS), -INFINITY);
     }

@@ -806,7 +806,7 @@ def test_qk_norm_rope_kv_write_from_partial_sums(tokens_each, nq, nkv, d, norm, 
 
 
 # ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("vocab", [320, 151_936, 1000])
+@pytest.mark.parametrize("vocab", [320, 151_936, 1000, 4099])
 def test_sample_argmax(vocab):
     from pylon_b200.kernels import ops
 
@@ -819,7 +819,8 @@ def test_sample_argmax(vocab):
     assert out.tolist() == expected.tolist()
 
 
-@pytest.mark.parametrize("vocab, temperature, top_p", [(320, 0.8, 1.0), (151_936, 0.7, 0.9), (1000, 1.5, 0.5), (50, 0.3, 0.95)])
+@pytest.mark.parametrize("vocab, temperature, top_p", [(320, 0.8, 1.0), (151_936, 0.7, 0.9), (1000, 1.5, 0.5), (50, 0.3, 0.95),
+                                                       (4099, 0.9, 0.8), (40_003, 1.2, 0.97), (4096, 0.5, 1.0)])
 def test_sample_temperature_and_top_p(vocab, temperature, top_p):
     """The kernel's token is the one the plain definition picks for the same uniform number,
     up to float32 rounding of the cumulative sums at a boundary."""
@@ -840,6 +841,35 @@ def test_sample_temperature_and_top_p(vocab, temperature, top_p):
         high = float(cdf[token])
         u = float(uniform[r])
         assert low - 1e-4 <= u <= high + 1e-4, (r, token, low, u, high)
+
+
+@pytest.mark.parametrize("vocab", [4099, 151_936, 777])
+def test_sample_rows_of_every_kind_in_one_call(vocab):
+    """Greedy rows, drawn rows, a nucleus so small that one token is left, a row of a wider matrix (a stride that is not the
+    vocabulary) and a row without a finite value, in one call; twice, with the same tokens."""
+    import plain_qwen3 as plain
+    from pylon_b200.kernels import ops
+
+    torch.manual_seed(vocab)
+    wide = torch.randn(6, vocab + 37, device=DEVICE) * 3
+    logits = wide[:, 5:5 + vocab]
+    logits[4, vocab - 2] = 40.0                                                 # the last block's share holds the winner
+    logits[5] = float("nan")
+    temperature = torch.tensor([0.0, 1.0, 0.7, 1.3, 1.0, 1.0], device=DEVICE)
+    top_p = torch.tensor([1.0, 1.0, 0.6, 1e-6, 0.9, 0.9], device=DEVICE)
+    uniform = torch.tensor([0.3, 0.999, 0.5, 0.7, 0.2, 0.4], device=DEVICE)
+    out = ops.sample(logits, temperature, top_p, uniform).tolist()
+    assert out[0] == int(logits[0].argmax())
+    assert out[3] == int(logits[3].argmax())                                    # the nucleus keeps the top token alone
+    assert out[4] == vocab - 2
+    assert 0 <= out[5] < vocab
+    for r in (1, 2):
+        probs = plain.sampling_distribution(logits[r].cpu(), float(temperature[r]), float(top_p[r]))
+        cdf = torch.cumsum(probs, 0)
+        assert probs[out[r]] > 0
+        assert float(cdf[out[r]] - probs[out[r]]) - 1e-4 <= float(uniform[r]) <= float(cdf[out[r]]) + 1e-4
+    for _ in range(50):
+        assert ops.sample(logits, temperature, top_p, uniform).tolist() == out
 
 
 def test_sample_mixed_rows_and_distribution():

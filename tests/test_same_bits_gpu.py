@@ -100,3 +100,7 @@ def test_norm_and_sampling():
     assert same_bits(lambda: ops.add_rmsnorm(residual.clone(), delta, weight, 1e-6, torch.bfloat16), 300) == 0
     logits = torch.randn(8, 151_936, device=DEVICE)
     assert same_bits(lambda: ops.sample(logits), 500) == 0
+    temperature = torch.tensor([0.2, 0.7, 1.0, 1.5] * 2, device=DEVICE)
+    top_p = torch.tensor([0.95, 0.9, 1.0, 0.5] * 2, device=DEVICE)
+    uniform = torch.rand(8, device=DEVICE)
+    assert same_bits(lambda: ops.sample(logits, temperature, top_p, uniform), 500) == 0
