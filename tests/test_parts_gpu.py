@@ -430,10 +430,37 @@ def register_routed_toy_parts():
     small experts, and a rotary encoding over neighbouring pairs (2j, 2j + 1), which is no
     rotation by the framework's table layout and therefore runs through ``apply``."""
     from pylon_b200.kernels import ops
-    from pylon_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding, TensorDecl
+    from pylon_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, CacheNeed, FeedForward, Mixer, PositionEncoding, TensorDecl
 
     if "toy_routed" in FEED_FORWARDS.kinds():
         return
+
+    @MIXERS.register("toy_cache_reader")
+    class CacheReader(Mixer):
+        """delta = Wo attention(q = Wq h; the keys and values of the run whose cache it is handed).  It keeps nothing
+        itself: its run of the order names an earlier run's cache, which holds this step's tokens already."""
+
+        def __init__(self, width: int, n_heads: int, head_dim: int) -> None:
+            self.width, self.n_heads, self.head_dim = width, n_heads, head_dim
+            self.wq = self.wo = None
+
+        def tensors(self):
+            return (TensorDecl("q_proj.weight", (self.n_heads * self.head_dim, self.width)),
+                    TensorDecl("o_proj.weight", (self.width, self.n_heads * self.head_dim)))
+
+        def load(self, tensors, dtype, device):
+            self.wq, self.wo = tensors["q_proj.weight"].contiguous(), tensors["o_proj.weight"].contiguous()
+
+        def cache_need(self):
+            return CacheNeed()
+
+        def forward(self, h, step, cache):
+            assert cache.k_pages is not None and cache.v_pages is not None and cache.k_pages.shape[3] == self.head_dim
+            q = ops.linear(h, self.wq)
+            context = ops.paged_attention(q, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len,
+                                          cache.block_table, self.n_heads, step.max_q, step.max_kv, row_tokens=step.row_tokens,
+                                          rows_alike=step.rows_alike)
+            return ops.linear(context, self.wo)
 
     @FEED_FORWARDS.register("toy_routed")
     class Routed(FeedForward):
@@ -489,7 +516,8 @@ def register_routed_toy_parts():
 @dataclass(frozen=True)
 class RoutedToyConfig:
     """Layer 0: attention with q/k norms and the neighbour-pair rotation, then the routed feed-forward;
-    layer 1: the same attention and a SwiGLU feed-forward."""
+    layer 1: the same attention and a SwiGLU feed-forward; layer 2: a mixer that has queries only and reads the
+    keys and values that layer 1 keeps (its run of the order names layer 1's cache), and a SwiGLU feed-forward."""
 
     architecture = "RoutedToyForCausalLM"
     vocab_size: int = 150
@@ -520,11 +548,13 @@ def routed_toy_spec(config: RoutedToyConfig, max_positions: Optional[int] = None
     })
     routed = PartSpec("toy_routed", {"width": config.width, "intermediate": config.intermediate, "experts": config.experts})
     dense = PartSpec("swiglu", {"width": config.width, "intermediate": config.intermediate})
-    block = lambda ffn: PartSpec("prenorm", {"mixer": attention, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm})
+    reader = PartSpec("toy_cache_reader", {"width": config.width, "n_heads": config.heads, "head_dim": config.head_dim})
+    block = lambda ffn, mixer=attention: PartSpec("prenorm", {"mixer": mixer, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm})
     return ModelSpec(
         width=config.width, vocab_size=config.vocab_size, max_positions=max_positions or 512, embedding_name="embed.weight",
         lm_head_name="head.weight", final_norm=norm, final_norm_prefix="norm.",
-        layers=(LayerSpec("layers.0.", block(routed)), LayerSpec("layers.1.", block(dense))), order=(RunSpec(0), RunSpec(1)),
+        layers=(LayerSpec("layers.0.", block(routed)), LayerSpec("layers.1.", block(dense)), LayerSpec("layers.2.", block(dense, reader))),
+        order=(RunSpec(0), RunSpec(1), RunSpec(2, cache_of=1)),
     )
 
 
@@ -545,7 +575,16 @@ def routed_toy_plain_forward(config: RoutedToyConfig, w: Mapping[str, torch.Tens
         project = lambda name, n: (h @ w[prefix + f"self_attn.{name}_proj.weight"].T).reshape(count, n, d).transpose(0, 1)
         q = rotate(plain.rms_norm(project("q", config.heads), w[prefix + "self_attn.q_norm.weight"], config.eps))
         k = rotate(plain.rms_norm(project("k", config.kv_heads), w[prefix + "self_attn.k_norm.weight"], config.eps))
-        context = plain.causal_attention(q, k, project("v", config.kv_heads))
+        v = project("v", config.kv_heads)
+        kept[prefix] = (k, v)
+        context = plain.causal_attention(q, k, v)
+        return context.transpose(0, 1).reshape(count, -1) @ w[prefix + "self_attn.o_proj.weight"].T
+
+    kept = {}   # what each attention layer's cache holds: normalised, rotated keys and the values
+
+    def reader(h, prefix, owner):
+        q = (h @ w[prefix + "self_attn.q_proj.weight"].T).reshape(count, config.heads, d).transpose(0, 1)
+        context = plain.causal_attention(q, *kept[owner])
         return context.transpose(0, 1).reshape(count, -1) @ w[prefix + "self_attn.o_proj.weight"].T
 
     smallest_gap = float("inf")
@@ -563,9 +602,10 @@ def routed_toy_plain_forward(config: RoutedToyConfig, w: Mapping[str, torch.Tens
             out[t] = probabilities[t, e] * (hidden @ w[prefix + f"mlp.experts.{e}.down.weight"].T)
         return out
 
-    for layer in (0, 1):
+    for layer in (0, 1, 2):
         prefix = f"layers.{layer}."
-        x = x + attention(plain.rms_norm(x, w[prefix + "input_layernorm.weight"], config.eps), prefix)
+        h = plain.rms_norm(x, w[prefix + "input_layernorm.weight"], config.eps)
+        x = x + (attention(h, prefix) if layer < 2 else reader(h, prefix, "layers.1."))
         h = plain.rms_norm(x, w[prefix + "post_attention_layernorm.weight"], config.eps)
         x = x + (routed(h, prefix) if layer == 0 else plain.swiglu_part(h, w, prefix))
     return plain.rms_norm(x, w["norm.weight"], config.eps) @ w["head.weight"].T, smallest_gap
@@ -628,6 +668,8 @@ def test_toy_model_with_routed_feed_forward_and_another_position_encoding(routed
     page = 16
     engine = Engine(routed_toy_folder, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=trace_tools.pool_tokens(steps, page),
                                                     max_context=128, max_batch_size=4))
+    # three runs, two caches: the reader's run is handed the pages of the run it names, and they are counted once
+    assert len(engine.cache.groups) == 1 and engine.cache.bytes_per_token() == 2 * 2 * config.kv_heads * config.head_dim * (4 if dtype == "float32" else 2)
     got = trace_tools.run_in_process(engine, steps)
     tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
     for rid in requests:
