@@ -677,3 +677,152 @@ def test_toy_model_with_routed_feed_forward_and_another_position_encoding(routed
     # every expert had work: the comparison covered all of them
     used = {int(t) % config.experts for tokens in requests.values() for t in tokens}
     assert used == set(range(config.experts))
+
+
+# ---------------------------------------------------------------------------------------
+# a third made-up architecture: another norm and another arrangement of a block
+# ---------------------------------------------------------------------------------------
+def register_parallel_toy_parts():
+    """Defined here, not in the framework: a norm that subtracts the mean and has a bias, and a block in which
+    the mixer and the feed-forward read the same normalised input and both add to the stream."""
+    from pylon_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Norm, TensorDecl
+
+    if "toy_layernorm" in NORMS.kinds():
+        return
+
+    @NORMS.register("toy_layernorm")
+    class LayerNorm(Norm):
+        """y = (x - mean) / sqrt(var + eps) * weight + bias, in float32, on the residual sum with the pending delta folded in."""
+
+        def __init__(self, width: int, eps: float) -> None:
+            self.width, self.eps = width, eps
+            self.weight = self.bias = self.dtype = None
+
+        def tensors(self):
+            return (TensorDecl("weight", (self.width,), "vector"), TensorDecl("bias", (self.width,), "vector"))
+
+        def load(self, tensors, dtype, device):
+            self.weight, self.bias, self.dtype = tensors["weight"].float(), tensors["bias"].float() - 1.0, dtype   # vectors are drawn around 1
+
+        def apply(self, stream, rows=None):
+            stream.flush()
+            x = stream.residual if rows is None else stream.residual[rows.long()]
+            centred = x - x.mean(-1, keepdim=True)
+            return (centred * torch.rsqrt(centred.square().mean(-1, keepdim=True) + self.eps) * self.weight + self.bias).to(self.dtype)
+
+    @BLOCKS.register("toy_parallel")
+    class ParallelBlock(Block):
+        """x += mixer(norm(x)) + feed_forward(norm(x)): one norm, two deltas."""
+
+        def __init__(self, mixer, feed_forward, norm) -> None:
+            self.mixer, self.feed_forward, self.norm = MIXERS.build(mixer), FEED_FORWARDS.build(feed_forward), NORMS.build(norm)
+            self._children = (("self_attn.", self.mixer), ("mlp.", self.feed_forward), ("input_layernorm.", self.norm))
+
+        def tensors(self):
+            return [TensorDecl(prefix + d.name, d.shape, d.role) for prefix, part in self._children for d in part.tensors()]
+
+        def load(self, tensors, dtype, device):
+            for prefix, part in self._children:
+                part.load({name[len(prefix):]: t for name, t in tensors.items() if name.startswith(prefix)}, dtype, device)
+
+        def weight_bytes(self):
+            return sum(part.weight_bytes() for _, part in self._children)
+
+        def forward(self, stream, step, cache):
+            h = self.norm.apply(stream)
+            stream.add(self.mixer.forward(h, step, cache))
+            stream.add(self.feed_forward.forward(h, step))   # the delta before it goes into the sum first
+
+
+@dataclass(frozen=True)
+class ParallelToyConfig:
+    architecture = "ParallelToyForCausalLM"
+    vocab_size: int = 170
+    width: int = 56
+    heads: int = 3
+    kv_heads: int = 1
+    head_dim: int = 32
+    intermediate: int = 104
+    eps: float = 3e-5
+    layers: int = 3
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: data[k] for k in ("vocab_size", "width", "heads", "kv_heads", "head_dim", "intermediate", "eps", "layers")})
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], **self.__dict__}
+
+
+def parallel_toy_spec(config: ParallelToyConfig, max_positions: Optional[int] = None):
+    from pylon_b200.parts import LayerSpec, ModelSpec, PartSpec
+
+    positions = max_positions or 512
+    norm = PartSpec("toy_layernorm", {"width": config.width, "eps": config.eps})
+    attention = PartSpec("gqa_attention", {
+        "width": config.width, "n_heads": config.heads, "n_kv_heads": config.kv_heads, "head_dim": config.head_dim, "qk_norm_eps": config.eps,
+        "window": None, "position": PartSpec("rope", {"head_dim": config.head_dim, "theta": 5_000.0, "max_positions": positions}),
+    })
+    block = PartSpec("toy_parallel", {"mixer": attention, "feed_forward": PartSpec("swiglu", {"width": config.width, "intermediate": config.intermediate}),
+                                      "norm": norm})
+    return ModelSpec(
+        width=config.width, vocab_size=config.vocab_size, max_positions=positions, embedding_name="embed.weight", lm_head_name=None,
+        final_norm=norm, final_norm_prefix="norm.", layers=tuple(LayerSpec(f"layers.{i}.", block) for i in range(config.layers)),
+        order=tuple(range(config.layers)),
+    )
+
+
+def parallel_toy_plain_forward(config: ParallelToyConfig, w: Mapping[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+    ids = torch.as_tensor(list(tokens))
+    x = w["embed.weight"][ids]
+    cos, sin = plain.rope_tables(config.head_dim, 5_000.0, torch.arange(len(ids)), x.dtype)
+    cfg = {"num_attention_heads": config.heads, "num_key_value_heads": config.kv_heads, "head_dim": config.head_dim, "rms_norm_eps": config.eps}
+
+    def layer_norm(x, prefix):
+        centred = x - x.mean(-1, keepdim=True)
+        return centred / torch.sqrt(centred.square().mean(-1, keepdim=True) + config.eps) * w[prefix + "weight"] + (w[prefix + "bias"] - 1.0)
+
+    for layer in range(config.layers):
+        prefix = f"layers.{layer}."
+        h = layer_norm(x, prefix + "input_layernorm.")
+        x = x + plain.attention_part(h, w, prefix, cfg, cos, sin, None) + plain.swiglu_part(h, w, prefix)
+    return layer_norm(x, "norm.") @ w["embed.weight"].T
+
+
+@pytest.fixture(scope="module")
+def parallel_toy_folder(tmp_path_factory):
+    from pylon_b200.config import register_architecture
+    from pylon_b200.config.registry import ARCHITECTURES
+    from pylon_b200.weights import write_random_model
+
+    register_parallel_toy_parts()
+    register_architecture(ParallelToyConfig.architecture, ParallelToyConfig, parallel_toy_spec)
+    folder = tmp_path_factory.mktemp("parallel_toy")
+    write_random_model(ParallelToyConfig(), 31, folder)
+    yield folder
+    ARCHITECTURES.pop(ParallelToyConfig.architecture, None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
+def test_toy_model_with_another_norm_and_another_block_arrangement(parallel_toy_folder, cutting, dtype):
+    """A norm with mean and bias and a block whose mixer and feed-forward share one normalised input, both defined
+    above; the head shares the embedding table; one KV head of size 32 under three query heads."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine
+
+    config = ParallelToyConfig()
+    _, weights = plain.read_model(parallel_toy_folder)
+    rng = np.random.default_rng(13)
+    requests = {f"p{i}": rng.integers(0, config.vocab_size, size=n).tolist() for i, n in enumerate((48, 70, 15, 33, 64))}
+    expected = {rid: plain.as_numpy(parallel_toy_plain_forward(config, weights, tokens)) for rid, tokens in requests.items()}
+    builders = {"whole": trace_tools.whole, "tail_one_by_one": trace_tools.tail_one_by_one,
+                "changing_portions": trace_tools.changing_portions, "mixed": trace_tools.mixed}
+    steps = builders[cutting](requests)
+    page = 4
+    engine = Engine(parallel_toy_folder, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=trace_tools.pool_tokens(steps, page),
+                                                      max_context=128, max_batch_size=4))
+    got = trace_tools.run_in_process(engine, steps)
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)
+    for rid in requests:
+        np.testing.assert_allclose(got[rid], expected[rid], err_msg=rid, **tol)
