@@ -146,12 +146,156 @@ struct TcStore {
   static_assert(BN % ACCUMULATOR_COLUMNS == 0, "the tile's width must divide into whole stores");
 };
 
+// What the epilogue of a fused QKV product needs to finish the heads it holds (TC_ROTATE): q and k heads are normalised
+// (RMSNorm over the head, when weights are given) and rotated by the tables, q goes to a tensor of its own, k and v into
+// their pages at the token's slot.
+struct RotateArgs {
+  __nv_bfloat16* q_out;            // [M, nq * D], row stride ldq
+  long long ldq;
+  const float* q_weight;           // [D] or null
+  const float* k_weight;
+  float eps;
+  const float* cos_table;          // [table_positions, D / 2]
+  const float* sin_table;
+  int table_positions;
+  const int* positions;            // [M]
+  const int* token_row;            // [M]; negative: a padding token, which belongs to no request
+  const int* block_table;          // [rows, table_width]
+  int table_width, page_size;
+  __nv_bfloat16* k_pages;          // [num_pages, nkv, page_size, D]
+  __nv_bfloat16* v_pages;
+  int num_pages, nq, nkv;
+  int* page_error;                 // set to PYLON_ERROR_BAD_PAGE when a block table names a page that is not there
+};
+enum TcMode { TC_PLAIN = 0, TC_SWIGLU = 1, TC_ROTATE = 2 };
+
+// The epilogue of a fused QKV product for one warp's 32 token rows (lane = row = lane of tensor memory) and the BN / D
+// heads of its tile, head by head, in two turns.  Row-wise: a thread reads its row of the head from tensor memory, sums
+// its squares in float32 and lays the row down in the warp's staging rows as bfloat16 (16-byte units XORed with the row,
+// so that neither these writes nor the reads along a row meet in a bank).  Then column-wise, row by row: lane l holds the
+// columns l * PER.. of the lower half and their rotation partners in the upper half, so the angles of a row are one
+// coalesced 128- or 256-byte read, the norm weights sit in registers, and a row leaves as whole sectors, into q or the
+// token's slot of its page.  (With the rotation row-wise as well, every thread read its own row of the tables: 32 lines a
+// load, which the little L1 that the ring leaves could not hold; a tile's epilogue then took longer than its products.)
+template <int BN, int D>
+__device__ __forceinline__ void rotate_epilogue(const RotateArgs& rot, uint32_t taddr, unsigned char* staging, int row0, int n0, int M, int lane) {
+  constexpr int HALF = D / 2, UNITS = D / 8, ROW_BYTES = D * 2, PER = HALF / 32;   // PER columns of each half to a lane: 2 or 1
+  static_assert((D == 64 || D == 128) && BN % D == 0 && 32 * ROW_BYTES <= 2 * 32 * 128, "head size 64 or 128, whole heads in a tile");
+  const int t = row0 + lane;
+  const bool live = t < M;
+  const int pos = live ? rot.positions[t] : 0;
+  const int row = live ? rot.token_row[t] : -1;
+  long long page_offset = -1;   // elements from the pages' start to this token's slot of KV head 0; negative: nothing is written
+  if (row >= 0) {
+    const int page = rot.block_table[(size_t)row * rot.table_width + pos / rot.page_size];
+    if (page >= 0 && page < rot.num_pages) page_offset = ((long long)page * rot.nkv * rot.page_size + pos % rot.page_size) * D;
+    else if (rot.page_error) atomicExch(rot.page_error, PYLON_ERROR_BAD_PAGE);   // always there for a prepared step: else the host is told
+  }
+  const int table_row = pos < rot.table_positions ? pos : rot.table_positions - 1;   // the host checks the range
+  const int heads = rot.nq + 2 * rot.nkv;
+  const int column = lane * PER;   // this lane's columns of the lower half in the column-wise turn
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += D) {
+    const int head = (n0 + c0) / D;
+    if (head >= heads) break;
+    const bool is_q = head < rot.nq, is_v = head >= rot.nq + rot.nkv;
+    const float* weight = is_v ? nullptr : (is_q ? rot.q_weight : rot.k_weight);
+    float sumsq = 0.f;
+#pragma unroll 1
+    for (int part = 0; part < D / 32; ++part) {
+      uint32_t raw[32];
+      tc_load_32(taddr + c0 + part * 32, raw);
+      if (weight) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sumsq += __uint_as_float(raw[j]) * __uint_as_float(raw[j]);
+      }
+#pragma unroll
+      for (int unit = 0; unit < 4; ++unit) {
+        const uint32_t physical = (uint32_t)(part * 4 + unit) ^ (uint32_t)(lane & (UNITS - 1));
+        *reinterpret_cast<uint4*>(staging + lane * ROW_BYTES + (physical << 4)) =
+            make_uint4(pack2(__uint_as_float(raw[unit * 8]), __uint_as_float(raw[unit * 8 + 1])), pack2(__uint_as_float(raw[unit * 8 + 2]), __uint_as_float(raw[unit * 8 + 3])),
+                       pack2(__uint_as_float(raw[unit * 8 + 4]), __uint_as_float(raw[unit * 8 + 5])), pack2(__uint_as_float(raw[unit * 8 + 6]), __uint_as_float(raw[unit * 8 + 7])));
+      }
+    }
+    const float inv = weight ? rsqrtf(sumsq / (float)D + rot.eps) : 1.f;
+    float w_lower[PER], w_upper[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      w_lower[i] = weight ? weight[column + i] : 1.f;
+      w_upper[i] = weight ? weight[HALF + column + i] : 1.f;
+    }
+    __syncwarp();
+    const int kv_head = is_q ? 0 : (head - rot.nq) % rot.nkv;
+    __nv_bfloat16* pages = is_v ? rot.v_pages : rot.k_pages;
+    const uint32_t lower_byte = (uint32_t)column * 2, upper_byte = (uint32_t)(HALF + column) * 2;
+    // Eight rows at a time: first everything they read (angles, staged values), then the arithmetic and the stores, so
+    // that the loads of a batch are in flight together (a load cannot pass a store that might write what it reads).
+    constexpr int BATCH = 8;
+#pragma unroll 1
+    for (int r0 = 0; r0 < 32 && row0 + r0 < M; r0 += BATCH) {
+      long long offsets[BATCH];
+      float inv_of[BATCH], c[BATCH][PER], sn[BATCH][PER], a[BATCH][PER], b[BATCH][PER];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int r = r0 + i;
+        offsets[i] = __shfl_sync(0xffffffffu, page_offset, r);
+        inv_of[i] = __shfl_sync(0xffffffffu, inv, r);
+        const int table_r = __shfl_sync(0xffffffffu, table_row, r);   // rows past the end have position 0: any row of the tables will do
+        if (!is_v) {
+          const float* cos_at = rot.cos_table + (size_t)table_r * HALF + column;
+          const float* sin_at = rot.sin_table + (size_t)table_r * HALF + column;
+          if (PER == 2) {
+            const float2 cv = *reinterpret_cast<const float2*>(cos_at), sv = *reinterpret_cast<const float2*>(sin_at);
+            c[i][0] = cv.x; c[i][PER - 1] = cv.y; sn[i][0] = sv.x; sn[i][PER - 1] = sv.y;
+          } else {
+            c[i][0] = cos_at[0]; sn[i][0] = sin_at[0];
+          }
+        }
+        const unsigned char* source = staging + r * ROW_BYTES;
+        const uint32_t swizzle = (uint32_t)(r & (UNITS - 1));
+        const unsigned char* lower_src = source + ((((lower_byte >> 4) ^ swizzle) << 4) | (lower_byte & 15));
+        const unsigned char* upper_src = source + ((((upper_byte >> 4) ^ swizzle) << 4) | (upper_byte & 15));
+        if (PER == 2) {
+          const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(lower_src)), fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(upper_src));
+          a[i][0] = fa.x; a[i][PER - 1] = fa.y; b[i][0] = fb.x; b[i][PER - 1] = fb.y;
+        } else {
+          a[i][0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(lower_src));
+          b[i][0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(upper_src));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int r = r0 + i;
+        if (row0 + r >= M || (!is_q && offsets[i] < 0)) continue;
+        if (!is_v) {
+#pragma unroll
+          for (int e = 0; e < PER; ++e) {
+            const float first = a[i][e] * inv_of[i] * w_lower[e], second = b[i][e] * inv_of[i] * w_upper[e];
+            a[i][e] = first * c[i][e] - second * sn[i][e];
+            b[i][e] = second * c[i][e] + first * sn[i][e];
+          }
+        }
+        __nv_bfloat16* dst = is_q ? rot.q_out + (size_t)(row0 + r) * rot.ldq + (size_t)head * D : pages + offsets[i] + (size_t)kv_head * rot.page_size * D;
+        if (PER == 2) {
+          *reinterpret_cast<uint32_t*>(dst + column) = pack2(a[i][0], a[i][PER - 1]);
+          *reinterpret_cast<uint32_t*>(dst + HALF + column) = pack2(b[i][0], b[i][PER - 1]);
+        } else {
+          dst[column] = __float2bfloat16_rn(a[i][0]);
+          dst[HALF + column] = __float2bfloat16_rn(b[i][0]);
+        }
+      }
+    }
+    __syncwarp();   // the next head writes the same staging rows
+  }
+}
+
 // error: 0 = fine; otherwise 1 producer, 2 MMA issuer, 3 epilogue gave up waiting.
-template <int BN, bool SWIGLU>
+template <int BN, int MODE, int D>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       const __grid_constant__ CUtensorMap map_b,
                                                                       const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
-                                                                      int* __restrict__ error) {
+                                                                      int* __restrict__ error, const RotateArgs rot) {
+  constexpr bool SWIGLU = MODE == TC_SWIGLU;
   using S = TcShared<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -248,6 +392,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
       tc_fence_after();
       const int row0 = m0 + quarter * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
+      if constexpr (MODE == TC_ROTATE) {
+        rotate_epilogue<BN, D>(rot, taddr, my_staging, row0, n0, M, lane);
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += Store::ACCUMULATOR_COLUMNS, ++staged) {
         unsigned char* stage_rows = my_staging + (staged & 1) * (32 * 128);
@@ -295,7 +442,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buffer]);   // four warps: the buffer may be overwritten
     }
-    if (lane == 0) tma_store_wait_all();
+    if (MODE != TC_ROTATE && lane == 0) tma_store_wait_all();
   }
 
   // Wind down: every role comes here, also after a wait that ran out.
@@ -342,7 +489,7 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 template <int BN, bool SWIGLU>
 static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __nv_bfloat16* c, int M, int N, int K, long long ldc,
                           int* error, int sm_count, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<BN, SWIGLU>;
+  auto kernel = gemm_tcgen05_kernel<BN, SWIGLU ? TC_SWIGLU : TC_PLAIN, 128>;
   static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
   bool& configured = configured_on[pylon::current_device_slot()];
   if (!configured) {
@@ -354,8 +501,26 @@ static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __
   if (!make_map(&map_c, c, M, SWIGLU ? N / 2 : N, ldc, 32, TcStore<BN, SWIGLU>::COLUMNS)) PYLON_REFUSE("gemm_tcgen05: the output's tensor map could not be made");
   const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   const int blocks = tiles < sm_count ? tiles : sm_count;
-  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error, RotateArgs{});
   PYLON_CHECK_LAUNCH("gemm_tcgen05");
+}
+
+template <int BN, int D>
+static int launch_rotate(const CUtensorMap& map_a, const CUtensorMap& map_b, int M, int N, int K, const RotateArgs& rot, int* error, int sm_count,
+                         cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<BN, TC_ROTATE, D>;
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShared<BN>::BYTES);
+    if (err != cudaSuccess) PYLON_REFUSE("gemm_tcgen05_qkv: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+  const int blocks = tiles < sm_count ? tiles : sm_count;
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_a /* no output map */, M, N, K, error,
+                                rot);
+  PYLON_CHECK_LAUNCH("gemm_tcgen05_qkv");
 }
 
 static int forced_columns = 0;
@@ -391,8 +556,10 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
     if (swiglu && (candidate == 160 || candidate == 288)) continue;   // their accumulator columns do not divide into stores of 32 output columns
     const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
     const long long rounds = (tiles + sm_count - 1) / sm_count;
-    long long cost = rounds * (candidate + 16);   // + a per-tile overhead
-    if (candidate > 256) cost += (rounds - 1) * 32;   // one accumulator buffer: the epilogue of a tile holds up the next
+    // A tile's time is what its operands take to arrive from L2, (128 + width) rows of k a step, plus its start and end:
+    // measured per round 11.9, 12.2, 13.9 and 16.3 us at widths 128, 160, 192 and 256 (k = 2,560), which is width + 213.
+    long long cost = rounds * (candidate + 213);
+    if (candidate > 256) cost += rounds * 100;   // one accumulator buffer: the epilogue of a tile holds up the next (21 us a round)
     if (best < 0 || cost < best) { best = cost; bn = candidate; }
   }
   CUtensorMap map_a, map_b;
@@ -410,4 +577,56 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
   if (bn == 160) return launch_tcgen05<160, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+}
+
+// The fused QKV product with its heads finished in the epilogue: x bfloat16 [M, K], w bfloat16 [(nq + 2 nkv) * d, K] (q rows,
+// then k, then v); q and k heads are normalised over the head (weights float32 [d], or null for none) and rotated by the
+// float32 cos/sin tables [table_positions, d / 2] at positions[t] (pairs (j, j + d / 2)); q goes to q_out bfloat16
+// [M, nq * d] (row stride ldq), k and v into the pages [num_pages, nkv, page_size, d] at the slot that the token's row of
+// the block table names (token_row[t] negative: a padding token, nothing written).  d 64 or 128.  page_error: set to
+// PYLON_ERROR_BAD_PAGE when a block table names a page that is not there (nothing is written for that token).
+extern "C" int pylon_gemm_tcgen05_qkv_rotate(const void* x, const void* w, void* q_out, int M, int K, long long ldx, long long ldw, long long ldq,
+                                             const float* q_weight, const float* k_weight, float eps, const float* cos_table, const float* sin_table,
+                                             int table_positions, const int* positions, const int* token_row, const int* block_table, int table_width,
+                                             int page_size, void* k_pages, void* v_pages, int num_pages, int nq, int nkv, int head_dim, int* page_error,
+                                             int* error, int sm_count, cudaStream_t stream) {
+  using namespace pylon;
+  if (M <= 0) return 0;
+  if (head_dim != 64 && head_dim != 128) PYLON_REFUSE("gemm_tcgen05_qkv: head size %d (64 or 128)", head_dim);
+  if (nq < 1 || nkv < 1 || page_size < 1 || table_width < 1 || num_pages < 1 || table_positions < 1)
+    PYLON_REFUSE("gemm_tcgen05_qkv: %d query heads, %d KV heads, pages of %d, tables of %d, %d pages, %d positions", nq, nkv, page_size, table_width, num_pages, table_positions);
+  const int N = (nq + 2 * nkv) * head_dim;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldq % 8) PYLON_REFUSE("gemm_tcgen05_qkv: K = %d and the row strides must be multiples of 8", K);
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)q_out % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) ||
+      ((uintptr_t)cos_table % 16) || ((uintptr_t)sin_table % 16) || ((uintptr_t)q_weight % 16) || ((uintptr_t)k_weight % 16))
+    PYLON_REFUSE("gemm_tcgen05_qkv: x, w, q, the pages, the tables and the norm weights must be 16-byte aligned");
+  if (ldx < K || ldw < K || ldq < (long long)nq * head_dim) PYLON_REFUSE("gemm_tcgen05_qkv: a row stride is shorter than its row");
+  if (!x || !w || !q_out || !cos_table || !sin_table || !positions || !token_row || !block_table || !k_pages || !v_pages || !error || sm_count < 1)
+    PYLON_REFUSE("gemm_tcgen05_qkv: a tensor, the error word or the SM count is missing");
+  RotateArgs rot;
+  rot.q_out = (__nv_bfloat16*)q_out; rot.ldq = ldq; rot.q_weight = q_weight; rot.k_weight = k_weight; rot.eps = eps;
+  rot.cos_table = cos_table; rot.sin_table = sin_table; rot.table_positions = table_positions; rot.positions = positions;
+  rot.token_row = token_row; rot.block_table = block_table; rot.table_width = table_width; rot.page_size = page_size;
+  rot.k_pages = (__nv_bfloat16*)k_pages; rot.v_pages = (__nv_bfloat16*)v_pages; rot.num_pages = num_pages; rot.nq = nq; rot.nkv = nkv;
+  rot.page_error = page_error;
+  // Tile width: a multiple of the head size; the one whose rounds over the SMs cover the fewest columns.
+  const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+  int bn = 128;
+  long long best = -1;
+  for (int candidate : {256, 192, 128}) {
+    if (candidate % head_dim || (forced_columns && candidate != forced_columns)) continue;
+    const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
+    const long long rounds = (tiles + sm_count - 1) / sm_count;
+    const long long cost = rounds * (candidate + 213);   // as for the plain product
+    if (best < 0 || cost < best) { best = cost; bn = candidate; }
+  }
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, N, K, ldw, bn)) PYLON_REFUSE("gemm_tcgen05_qkv: the tensor maps could not be made");
+  if (head_dim == 128) {
+    if (bn == 256) return launch_rotate<256, 128>(map_a, map_b, M, N, K, rot, error, sm_count, stream);
+    return launch_rotate<128, 128>(map_a, map_b, M, N, K, rot, error, sm_count, stream);
+  }
+  if (bn == 256) return launch_rotate<256, 64>(map_a, map_b, M, N, K, rot, error, sm_count, stream);
+  if (bn == 192) return launch_rotate<192, 64>(map_a, map_b, M, N, K, rot, error, sm_count, stream);
+  return launch_rotate<128, 64>(map_a, map_b, M, N, K, rot, error, sm_count, stream);
 }

@@ -194,6 +194,9 @@ _SIGNATURES = {
         "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                                     c_void_p, c_int, c_void_p],
         "pylon_gemm_tcgen05_force_tile": [c_int],
+        "pylon_gemm_tcgen05_qkv_rotate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_float,
+                                          c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                          c_int, c_void_p, c_void_p, c_int, c_void_p],
     },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -611,6 +614,53 @@ def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> to
     _check(library, library.pylon_gemm_tcgen05_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), int(swiglu),
                                                     _ptr(tcgen05_error_word(x.device)), _multiprocessors(x.device), _stream()))
     return y
+
+QKV_ROTATION_MIN_ROWS = 3_072
+
+
+def qkv_rotation_fuses(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int, k_pages: torch.Tensor) -> bool:
+    """Whether :func:`linear_qkv_rotated` takes this step's QKV product: a long prompt portion, in bfloat16, heads of 64
+    or 128 rotated as a whole.  The last tile's longer epilogue has nothing to hide behind, so the fusion pays from some
+    3,000 rows on (Qwen3-4B widths: 108 us against 115 us for product and rotation kernel at 4,096 rows, 204 against 239
+    at 8,192; 61 against 59 at 2,048)."""
+    m, k = x.shape
+    return (m >= QKV_ROTATION_MIN_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and x.is_cuda and head_dim in (64, 128)
+            and rotary_dim == head_dim and k % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and _tcgen05_fills_the_sms(m, w.shape[0], _multiprocessors(x.device)))
+
+
+def linear_qkv_rotated(
+    x: torch.Tensor, w: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float, cos: torch.Tensor,
+    sin: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor, block_table: torch.Tensor, page_size: int, k_pages: torch.Tensor,
+    v_pages: torch.Tensor, nq: int, nkv: int, head_dim: int,
+) -> torch.Tensor:
+    """The fused QKV product ``x [T, K] @ w [(nq + 2 nkv) * d, K].T`` on the tcgen05 kernel with
+    :func:`qk_norm_rope_kv_write` in its epilogue: the heads are normalised and rotated from the float32 accumulators, k
+    and v go straight into their pages and q, ``[T, nq * d]`` in bfloat16, is returned; the product never goes to memory."""
+    _need_cuda(x, w, q_weight, k_weight, cos, sin, positions, token_row, block_table, k_pages, v_pages)
+    tokens, k = x.shape
+    _need(x.dim() == 2 and w.dim() == 2 and w.shape == ((nq + 2 * nkv) * head_dim, k) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+          and x.stride(1) == 1 and w.stride(1) == 1, "linear_qkv_rotated: bfloat16 x [T, K] and w [(nq + 2 nkv) * d, K]")
+    for weight in (q_weight, k_weight):
+        if weight is not None:
+            _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "linear_qkv_rotated: norm weights must be float32 [d]")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape and cos.dim() == 2 and cos.shape[1] * 2 == head_dim
+          and cos.is_contiguous() and sin.is_contiguous(), "linear_qkv_rotated: cos/sin must be float32 [positions, d / 2]")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "linear_qkv_rotated: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "linear_qkv_rotated: block_table must be contiguous int32 [rows, width]")
+    for pages in (k_pages, v_pages):
+        _need(pages.dtype == torch.bfloat16 and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, head_dim),
+              "linear_qkv_rotated: pages must be contiguous bfloat16 [pages, nkv, page_size, d]")
+    q = torch.empty((tokens, nq * head_dim), dtype=torch.bfloat16, device=x.device)
+    library = _library("gemm_tcgen05.cu")
+    _check(library, library.pylon_gemm_tcgen05_qkv_rotate(
+        _ptr(x), _ptr(w), _ptr(q), tokens, k, x.stride(0), w.stride(0), q.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin),
+        cos.shape[0], _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
+        k_pages.shape[0], nq, nkv, head_dim, _ptr(cache_write_error_word(k_pages.device)), _ptr(tcgen05_error_word(x.device)),
+        _multiprocessors(x.device), _stream()))
+    return q
+
 
 # Small integer buffers kernels use to find out which of their blocks finishes last.  They
 # are zero between launches (a kernel leaves its counters as it found them) and launches on

@@ -91,12 +91,20 @@ class GroupedQueryAttention(Mixer):
                 ops.qk_norm(qkv, q_norm, k_norm, self.qk_norm_eps, self.n_heads, self.n_kv_heads, self.head_dim)
                 q_norm = k_norm = None
             self.position.apply(qkv[:, : self.q_size], qkv[:, self.q_size : self.q_size + self.kv_size], step)
+        elif cos is not None and ops.qkv_rotation_fuses(h, self.w_qkv, self.head_dim, rotary_dim, cache.k_pages):
+            qkv = None   # a long prompt portion: norms, rotation and cache write in the product's epilogue
         else:
             qkv = ops.linear_for_rotation(h, self.w_qkv, self.head_dim, rotary_dim)   # may be partial sums: the next kernel adds them
-        q = ops.qk_norm_rope_kv_write(
-            qkv, q_norm, k_norm, self.qk_norm_eps or 0.0, cos, sin, rotary_dim, step.positions, step.token_row,
-            cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
-        )
+        if qkv is None:
+            q = ops.linear_qkv_rotated(
+                h, self.w_qkv, q_norm, k_norm, self.qk_norm_eps or 0.0, cos, sin, step.positions, step.token_row,
+                cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
+            )
+        else:
+            q = ops.qk_norm_rope_kv_write(
+                qkv, q_norm, k_norm, self.qk_norm_eps or 0.0, cos, sin, rotary_dim, step.positions, step.token_row,
+                cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim,
+            )
         context = ops.paged_attention(
             q, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,

@@ -805,6 +805,74 @@ def test_qk_norm_rope_kv_write_from_partial_sums(tokens_each, nq, nkv, d, norm, 
                                   torch.zeros(4, nkv, page, 48, device=DEVICE, dtype=torch.bfloat16), nq, nkv, 48)
 
 
+@pytest.mark.parametrize("tokens_each, nq, nkv, d, k, norm, page", [
+    ((300, 1, 150), 8, 2, 128, 256, True, 16),      # two whole row tiles and a partly empty one; a row of one token between
+    ((1, 130), 6, 3, 64, 200, True, 64),            # heads of 64: four to a tile of 256; k with a remainder
+    ((257,), 5, 1, 128, 64, False, 256),            # 7 heads: the last tile is half outside the matrix; no norms; one step of k
+    ((64, 64, 64, 64), 4, 4, 64, 72, True, 8),      # rows that end on tile edges
+])
+def test_qkv_product_with_rotation_in_its_epilogue(tokens_each, nq, nkv, d, k, norm, page):
+    """x @ w.T on the tcgen05 kernel with the q/k norms, the rotation and the cache write in its epilogue, against the
+    same in float64: q in a tensor of its own, k and v at each token's slot, nothing else in the cache touched, and the
+    same bits at the second call; a padding token (row -1) writes nothing, a page that is not there is reported."""
+    from pylon_b200.kernels import ops
+
+    eps = 1e-6
+    cache = Paged([tokens + 37 for tokens in tokens_each], list(tokens_each), nkv, d, page, torch.bfloat16, seed=11)
+    width = (nq + 2 * nkv) * d
+    torch.manual_seed(k)
+    x = torch.randn(cache.tokens, k, device=DEVICE).to(torch.bfloat16)
+    w = (torch.randn(width, k, device=DEVICE) / math.sqrt(k)).to(torch.bfloat16)
+    total = (x.double() @ w.double().T).reshape(cache.tokens, nq + 2 * nkv, d)
+    qw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    kw = torch.rand(d, device=DEVICE) + 0.5 if norm else None
+    inv_freq = 1.0 / (10_000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angles = torch.arange(512, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)
+    cos, sin = torch.cos(angles).to(DEVICE), torch.sin(angles).to(DEVICE)
+    k_before, v_before = cache.k_pages.clone(), cache.v_pages.clone()
+    call = lambda: ops.linear_qkv_rotated(x, w, qw, kw, eps, cos, sin, cache.positions, cache.token_row, cache.table, page, cache.k_pages,
+                                          cache.v_pages, nq, nkv, d)
+    q = call()
+    assert q.shape == (cache.tokens, nq * d) and q.dtype == torch.bfloat16
+
+    def reference(heads, weight):
+        if weight is not None:
+            heads = heads / torch.sqrt((heads * heads).mean(-1, keepdim=True) + eps) * weight.double()
+        c, s2 = cos[cache.positions.long()].double().unsqueeze(1), sin[cache.positions.long()].double().unsqueeze(1)
+        first, second = heads[..., : d // 2], heads[..., d // 2 :]
+        return torch.cat((first * c - second * s2, second * c + first * s2), dim=-1)
+
+    tol = tolerance(torch.bfloat16)
+    torch.testing.assert_close(q.double().reshape(cache.tokens, nq, d), reference(total[:, :nq], qw), **tol)
+    want_k, want_v = reference(total[:, nq : nq + nkv], kw), total[:, nq + nkv :]
+    written = torch.zeros_like(cache.k_pages, dtype=torch.bool)
+    for t in range(cache.tokens):
+        r, pos = int(cache.token_row[t]), int(cache.positions[t])
+        p, slot = int(cache.table[r, pos // page]), pos % page
+        torch.testing.assert_close(cache.k_pages[p, :, slot].double(), want_k[t], **tol)
+        torch.testing.assert_close(cache.v_pages[p, :, slot].double(), want_v[t], **tol)
+        written[p, :, slot] = True
+    assert torch.equal(cache.k_pages[~written], k_before[~written]) and torch.equal(cache.v_pages[~written], v_before[~written])
+    first_k, first_v = cache.k_pages.clone(), cache.v_pages.clone()
+    for _ in range(20):
+        assert torch.equal(call(), q) and torch.equal(cache.k_pages, first_k) and torch.equal(cache.v_pages, first_v)
+    assert int(ops.tcgen05_error_word(torch.device(DEVICE)).item()) == 0
+    # a padding token, and a table that names a page outside the pool
+    cache.k_pages.copy_(k_before); cache.v_pages.copy_(v_before)
+    rows = cache.token_row.clone()
+    rows[cache.tokens - 1] = -1
+    ops.linear_qkv_rotated(x, w, qw, kw, eps, cos, sin, cache.positions, rows, cache.table, page, cache.k_pages, cache.v_pages, nq, nkv, d)
+    r, pos = int(cache.token_row[-1]), int(cache.positions[cache.tokens - 1])
+    p, slot = int(cache.table[r, pos // page]), pos % page
+    assert torch.equal(cache.k_pages[p, :, slot], k_before[p, :, slot]) and torch.equal(cache.v_pages[p, :, slot], v_before[p, :, slot])
+    ops.raise_on_kernel_errors(torch.device(DEVICE))
+    table = cache.table.clone()
+    table[0, (cache.kv_lens[0] - 1) // page] = cache.k_pages.shape[0] + 5   # the page of the first row's last token
+    ops.linear_qkv_rotated(x, w, qw, kw, eps, cos, sin, cache.positions, cache.token_row, table, page, cache.k_pages, cache.v_pages, nq, nkv, d)
+    with pytest.raises(ops.KernelError, match="page"):
+        ops.raise_on_kernel_errors(torch.device(DEVICE))
+
+
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("vocab", [320, 151_936, 1000, 4099])
 def test_sample_argmax(vocab):

@@ -244,6 +244,61 @@ def test_steps_of_64_rows_at_4b_widths(wide_model, dtype, graphs):
     ops.raise_on_kernel_errors(engine.device)
 
 
+WIDE_LONG = 1_300
+
+
+@pytest.fixture(scope="module")
+def wide_long_model(tmp_path_factory):
+    folder, cfg, weights = make_model(tmp_path_factory, "wide_long", WIDE_MODEL, 35)
+    rng = np.random.default_rng(47)
+    requests = {f"s{i}": rng.integers(0, WIDE_MODEL["vocab_size"], size=n + 3).tolist() for i, n in enumerate(rng.integers(20, 200, size=8).tolist())}
+    requests["long"] = rng.integers(0, WIDE_MODEL["vocab_size"], size=WIDE_LONG).tolist()
+    expected = {rid: plain_logits(cfg, weights, tokens)[-4:] for rid, tokens in requests.items()}
+    del weights
+    torch.cuda.empty_cache()
+    return folder, requests, expected
+
+
+def test_long_portions_at_4b_widths_finish_their_heads_in_the_product(wide_long_model, monkeypatch):
+    """Portions of some 650 tokens at Qwen3-4B widths: their QKV product normalises, rotates and stores its heads in its
+    own epilogue.  Eight short prompts run as one such step, the long request's first portion alone, its second beside the eight requests' decoded tokens (rows of one token before
+    it in the step, positions that start at 650, pages of 256 that the portion crosses); the last three tokens and the
+    decoded rows then go the usual way and read what the epilogues wrote."""
+    from pylon_b200.config import EngineConfig
+    from pylon_b200.engine import Engine, StepEntry
+    from pylon_b200.kernels import ops
+
+    folder, requests, expected = wide_long_model
+    fused_rows = []
+    fused = ops.linear_qkv_rotated
+    monkeypatch.setattr(ops, "linear_qkv_rotated", lambda x, *args: (fused_rows.append(x.shape[0]), fused(x, *args))[1])
+    monkeypatch.setattr(ops, "QKV_ROTATION_MIN_ROWS", 512)   # the engine fuses from some 3,000 rows on, where it pays; the test makes do with fewer
+    short = [f"s{i}" for i in range(8)]
+    engine = Engine(folder, EngineConfig(dtype="bfloat16", page_size=256, max_cache_tokens=(8 + 6) * 256, max_context=1_536, max_batch_size=9,
+                                         prefill_chunk_size=1_024, cuda_graphs=False))
+    live = {rid: engine.open(rid, 256) for rid in short}
+    live["long"] = engine.open("long", WIDE_LONG)
+    engine.step([StepEntry(live[rid], requests[rid][:-3], ()) for rid in short])
+    got = {rid: [] for rid in requests}
+    engine.step([StepEntry(live["long"], requests["long"][:650], ())])
+    logits = engine.step([StepEntry(live[rid], [requests[rid][-3]], (0,)) for rid in short]
+                         + [StepEntry(live["long"], requests["long"][650 : WIDE_LONG - 3], (WIDE_LONG - 3 - 650 - 1,))]).float().cpu().numpy()
+    for index, rid in enumerate(short):
+        got[rid].append(logits[index])
+    got["long"].append(logits[len(short)])
+    prompts = sum(len(requests[rid]) - 3 for rid in short)   # the eight short prompts together are long enough as well
+    assert fused_rows == [prompts] * 2 + [650] * 2 + [len(short) + WIDE_LONG - 3 - 650] * 2, fused_rows   # two layers a step
+    logits = engine.step([StepEntry(live["long"], requests["long"][WIDE_LONG - 3 :], (0, 1, 2))]
+                         + [StepEntry(live[rid], [requests[rid][-2]], (0,)) for rid in short]).float().cpu().numpy()
+    got["long"] += list(logits[:3])
+    for index, rid in enumerate(short):
+        got[rid].append(logits[3 + index])
+    check(np.stack(got["long"]), expected["long"], "bfloat16", "long")
+    for rid in short:
+        check(np.stack(got[rid]), expected[rid][1:3], "bfloat16", rid)
+    ops.raise_on_kernel_errors(engine.device)
+
+
 # ---------------------------------------------------------------------------------------
 # (d) steps the scheduler makes
 # ---------------------------------------------------------------------------------------
