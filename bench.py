@@ -555,7 +555,7 @@ def main() -> int:
     if args.profile:
         engine_config = EngineConfig(
             dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=max(args.batch, 2) * CONTEXT, max_context=CONTEXT,
-            max_batch_size=max(args.batch, 2), prefill_chunk_size=PREFILL_TOKENS, cuda_graphs=False,
+            max_batch_size=max(args.batch, 2), prefill_chunk_size=max(PREFILL_TOKENS, args.profile_tokens), cuda_graphs=False,
         )
     engine = Engine(None, engine_config, device="cuda:0", model_config=model_config, random_seed=0)
     if args.profile:
