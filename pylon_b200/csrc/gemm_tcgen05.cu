@@ -557,7 +557,7 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
     const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
     const long long rounds = (tiles + sm_count - 1) / sm_count;
     // A tile's time is what its operands take to arrive from L2, (128 + width) rows of k a step, plus its start and end:
-    // measured per round 11.9, 12.2, 13.9 and 16.3 us at widths 128, 160, 192 and 256 (k = 2,560), which is width + 213.
+    // one pass of all SMs over their tiles took 11.9, 12.2, 13.9 and 16.3 us at widths 128, 160, 192 and 256 (k = 2,560), which is width + 213.
     long long cost = rounds * (candidate + 213);
     if (candidate > 256) cost += rounds * 100;   // one accumulator buffer: the epilogue of a tile holds up the next (21 us a round)
     if (best < 0 || cost < best) { best = cost; bn = candidate; }
