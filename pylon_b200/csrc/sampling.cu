@@ -14,6 +14,23 @@ namespace pylon {
 
 constexpr int SAMPLE_THREADS = 1024;
 
+// Where a launch leaves a second copy of its result for the host, in pinned host memory that the device can write
+// (null: none): the tokens, and the kernels' error words as they stand when the step's last kernel, this one, runs.  The
+// host then needs no copy behind the launch, only to wait for it.
+struct SampleMirror {
+  int* tokens;          // [rows]
+  const int* words;     // [4] on the device
+  int* words_copy;      // [4]
+};
+__device__ __forceinline__ void sample_emit(int* __restrict__ out, const SampleMirror& mirror, int row, int token) {
+  out[row] = token;
+  if (mirror.tokens) mirror.tokens[row] = token;
+  if (row == 0 && mirror.words_copy) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mirror.words_copy[i] = mirror.words[i];
+  }
+}
+
 struct ArgMax {
   float value;
   int index;
@@ -61,7 +78,7 @@ __device__ float mass_above(const float* __restrict__ logits, int vocab, float m
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
-    const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out) {
+    const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out, const SampleMirror mirror) {
   __shared__ ArgMax arg_scratch[33];
   __shared__ float scratch[33];
   __shared__ float prefix[SAMPLE_THREADS];
@@ -95,7 +112,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
   best = block_argmax(best, arg_scratch);
   const float t = temperature ? temperature[row] : 0.f;
   if (!(t > 0.f) || best.index >= vocab) {  // greedy (or a row of NaN: index stays in range)
-    if (tid == 0) out[row] = best.index < vocab ? best.index : 0;
+    if (tid == 0) sample_emit(out, mirror, row, best.index < vocab ? best.index : 0);
     return;
   }
   const float inv_t = 1.f / t;
@@ -157,7 +174,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
   }
   __syncthreads();
   // Rounding at a segment edge can leave no owner: fall back to the most likely token.
-  if (tid == 0) out[row] = chosen != 0xffffffffu ? (int)chosen : best.index;
+  if (tid == 0) sample_emit(out, mirror, row, chosen != 0xffffffffu ? (int)chosen : best.index);
 }
 
 
@@ -206,7 +223,7 @@ __device__ __forceinline__ float sample_total(const unsigned* slots) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_cluster_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, int slice, const float* __restrict__ temperature,
-    const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out) {
+    const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out, const SampleMirror mirror) {
   extern __shared__ float weights[];   // [slice]: this block's share of the row
   __shared__ ArgMax arg_scratch[33];
   __shared__ float scratch[33];
@@ -233,7 +250,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_cluster_kernel(
   for (int c = 0; c < SAMPLE_CLUSTER; ++c) best = better(best, ArgMax{__uint_as_float(slots[0][c]), (int)index_slots[c]});
   const float t = temperature ? temperature[row] : 0.f;
   if (!(t > 0.f) || best.index >= vocab) {   // greedy (or a row of NaN: the index stays in range): the same for every block
-    if (rank == 0 && tid == 0) out[row] = best.index < vocab ? best.index : 0;
+    if (rank == 0 && tid == 0) sample_emit(out, mirror, row, best.index < vocab ? best.index : 0);
     return;
   }
   const float inv_t = 1.f / t, max_logit = best.value;
@@ -324,18 +341,22 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_cluster_kernel(
     int token = best.index;
     for (int c = SAMPLE_CLUSTER - 1; c >= 0; --c)
       if ((int)index_slots[c] >= 0) token = (int)index_slots[c];
-    out[row] = token;
+    sample_emit(out, mirror, row, token);
   }
 }
 
 }  // namespace pylon
 
 // logits: float32 [rows, vocab] with `row_stride` elements between rows.  temperature, top_p
-// and uniform are per row (device pointers; null temperature means arg-max for every row).
+// and uniform are per row (pointers the device can read: device memory or pinned host memory; null temperature means
+// arg-max for every row).  tokens_copy (int [rows]) and words_copy (int [4], with words, the device's four error words):
+// pinned host memory, or null; the kernel leaves the tokens, and the words as they stand, there as well.
 extern "C" int pylon_sample(const float* logits, long long row_stride, int rows, int vocab,
                             const float* temperature, const float* top_p, const float* uniform, int* out,
-                            cudaStream_t stream) {
+                            int* tokens_copy, const int* words, int* words_copy, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (words_copy && !words) PYLON_REFUSE("sample: a copy of the error words without the words");
+  const pylon::SampleMirror mirror{tokens_copy, words, words_copy};
   if (vocab <= 0 || row_stride < vocab) PYLON_REFUSE("sample: vocabulary %d, row stride %lld", vocab, row_stride);
   // Rows that may be drawn from (a temperature is given) go to a cluster of blocks each, where the device places such
   // clusters and a slice of the row fits a block's shared memory; arg-max alone is one pass, for which one block does.
@@ -369,11 +390,11 @@ extern "C" int pylon_sample(const float* logits, long long row_stride, int rows,
       attribute[0].id = cudaLaunchAttributeClusterDimension;
       attribute[0].val.clusterDim.x = pylon::SAMPLE_CLUSTER; attribute[0].val.clusterDim.y = 1; attribute[0].val.clusterDim.z = 1;
       config.attrs = attribute; config.numAttrs = 1;
-      cudaLaunchKernelEx(&config, pylon::sample_cluster_kernel, logits, row_stride, vocab, slice, temperature, top_p, uniform, out);
+      cudaLaunchKernelEx(&config, pylon::sample_cluster_kernel, logits, row_stride, vocab, slice, temperature, top_p, uniform, out, mirror);
       PYLON_CHECK_LAUNCH("sample");
     }
   }
   pylon::sample_kernel<<<rows, pylon::SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, top_p,
-                                                                   uniform, out);
+                                                                   uniform, out, mirror);
   PYLON_CHECK_LAUNCH("sample");
 }

@@ -215,7 +215,7 @@ _SIGNATURES = {
                                           c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "sampling.cu": {
-        "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
 }
 
@@ -859,19 +859,31 @@ def sample(
     top_p: Optional[torch.Tensor] = None,
     uniform: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
+    host_copy: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One token per row of float32 ``logits [R, vocab]``: arg-max where a row's temperature
     is 0 (or none is given), else a draw from ``softmax(logits / T)`` cut to the ``top_p``
-    nucleus, using the row's number from ``uniform`` (float32 in [0, 1))."""
-    _need_cuda(logits, temperature, top_p, uniform, out)
+    nucleus, using the row's number from ``uniform`` (float32 in [0, 1)).  The per-row parameters may lie in pinned
+    host memory, which the kernel then reads where it is.  ``host_copy``: int32 ``[R + 4]`` in pinned host memory, into
+    which the kernel also writes the tokens and, behind them, the kernels' four error words as they stand: whoever
+    waits for the launch can read both there, and no copy has to follow it."""
+    _need_cuda(logits, out)
     _need(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be float32 [R, vocab]")
     rows, vocab = logits.shape
     for per_row in (temperature, top_p, uniform):
         if per_row is not None:
-            _need(per_row.dtype == torch.float32 and per_row.is_contiguous() and per_row.shape[0] >= rows, "sample: per-row parameters must be float32 [R]")
+            _need(per_row.dtype == torch.float32 and per_row.is_contiguous() and per_row.shape[0] >= rows
+                  and (per_row.is_cuda or per_row.is_pinned()), "sample: per-row parameters must be float32 [R] on the device or in pinned memory")
+    words = None
+    if host_copy is not None:
+        _need(host_copy.dtype == torch.int32 and host_copy.is_contiguous() and host_copy.shape == (rows + 4,) and host_copy.is_pinned(),
+              "sample: host_copy must be int32 [R + 4] in pinned memory")
+        words = _error_words(logits.device)
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     _need(out.dtype == torch.int32 and out.is_contiguous() and out.shape[0] >= rows, "sample: out must be int32 [R]")
     library = _library("sampling.cu")
-    _check(library, library.pylon_sample(_ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(out), _stream()))
+    _check(library, library.pylon_sample(
+        _ptr(logits), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(out),
+        None if host_copy is None else host_copy.data_ptr(), _ptr(words), None if host_copy is None else host_copy.data_ptr() + 4 * rows, _stream()))
     return out

@@ -31,13 +31,15 @@ class SampledTokens:
     """The tokens of one sampling launch: on the device at once (``device``, int32 ``[rows]``, for a next step that
     takes its tokens from there), on the host when :meth:`result` has waited for them."""
 
-    def __init__(self, device_tokens: torch.Tensor, check_errors: bool) -> None:
+    def __init__(self, device_tokens: torch.Tensor, host_copy: torch.Tensor, check_errors: bool, keep: tuple = ()) -> None:
+        """``host_copy``: the pinned int32 ``[rows + 4]`` buffer into which the sampling kernel itself writes the tokens
+        and the kernels' error words (no copy is queued behind the launch: the next step's work follows it at once).
+        ``keep``: pinned buffers the kernel reads, held until it has run."""
         self.device = device_tokens
         self.rows = device_tokens.shape[0]
         self._check_errors = check_errors
-        self._error_words = ops.queue_error_word_copy(device_tokens.device) if check_errors else None   # behind the step's kernels
-        self._host = torch.empty((self.rows,), dtype=torch.int32, pin_memory=True)
-        self._host.copy_(device_tokens, non_blocking=True)
+        self._host = host_copy
+        self._keep = keep
         self._arrived = torch.cuda.Event()
         self._arrived.record()
         self._tokens: Optional[list[int]] = None
@@ -47,10 +49,19 @@ class SampledTokens:
         that its result is void."""
         if self._tokens is None:
             self._arrived.synchronize()
-            if self._error_words is not None:
-                ops.raise_on_kernel_errors(self.device.device, words=self._error_words)
-            self._tokens = self._host.tolist()
+            self._keep = ()
+            if self._check_errors:
+                ops.raise_on_kernel_errors(self.device.device, words=self._host[self.rows:])
+            self._tokens = self._host[: self.rows].tolist()
         return self._tokens
+
+    def __del__(self) -> None:
+        # The kernel writes into pinned memory that goes back to the allocator with this object: not before it has run.
+        if self._tokens is None:
+            try:
+                self._arrived.synchronize()
+            except Exception:
+                pass
 
 
 class Sampler:
@@ -64,16 +75,19 @@ class Sampler:
         rows = logits.shape[0]
         if rows != len(params) or rows != len(randoms):
             raise ValueError("one set of sampling options and one random stream per row of logits")
+        host_copy = torch.zeros((rows + 4,), dtype=torch.int32, pin_memory=True)
         if all(p.greedy for p in params):
-            return SampledTokens(ops.sample(logits), check_errors)
-        host = torch.empty((3, rows), dtype=torch.float32, pin_memory=True)
-        values = host.numpy()
+            return SampledTokens(ops.sample(logits, host_copy=host_copy), host_copy, check_errors)
+        # The kernel reads the rows' options where the host wrote them: a copy to the device would stand between this
+        # step's last kernel and the next step's first.
+        options = torch.empty((3, rows), dtype=torch.float32, pin_memory=True)
+        values = options.numpy()
         for row, (p, random) in enumerate(zip(params, randoms)):
             values[0, row] = p.temperature
             values[1, row] = p.top_p
             values[2, row] = 0.0 if p.greedy or random is None else random.next_uniform()
-        device_values = host.to(self.device, non_blocking=True)
-        return SampledTokens(ops.sample(logits, device_values[0], device_values[1], device_values[2]), check_errors)
+        tokens = ops.sample(logits, options[0], options[1], options[2], host_copy=host_copy)
+        return SampledTokens(tokens, host_copy, check_errors, keep=(options,))
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[Optional[RequestRandom]]) -> list[int]:
         """The same, waited for: one token id per row."""

@@ -940,6 +940,43 @@ def test_sample_rows_of_every_kind_in_one_call(vocab):
         assert ops.sample(logits, temperature, top_p, uniform).tolist() == out
 
 
+@pytest.mark.parametrize("vocab", [777, 151_936])
+def test_sample_reads_and_writes_pinned_host_memory(vocab):
+    """The rows' options may lie in pinned host memory, and the kernel leaves the tokens and the kernels' four error words
+    in a pinned buffer of the caller: the same tokens as with everything on the device, nothing to copy afterwards."""
+    from pylon_b200.kernels import ops
+
+    device = torch.device(DEVICE)
+    ops.raise_on_kernel_errors(device)
+    rows = 9
+    torch.manual_seed(vocab)
+    logits = torch.randn(rows, vocab, device=DEVICE) * 2
+    options = torch.empty((3, rows), dtype=torch.float32, pin_memory=True)
+    options[0] = torch.tensor([0.0, 0.7, 1.0, 0.2, 1.5, 0.0, 0.9, 1.0, 0.4])
+    options[1] = torch.tensor([1.0, 0.9, 1.0, 0.95, 0.5, 1.0, 0.3, 1.0, 0.8])
+    options[2] = torch.rand(rows)
+    on_device = options.to(DEVICE)
+    want = ops.sample(logits, on_device[0], on_device[1], on_device[2]).tolist()
+    host_copy = torch.full((rows + 4,), -7, dtype=torch.int32, pin_memory=True)
+    got = ops.sample(logits, options[0], options[1], options[2], host_copy=host_copy)
+    torch.cuda.synchronize()
+    assert got.tolist() == want and host_copy[:rows].tolist() == want and host_copy[rows:].tolist() == [0, 0, 0, 0]
+    greedy_copy = torch.full((rows + 4,), -7, dtype=torch.int32, pin_memory=True)
+    greedy = ops.sample(logits, host_copy=greedy_copy)
+    torch.cuda.synchronize()
+    assert greedy_copy[:rows].tolist() == greedy.tolist() == logits.argmax(-1).tolist()
+    # the words as they stand when the kernel runs (written from the host here: no kernel is made to give up)
+    ops.stream_error_word(device).fill_(3)
+    ops.sample(logits, host_copy=host_copy)
+    torch.cuda.synchronize()
+    assert host_copy[rows:].tolist() == [0, 0, 3, 0]
+    with pytest.raises(ops.KernelError, match="TMA-fed decode product"):
+        ops.raise_on_kernel_errors(device, words=host_copy[rows:])
+    ops.raise_on_kernel_errors(device)
+    with pytest.raises(ops.KernelError, match="pinned"):
+        ops.sample(logits, host_copy=torch.zeros(rows + 4, dtype=torch.int32))
+
+
 def test_sample_mixed_rows_and_distribution():
     from pylon_b200.kernels import ops
 
