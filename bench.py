@@ -8,7 +8,7 @@ real prefill through the engine).  ``value`` is decoded tokens a second timed on
 over exactly K steps of the step function; ``e2e`` is the same through the public entry
 point (``Engine.submit`` / ``Engine.tick``: host token lists in, host token lists out, with
 the scheduler, the host-to-device copy of each step's inputs and the device-to-host read of
-its tokens inside the timed region).  ``prefill`` is one 2,048-token prompt in one step;
+its tokens inside the timed region; the median of the same R repeats of K ticks, on the host's clock).  ``prefill`` is one 2,048-token prompt in one step;
 ``roofline`` relates the decode step to HBM bandwidth.  The K timed steps are repeated R times
 (``config.repeats``); ``value`` is the median repeat, ``spread`` its lowest and highest, and
 ``clocks.sm_mhz_per_repeat`` the SM clock sampled during each.  ``points`` holds the other sizes
@@ -306,16 +306,18 @@ def float32_14b_check(torch) -> dict:
             "logit_spread": float(expected.std())}
 
 
-def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
+def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng, repeats: int = 1) -> dict:
     """The same decode through submit()/tick(): host tokens in, host tokens out.  Prompts are
     sized so that every request is still decoding when the timed ticks end (requests finish
-    their prompts at different ticks), and the value counts the tokens the ticks returned."""
+    their prompts at different ticks), and the value counts the tokens the ticks returned.  The K
+    timed ticks are repeated ``repeats`` times, each between synchronisations and on the host's clock;
+    the value is that of the median repeat (56 ms of ticks by themselves gave figures 2 % apart)."""
     from pylon_b200.engine.step import StepLayout
     from pylon_b200.sampling import SamplingParams
 
     vocab = engine.spec.vocab_size
     prompt_ticks = batch * -(-CONTEXT // PREFILL_TOKENS)          # ticks until the last prompt is in
-    new_tokens = warmup + steps + prompt_ticks + 8
+    new_tokens = warmup + repeats * steps + prompt_ticks + 8
     prompt_length = CONTEXT - new_tokens
     params = SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True)
     for _ in range(batch):
@@ -325,21 +327,25 @@ def time_e2e(engine, torch, batch: int, steps: int, warmup: int, rng) -> dict:
         engine.tick()
     for _ in range(warmup):
         engine.tick()
-    torch.cuda.synchronize()
-    before = sum(len(r.output_ids) for r in scheduler.active)
-    started = time.perf_counter()
-    finished = []
-    for _ in range(steps):
-        finished += engine.tick()
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - started
-    produced = sum(len(r.output_ids) for r in scheduler.active) + sum(len(f.output_ids) for f in finished) - before
-    assert not finished and produced == batch * steps, (len(finished), produced)
+    rates = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        before = sum(len(r.output_ids) for r in scheduler.active)
+        started = time.perf_counter()
+        finished = []
+        for _ in range(steps):
+            finished += engine.tick()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - started
+        produced = sum(len(r.output_ids) for r in scheduler.active) + sum(len(f.output_ids) for f in finished) - before
+        assert not finished and produced == batch * steps, (len(finished), produced)
+        rates.append(produced / seconds)
     while scheduler.has_work():
         engine.tick()
     # per step: the packed int32 metadata buffer goes up; one int32 token per request and the kernels' four error words come back
     layout = StepLayout(tokens=batch, rows=batch, logits=batch, table_widths=(CONTEXT // PAGE_SIZE,))
-    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4, "d2h_bytes_per_step": batch * 4 + 16}
+    return {"value": sorted(rates)[len(rates) // 2], "unit": "tokens/s", "h2d_bytes_per_step": layout.total * 4, "d2h_bytes_per_step": batch * 4 + 16,
+            "spread": [round(min(rates), 1), round(max(rates), 1)]}
 
 
 def time_prefill(engine, torch, repeats: int, rng) -> dict:
@@ -568,7 +574,7 @@ def main() -> int:
         decode = time_decode(engine, torch, ops, args.batch, args.steps, args.warmup, rng, repeats=REPEATS)
     clocks = sampler.summary(decode["windows"][0][0], decode["windows"][-1][1])
     clocks["sm_mhz_per_repeat"] = [sampler.summary(begin, end)["sm_mhz"] for begin, end in decode["windows"]]
-    e2e = time_e2e(engine, torch, args.batch, args.steps, args.warmup, rng)
+    e2e = time_e2e(engine, torch, args.batch, args.steps, args.warmup, rng, repeats=REPEATS)
     points = {}
     if not args.skip_points:
         for batch in (1, 64):
